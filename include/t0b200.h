@@ -1,0 +1,293 @@
+/*
+ * t0b200.h -- C ABI of libt0b200.so: the B200 (sm_100a) implementation of T0-GPU's bf16 GEMM hot path.
+ *
+ * This is the boundary a binding of the reference's Rust crate (an `extern "C"` -sys module), a C++
+ * program or Python ctypes links against.  Plain pointers and sizes only.  Device pointers are passed
+ * as uint64_t, like the reference's `GpuBuffer::gpu_addr()` (src/kfd/mod.rs:947-1055).
+ *
+ * Conventions
+ *   - every function that can fail returns int32_t: 0 = ok, negative = T0B_ERR_*; the message is
+ *     available from t0b_last_error(ctx) (the reference returns Result<_, String>).
+ *   - after any CUDA error the context is "poisoned" and refuses further launches, as the reference's
+ *     GpuRuntime does after a queue timeout (src/ignis/gpu_context.rs:149-157, 270-272, 284-287).
+ *   - there is no CPU fallback: without a CUDA device t0b_ctx_create fails.
+ *   - a context is thread-safe; all launches of a context go to one CUDA stream.
+ */
+#ifndef T0B200_H
+#define T0B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define T0B_API __attribute__((visibility("default")))
+#else
+#define T0B_API
+#endif
+
+typedef struct t0b_ctx t0b_ctx;
+
+enum {
+    T0B_OK = 0,
+    T0B_ERR_INVALID = -1,    /* bad argument (dims, alignment, null pointer, undersized buffer) */
+    T0B_ERR_CUDA = -2,       /* a CUDA runtime/driver call failed; context is poisoned */
+    T0B_ERR_POISONED = -3,   /* context refused the call because an earlier error poisoned it */
+    T0B_ERR_DEVICE = -4,     /* a kernel reported a device status code (bounded wait ran out) */
+    T0B_ERR_NOMEM = -5,
+    T0B_ERR_UNSUPPORTED = -6
+};
+
+/* ------------------------------------------------------------------------------------------------
+ * GemmConfig and the generator front-end (host only, no context needed).
+ * Mirrors `struct GemmConfig` and friends, src/t0/gemm_gen.rs:23-84.
+ * ---------------------------------------------------------------------------------------------- */
+
+enum { T0B_TRANSPOSE_NT = 0, T0B_TRANSPOSE_NN = 1 };                       /* GemmTranspose, gemm_gen.rs:23-33 */
+enum { T0B_EPI_STORE_F32 = 0, T0B_EPI_BIAS_ADD = 1, T0B_EPI_BIAS_ADD_RELU = 2, /* EpilogueOp, gemm_gen.rs:40-49 */
+       T0B_EPI_RELU = 3, T0B_EPI_SILU = 4, T0B_EPI_GELU_SIGMOID = 5,           /* tile_ir EpilogueOp members,   */
+       T0B_EPI_SCALE = 6, T0B_EPI_ABS = 7, T0B_EPI_NEG = 8 };                  /* src/t0/tile_ir.rs:41-62       */
+enum { T0B_OUT_F32 = 0, T0B_OUT_BF16 = 1 };
+
+typedef struct t0b_gemm_config {
+    uint32_t tile_m, tile_n, tile_k;
+    uint32_t wg_size;
+    uint32_t use_lds, double_buffer;
+    uint32_t split_k;        /* 0 = None (the reference's Option<u32>) */
+    uint32_t lds_pad, n_col_passes;
+    uint32_t swap_grid, wgp_mode;
+    uint32_t transpose;      /* T0B_TRANSPOSE_* (a name tag in the reference; the data layout is given per call) */
+    uint32_t epilogue;       /* T0B_EPI_* */
+} t0b_gemm_config;
+
+/* What a GemmConfig resolves to on B200: the kernel variant that will actually run. */
+typedef struct t0b_gemm_plan {
+    uint32_t bm, bn, bk;       /* cluster tile: bm = 128 * cta_group */
+    uint32_t cta_group;        /* 1, or 2 = CTA pair sharing one tcgen05.mma (from wgp_mode / tile_m >= 256) */
+    uint32_t stages;
+    uint32_t split_k;          /* effective split (>= 1); may be lower than asked when K has too few 64-blocks */
+    uint32_t kb_per_split;     /* 64-wide K blocks per split */
+    uint32_t use_tma;          /* 0 = operands not TMA-addressable, CUDA-core kernel is used */
+    uint32_t grid;             /* CTAs launched */
+    uint32_t smem_bytes;
+} t0b_gemm_plan;
+
+/* GemmConfig presets by name ("16x64_k16", "32x64_direct", "32x64_k16", "32x64_k32", "32x128_k16", "64x64_k16",
+ * "64x64_k32", "128x64_k16", "64x128_k16", "128x64_k32", "128x128_k16", "64x64_k64", "128x128_2pass",
+ * "64x128_2pass"): gemm_gen.rs:86-145.  B200-native presets: "b200_128x64", "b200_128x128", "b200_128x256",
+ * "b200_256x128", "b200_256x256". */
+T0B_API int32_t t0b_config_preset(const char* name, t0b_gemm_config* out);
+/* GemmConfig::name(), gemm_gen.rs:207-227 (the kernel-cache / autotune key). Returns the length written. */
+T0B_API int32_t t0b_config_name(const t0b_gemm_config* cfg, char* buf, size_t cap);
+/* sweep_configs(), gemm_gen.rs:231-243; standard_configs(), :382-399. Return the count (<= cap written). */
+T0B_API int32_t t0b_sweep_configs(t0b_gemm_config* out, int32_t cap);
+T0B_API int32_t t0b_standard_configs(t0b_gemm_config* out, int32_t cap);
+/* Derived getters, gemm_gen.rs:147-205. */
+T0B_API uint32_t t0b_config_lds_total(const t0b_gemm_config* cfg);
+T0B_API uint32_t t0b_config_estimated_vgprs(const t0b_gemm_config* cfg);
+T0B_API int32_t t0b_config_is_feasible(const t0b_gemm_config* cfg);
+
+/* auto_select(m, k, n): gemm_gen.rs:320-322.  NOTE the argument order (M, K, N).  Returns the config the
+ * measured B200 table picks for the shape (cost_model::predict_best in the reference). */
+T0B_API int32_t t0b_auto_select(uint32_t m, uint32_t k, uint32_t n, t0b_gemm_config* out);
+/* auto_select_legacy(m, k, n): gemm_gen.rs:331-379, the 7-branch heuristic kept for A/B comparison. */
+T0B_API int32_t t0b_auto_select_legacy(uint32_t m, uint32_t k, uint32_t n, t0b_gemm_config* out);
+/* auto_select_backward_{data,weight}(m, n_orig, k_orig): gemm_gen.rs:482-486, 517-521. */
+T0B_API int32_t t0b_auto_select_backward_data(uint32_t m, uint32_t n_orig, uint32_t k_orig, t0b_gemm_config* out);
+T0B_API int32_t t0b_auto_select_backward_weight(uint32_t m, uint32_t n_orig, uint32_t k_orig, t0b_gemm_config* out);
+
+/* compute_grid / compute_grid_split_k / compute_grid_auto: gemm_gen.rs:286-309, 402-409.  Grid x is in
+ * THREADS (tiles * wg_size) exactly as the reference returns it. split_k must be a power of two. */
+T0B_API int32_t t0b_compute_grid(const t0b_gemm_config* cfg, uint32_t m, uint32_t n, uint32_t* gx, uint32_t* gy);
+T0B_API int32_t t0b_compute_grid_split_k(const t0b_gemm_config* cfg, uint32_t m, uint32_t n, uint32_t split_k,
+                                         uint32_t* gx, uint32_t* gy);
+T0B_API int32_t t0b_compute_grid_auto(const t0b_gemm_config* cfg, uint32_t m, uint32_t n, uint32_t* gx, uint32_t* gy);
+/* compute_grid_backward_{data,weight}: gemm_gen.rs:505-508, 539-542. */
+T0B_API int32_t t0b_compute_grid_backward_data(const t0b_gemm_config* cfg, uint32_t m, uint32_t k_orig, uint32_t* gx,
+                                               uint32_t* gy);
+T0B_API int32_t t0b_compute_grid_backward_weight(const t0b_gemm_config* cfg, uint32_t n_orig, uint32_t k_orig,
+                                                 uint32_t* gx, uint32_t* gy);
+
+/* build_kernargs(x, wt, y, k, n, m, cfg) -> 40 bytes: gemm_gen.rs:414-430.  NOTE the order (k, n, m).
+ * Layout [X:u64, WT:u64, Y:u64, K:u32, N:u32, 0:u32, y_split_stride:u32], little endian. */
+T0B_API int32_t t0b_build_kernargs(uint64_t x, uint64_t wt, uint64_t y, uint32_t k, uint32_t n, uint32_t m,
+                                   const t0b_gemm_config* cfg, uint8_t out[40]);
+/* build_kernargs_with_bias -> 48 bytes (bias pointer at 40..48): gemm_gen.rs:438-456. */
+T0B_API int32_t t0b_build_kernargs_with_bias(uint64_t x, uint64_t wt, uint64_t y, uint32_t k, uint32_t n, uint32_t m,
+                                             const t0b_gemm_config* cfg, uint64_t bias, uint8_t out[48]);
+/* tile_ir::build_kernargs_m -> 44 bytes (M at 40..44, y_split_stride always 0): src/t0/tile_ir.rs:3173-3190. */
+T0B_API int32_t t0b_build_kernargs_m(uint64_t x, uint64_t wt, uint64_t y, uint32_t k, uint32_t n, uint32_t m,
+                                     uint8_t out[44]);
+/* build_kernargs_backward_{data,weight}: gemm_gen.rs:495-502, 529-536. */
+T0B_API int32_t t0b_build_kernargs_backward_data(uint64_t dy, uint64_t w, uint64_t dx, uint32_t m, uint32_t n_orig,
+                                                 uint32_t k_orig, const t0b_gemm_config* cfg, uint8_t out[40]);
+T0B_API int32_t t0b_build_kernargs_backward_weight(uint64_t dy_t, uint64_t x_t, uint64_t dw, uint32_t m,
+                                                   uint32_t n_orig, uint32_t k_orig, const t0b_gemm_config* cfg,
+                                                   uint8_t out[40]);
+
+/* Resolve a GemmConfig for a problem to the B200 kernel variant (no launch, no device needed when
+ * num_sms > 0 is given; pass 0 to use 148). */
+T0B_API int32_t t0b_resolve_plan(const t0b_gemm_config* cfg, uint32_t m, uint32_t n, uint32_t k, int32_t trans_a,
+                                 int32_t trans_b, uint64_t lda, uint64_t ldb, int32_t num_sms, t0b_gemm_plan* out);
+
+/* ------------------------------------------------------------------------------------------------
+ * Runtime: context, device memory, copies.  Replaces GpuRuntime (src/ignis/gpu_context.rs:30-106, 113-483)
+ * and the KFD objects under it (KfdDevice / GpuBuffer / AqlQueue / DispatchPool, src/kfd/mod.rs).
+ * ---------------------------------------------------------------------------------------------- */
+
+/* GpuRuntime::new(), gpu_context.rs:113.  Fails (T0B_ERR_CUDA) when no CUDA device is usable. */
+T0B_API int32_t t0b_ctx_create(int32_t device, t0b_ctx** out);
+T0B_API void t0b_ctx_destroy(t0b_ctx* ctx);
+/* Launch on a caller-owned cudaStream_t (e.g. the current stream of a host framework); NULL restores the
+ * context's own stream.  The reference has a single AQL queue per runtime (src/kfd/mod.rs:1141). */
+T0B_API int32_t t0b_ctx_set_stream(t0b_ctx* ctx, void* cuda_stream);
+T0B_API void* t0b_ctx_stream(t0b_ctx* ctx);
+T0B_API const char* t0b_last_error(t0b_ctx* ctx);
+/* GpuRuntime::is_poisoned(), gpu_context.rs:149-157. */
+T0B_API int32_t t0b_is_poisoned(t0b_ctx* ctx);
+T0B_API int32_t t0b_num_sms(t0b_ctx* ctx);
+/* Device status word written by kernels whose bounded waits ran out (0 = none). Reading clears it when
+ * `clear` is non-zero.  Takes the place of the reference's wait_read_ptr timeout (src/kfd/mod.rs:1607-1642). */
+T0B_API int32_t t0b_device_status(t0b_ctx* ctx, int32_t clear);
+/* Limit of every in-kernel wait, in nanoseconds (default 2e9). */
+T0B_API int32_t t0b_set_wait_limit_ns(t0b_ctx* ctx, uint64_t ns);
+
+/* GpuRuntime::alloc / alloc_zero / recycle, gpu_context.rs:437-457; BufferPool keyed by 4 KiB-rounded size, :48.
+ * t0b_alloc takes from the pool first; t0b_recycle returns a buffer to the pool; t0b_free releases it. */
+T0B_API int32_t t0b_alloc(t0b_ctx* ctx, size_t bytes, uint64_t* dptr);
+T0B_API int32_t t0b_alloc_zero(t0b_ctx* ctx, size_t bytes, uint64_t* dptr);
+T0B_API int32_t t0b_recycle(t0b_ctx* ctx, uint64_t dptr);
+T0B_API int32_t t0b_free(t0b_ctx* ctx, uint64_t dptr);
+/* BufferPool::cached_bytes, gpu_context.rs:76-78, plus hit/miss counters. */
+T0B_API int32_t t0b_pool_stats(t0b_ctx* ctx, uint64_t* cached_bytes, uint64_t* hits, uint64_t* misses);
+/* GpuBuffer::write / read / zero, src/kfd/mod.rs:962-1040: explicit copies (the reference maps VRAM into the
+ * host).  Synchronous with respect to the host. */
+T0B_API int32_t t0b_memcpy_h2d(t0b_ctx* ctx, uint64_t dst, const void* src, size_t bytes);
+T0B_API int32_t t0b_memcpy_d2h(t0b_ctx* ctx, void* dst, uint64_t src, size_t bytes);
+T0B_API int32_t t0b_memset0(t0b_ctx* ctx, uint64_t dst, size_t bytes);
+/* GpuRuntime::synchronize / wait_idle, gpu_context.rs:297-332.  Also checks the device status word. */
+T0B_API int32_t t0b_sync(t0b_ctx* ctx);
+
+/* ------------------------------------------------------------------------------------------------
+ * GEMM dispatch
+ * ---------------------------------------------------------------------------------------------- */
+
+/* C[M,N] = epilogue(op(A) * op(B)), bf16 inputs, f32 accumulate.
+ *   trans_a = 0: A is [M,K] with row pitch lda;  1: A is [K,M] with row pitch lda.
+ *   trans_b = 0: B is [K,N] with row pitch ldb ("NN");  1: B is [N,K] with row pitch ldb ("NT", the
+ *   reference kernels' only native layout, src/t0/gemm_gen.rs:25).
+ *   cfg may be NULL (auto_select).  out_dtype: T0B_OUT_F32 / T0B_OUT_BF16 (RNE).  epilogue: T0B_EPI_*; bias f32[N].
+ *   Split-K (cfg->split_k > 1) needs split_k*M*N*4 bytes of workspace: pass one, or 0 to let the context keep
+ *   a grow-only workspace.  The partial slabs are summed in slab order by a second kernel (deterministic).
+ *   async = 0 waits for completion (GpuRuntime::dispatch, gpu_context.rs:264); 1 only enqueues (dispatch_async, :332).
+ * Entry point behind ops::bf16_matmul::dispatch_gemm_forward / gemm_backward_data / gemm_backward_weight
+ * (src/ignis/ops/bf16_matmul.rs:162-308), which stage transposes on the host instead. */
+T0B_API int32_t t0b_gemm(t0b_ctx* ctx, const t0b_gemm_config* cfg, int32_t trans_a, int32_t trans_b, uint64_t a,
+                         uint64_t b, uint64_t c, uint32_t m, uint32_t n, uint32_t k, uint64_t lda, uint64_t ldb,
+                         uint64_t ldc, int32_t out_dtype, int32_t epilogue, uint64_t bias, float alpha,
+                         uint64_t workspace, size_t workspace_bytes, int32_t async);
+T0B_API size_t t0b_gemm_workspace_bytes(const t0b_gemm_config* cfg, uint32_t m, uint32_t n, uint32_t k);
+
+/* Column-sharded GEMM with the all-gather folded into the epilogue: this rank computes C[:, col0 : col0+n_local]
+ * and stores every finished tile into each of the n_dst row-major [M, ldc] destinations (its own and its
+ * peers', as peer-mapped device pointers).  No counterpart in the reference (single GPU). */
+T0B_API int32_t t0b_gemm_multi_dst(t0b_ctx* ctx, const t0b_gemm_config* cfg, int32_t trans_a, int32_t trans_b,
+                                   uint64_t a, uint64_t b, const uint64_t* c_dsts, int32_t n_dst, uint32_t m,
+                                   uint32_t n_local, uint32_t k, uint64_t lda, uint64_t ldb, uint64_t ldc,
+                                   uint64_t col0, int32_t out_dtype, int32_t async);
+
+/* The reference's split-K contract, unreduced: slab s (f32 [M,N], at y + s*M*N*4) receives the partial sum
+ * of K chunk s; the caller reduces (src/t0/gemm_gen.rs:746-752; examples/test_gemm_correctness.rs:165-207).
+ * NT layout, lda = ldb = k, as the 40-byte kernarg implies. */
+T0B_API int32_t t0b_gemm_slabs(t0b_ctx* ctx, const t0b_gemm_config* cfg, uint64_t x, uint64_t wt, uint64_t y,
+                               uint32_t m, uint32_t n, uint32_t k, uint32_t split_k, int32_t async);
+/* Deterministic slab sum, s = 0..split_k-1 in order, starting from +0.0 (the order of
+ * examples/test_gemm_correctness.rs:203-207), with optional fused epilogue / bf16 output. */
+T0B_API int32_t t0b_splitk_reduce(t0b_ctx* ctx, uint64_t partial, uint32_t split_k, uint32_t m, uint32_t n,
+                                  uint64_t slab_stride_elems, uint64_t ld_partial, uint64_t c, uint64_t ldc,
+                                  int32_t out_dtype, int32_t epilogue, uint64_t bias, float alpha, int32_t async);
+
+/* Drop-in for `queue.submit(&kernel, [gx, gy, 1], kernargs)` + optional wait (src/kfd/mod.rs:1290, 1571;
+ * GpuRuntime::dispatch, gpu_context.rs:264-288): takes the reference's kernarg blob (40, 44 or 48 bytes) and
+ * the thread grid compute_grid* returned.  The 40/48-byte blobs do not carry M: it is recovered from the
+ * grid, M = tiles_m * tile_m, exact because that path requires tile-aligned shapes. Split-K blobs
+ * (y_split_stride != 0) leave unreduced slabs in Y. */
+T0B_API int32_t t0b_dispatch_kernargs(t0b_ctx* ctx, const t0b_gemm_config* cfg, uint32_t grid_x, uint32_t grid_y,
+                                      const uint8_t* kernargs, size_t kernargs_len, int32_t async);
+
+/* Measure the candidate configs for (M, N, K) on the device and return the fastest
+ * (GemmTuner::tune(rt, m, n, k), src/t0/auto_gemm.rs:82-162 -- argument order (M, N, K)). */
+T0B_API int32_t t0b_tune(t0b_ctx* ctx, uint32_t m, uint32_t n, uint32_t k, int32_t trans_a, int32_t trans_b,
+                         int32_t out_dtype, t0b_gemm_config* best, float* best_tflops);
+
+/* ------------------------------------------------------------------------------------------------
+ * Element-wise and row kernels around the GEMMs (f32 activations)
+ * ---------------------------------------------------------------------------------------------- */
+
+/* f32 -> bf16, round to nearest even (src/ignis/ops/bf16_matmul.rs:357-384, done on the host there). */
+T0B_API int32_t t0b_cast_f32_to_bf16(t0b_ctx* ctx, uint64_t src, uint64_t dst, size_t n, int32_t async);
+/* f32 [rows, cols] -> bf16 [cols, rows] (f32_to_bf16_transpose_gpu_padded, bf16_matmul.rs:390-424). */
+T0B_API int32_t t0b_cast_f32_to_bf16_transpose(t0b_ctx* ctx, uint64_t src, uint64_t dst, uint32_t rows,
+                                               uint32_t cols, int32_t async);
+/* RMSNorm forward: y = x * rsqrt(mean(x^2) + eps) * weight; optionally saves inv_rms[row]
+ * (src/t0/rmsnorm_kernels.rs:37-88, 140-153; src/ignis/ops/rmsnorm.rs:40-124). */
+T0B_API int32_t t0b_rmsnorm_fwd(t0b_ctx* ctx, uint64_t x, uint64_t weight, uint64_t y, uint64_t inv_rms,
+                                uint32_t rows, uint32_t cols, float eps, int32_t async);
+/* RMSNorm backward: dx (rmsnorm_kernels.rs:90-137, 155-174) and, when dgamma != 0, dgamma[c] = sum_r dy*x*inv_rms
+ * reduced in a fixed order (the reference uses unordered atomics, src/ignis/ops/rmsnorm.rs:239-293).
+ * dgamma needs a scratch of t0b_rmsnorm_bwd_scratch_bytes(rows, cols). */
+T0B_API int32_t t0b_rmsnorm_bwd(t0b_ctx* ctx, uint64_t dy, uint64_t x, uint64_t weight, uint64_t dx, uint64_t dgamma,
+                                uint64_t scratch, size_t scratch_bytes, uint32_t rows, uint32_t cols, float eps,
+                                int32_t async);
+T0B_API size_t t0b_rmsnorm_bwd_scratch_bytes(uint32_t rows, uint32_t cols);
+/* Row softmax forward / backward, any column count (src/t0/softmax_kernels.rs:38-146; cols <= 256 there). */
+T0B_API int32_t t0b_softmax_fwd(t0b_ctx* ctx, uint64_t x, uint64_t y, uint32_t rows, uint32_t cols, int32_t async);
+T0B_API int32_t t0b_softmax_bwd(t0b_ctx* ctx, uint64_t dy, uint64_t y, uint64_t dx, uint32_t rows, uint32_t cols,
+                                int32_t async);
+/* Fused softmax cross-entropy: losses[r] = logsumexp(x_r) - x_r[target_r] and
+ * dlogits = (softmax - onehot) * scale in one pass pair over the logits
+ * (src/t0/ce_loss_kernels.rs:26-192; examples/kernels/softmax_ce_loss.rs:58-308). Either output may be 0. */
+T0B_API int32_t t0b_softmax_ce(t0b_ctx* ctx, uint64_t logits, uint64_t targets_u32, uint64_t losses,
+                               uint64_t dlogits, uint32_t rows, uint32_t cols, uint64_t ld, float scale,
+                               int32_t async);
+/* SiLU gate forward / backward (src/ignis/ops/silu.rs:32-152). up == 0 means plain SiLU (up = 1). */
+T0B_API int32_t t0b_silu_gate_fwd(t0b_ctx* ctx, uint64_t gate, uint64_t up, uint64_t out, size_t n, int32_t async);
+T0B_API int32_t t0b_silu_gate_bwd(t0b_ctx* ctx, uint64_t grad, uint64_t gate, uint64_t up, uint64_t dgate,
+                                  uint64_t dup, size_t n, int32_t async);
+/* y += x (grad accumulate; src/ignis/tape.rs:343-367, src/t0/elementwise_kernels.rs:41-61). */
+T0B_API int32_t t0b_residual_add(t0b_ctx* ctx, uint64_t y, uint64_t x, size_t n, int32_t async);
+/* Fused AdamW step (src/t0/adamw_kernels.rs:35-119); optionally refreshes a bf16 copy of the parameters. */
+T0B_API int32_t t0b_adamw_step(t0b_ctx* ctx, uint64_t params, uint64_t grads, uint64_t m, uint64_t v,
+                               uint64_t params_bf16, size_t n, float lr, float beta1, float beta2, float eps,
+                               float weight_decay, uint32_t t, float grad_scale, int32_t async);
+
+/* ------------------------------------------------------------------------------------------------
+ * CUDA-graph capture for launch-bound shapes (takes the place of the AQL batch submit,
+ * GpuRuntime::dispatch_async + wait_idle, gpu_context.rs:332, 297).
+ * ---------------------------------------------------------------------------------------------- */
+T0B_API int32_t t0b_graph_begin(t0b_ctx* ctx);
+T0B_API int32_t t0b_graph_end(t0b_ctx* ctx, uint64_t* graph_handle);
+T0B_API int32_t t0b_graph_launch(t0b_ctx* ctx, uint64_t graph_handle, int32_t async);
+T0B_API int32_t t0b_graph_destroy(t0b_ctx* ctx, uint64_t graph_handle);
+
+/* ------------------------------------------------------------------------------------------------
+ * Diagnostics
+ * ---------------------------------------------------------------------------------------------- */
+/* Runs a one-thread kernel that waits on a barrier nobody signals; the wait runs out after limit_ns, the
+ * kernel records its status code and returns.  Returns T0B_ERR_DEVICE and leaves the context usable. */
+T0B_API int32_t t0b_selftest_bounded_wait(t0b_ctx* ctx, uint64_t limit_ns);
+/* Time `iters` back-to-back launches of one GEMM with CUDA events on the context's stream; ms per launch. */
+T0B_API int32_t t0b_gemm_time(t0b_ctx* ctx, const t0b_gemm_config* cfg, int32_t trans_a, int32_t trans_b, uint64_t a,
+                              uint64_t b, uint64_t c, uint32_t m, uint32_t n, uint32_t k, uint64_t lda, uint64_t ldb,
+                              uint64_t ldc, int32_t out_dtype, int32_t warmup, int32_t iters, float* ms_per_launch);
+/* Number of kernels this context has launched so far. */
+T0B_API uint64_t t0b_launch_count(t0b_ctx* ctx);
+T0B_API const char* t0b_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* T0B200_H */

@@ -1,0 +1,58 @@
+"""Build libt0b200.so (the C-ABI CUDA library) in-tree for sm_100a with nvcc.
+
+    python -m t0_gpu_b200.build [--force] [--verbose]
+
+The library is cross-compiled (no GPU needed) and lands in t0_gpu_b200/lib/libt0b200.so.
+"""
+from __future__ import annotations
+
+import os
+import subprocess
+import sys
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+CSRC = os.path.join(HERE, "csrc")
+OUT_DIR = os.path.join(HERE, "lib")
+OUT = os.path.join(OUT_DIR, "libt0b200.so")
+OBJ_DIR = os.path.join(OUT_DIR, "obj")
+
+SOURCES = ["t0b_runtime.cu", "t0b_gemm.cu", "t0b_rowops.cu", "t0b_gemm_gen.cpp"]
+HEADERS = ["gemm_sm100.cuh", "ptx_sm100.cuh", "t0b_internal.hpp", os.path.join("..", "..", "include", "t0b200.h")]
+
+NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
+ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
+CFLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC,-fvisibility=hidden", "--expt-relaxed-constexpr"]
+
+
+def _newest(paths) -> float:
+    return max(os.path.getmtime(p) for p in paths)
+
+
+def build(force: bool = False, verbose: bool = False) -> str:
+    os.makedirs(OBJ_DIR, exist_ok=True)
+    hdr_time = _newest([os.path.join(CSRC, h) for h in HEADERS])
+    objs = []
+    for src in SOURCES:
+        sp = os.path.join(CSRC, src)
+        obj = os.path.join(OBJ_DIR, os.path.splitext(src)[0] + ".o")
+        objs.append(obj)
+        stale = force or not os.path.exists(obj) or os.path.getmtime(obj) < max(os.path.getmtime(sp), hdr_time)
+        if stale:
+            cmd = [NVCC, *ARCH, *CFLAGS, "-c", sp, "-o", obj]
+            if src.endswith(".cpp"):
+                cmd.insert(1, "-x")
+                cmd.insert(2, "cu")
+            if verbose:
+                cmd += ["-Xptxas", "-v"]
+                print(" ".join(cmd), flush=True)
+            subprocess.run(cmd, check=True)
+    if force or not os.path.exists(OUT) or os.path.getmtime(OUT) < _newest(objs):
+        cmd = [NVCC, *ARCH, "-shared", "-o", OUT, *objs, "-cudart", "static"]
+        if verbose:
+            print(" ".join(cmd), flush=True)
+        subprocess.run(cmd, check=True)
+    return OUT
+
+
+if __name__ == "__main__":
+    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))

@@ -1,0 +1,582 @@
+// bf16 x bf16 -> f32-accumulate GEMM for sm_100a: persistent, warp-specialised, TMA-fed shared-memory
+// ring, tcgen05.mma with double-buffered TMEM accumulators, optional CTA pairs (cta_group::2).
+//
+// Replaces the reference's generated RDNA3 WMMA kernels (src/t0/gemm_gen.rs:637-1348 `generate_lds_db`,
+// src/t0/tile_ir.rs:585 `lower_gemm`): same math (Y = op(A) * op(B), bf16 in, f32 accumulate), same
+// split-K contract (slab s holds the partial sum of K-chunk s, src/t0/gemm_gen.rs:746-752), same edge
+// behaviour as the tile_ir path (rows/cols beyond M/N are never stored, src/t0/tile_ir.rs:2462-2472;
+// the K tail contributes zeros, :768-787) -- here the zero fill is TMA's out-of-bounds fill, so callers
+// do not have to pad.
+//
+// Roles per CTA (192 threads): warp 0 = TMA producer, warp 1 = TMEM owner + MMA issuer,
+// warps 2..5 = epilogue (TMEM -> registers -> global).  Every wait is bounded: when a wait runs out the
+// CTA records a status code, raises its abort flag, drains, frees its TMEM and returns.
+#pragma once
+#include <cuda_bf16.h>
+#include <cstdint>
+
+#include "ptx_sm100.cuh"
+
+namespace t0b {
+
+// Fused store-phase operations.  0..2 are the generator's EpilogueOp (src/t0/gemm_gen.rs:40-49); the rest
+// are the tile_ir chain's single-op members (src/t0/tile_ir.rs:41-62).
+enum EpilogueKind : int {
+    EPI_STORE = 0,
+    EPI_BIAS = 1,
+    EPI_BIAS_RELU = 2,
+    EPI_RELU = 3,
+    EPI_SILU = 4,
+    EPI_GELU_SIGMOID = 5,  // x * sigmoid(1.702 x)
+    EPI_SCALE = 6,
+    EPI_ABS = 7,
+    EPI_NEG = 8,
+};
+
+// Device status codes written to the context's status word.
+enum DeviceStatus : int {
+    DEV_OK = 0,
+    DEV_TIMEOUT_EMPTY = 101,      // producer waited for a free ring slot
+    DEV_TIMEOUT_FULL = 102,       // MMA issuer waited for TMA data
+    DEV_TIMEOUT_TMEM_EMPTY = 103, // MMA issuer waited for the epilogue to drain an accumulator
+    DEV_TIMEOUT_TMEM_FULL = 104,  // epilogue waited for an accumulator
+    DEV_TIMEOUT_SELFTEST = 105,   // the bounded-wait self test (a barrier nobody arrives on)
+};
+
+constexpr int kMaxDst = 8;
+
+struct GemmParams {
+    void* c_dst[kMaxDst];   // destinations of the epilogue store: [0] local, [1..] peers of a column-sharded GEMM
+    int n_dst;
+    long long ldc;          // row pitch of C in elements
+    const float* bias;      // f32[N] or null
+    float alpha;            // EPI_SCALE factor
+    float* partial;         // split-K slabs (f32, slab s at partial + s * slab_stride); null when split_k == 1
+    long long slab_stride;  // elements
+    long long ld_partial;   // row pitch of a slab in elements
+    int M, N, K;
+    int tiles_m, tiles_n;   // in units of the cluster tile (128*CG x BN)
+    int split_k;
+    int kb_total, kb_per_split;  // K blocks of 64
+    int a_mn_major, b_mn_major;  // 0: operand stored K-contiguous; 1: stored M/N-contiguous
+    int out_bf16;
+    int epilogue;
+    int raster_along_n;     // 0: group tile rows (walk N inside a group of M tiles); 1: the transpose
+    int group;              // rasterisation group width in tiles
+    unsigned mn_lbo, mn_sbo, mn_kstep;  // descriptor byte offsets for M/N-contiguous operands
+    int* status;
+    unsigned long long wait_limit_ns;
+};
+
+constexpr int kBmCta = 128;   // accumulator rows per CTA (TMEM lanes)
+constexpr int kBk = 64;       // K block: 64 bf16 = one 128-byte swizzle row
+constexpr int kUmmaK = 16;
+constexpr int kATileBytes = kBmCta * kBk * 2;
+constexpr int kGemmThreads = 192;
+
+template <int BN, int CG>
+struct GemmTraits {
+    static_assert(BN == 64 || BN == 128 || BN == 256, "BN");
+    static_assert(CG == 1 || CG == 2, "CG");
+    static constexpr int kBnCta = BN / CG;               // B rows this CTA loads
+    static_assert(kBnCta % 64 == 0, "each CTA's B slice must be whole 64-column swizzle blocks");
+    static constexpr int kBTileBytes = kBnCta * kBk * 2;
+    static constexpr int kStageBytes = kATileBytes + kBTileBytes;
+    static constexpr int kCtrlBytes = 512;
+    static constexpr int kBudget = 227 * 1024 - 1024 - kCtrlBytes;
+    static constexpr int kStagesRaw = kBudget / kStageBytes;
+    static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
+    static constexpr int kTmemCols = 2 * BN;             // two accumulator buffers
+    static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + kCtrlBytes;
+};
+
+struct WorkItem {
+    int m0, n0, split, kb_begin, kb_end;
+};
+
+__device__ __forceinline__ WorkItem decode_work(const GemmParams& p, int w, int bm, int bn) {
+    const int num_tiles = p.tiles_m * p.tiles_n;
+    const int split = w / num_tiles;
+    const int tile = w - split * num_tiles;
+    int major_cnt = p.raster_along_n ? p.tiles_n : p.tiles_m;   // dimension that is grouped
+    int minor_cnt = p.raster_along_n ? p.tiles_m : p.tiles_n;
+    const int per_group = p.group * minor_cnt;
+    const int g = tile / per_group;
+    const int first = g * p.group;
+    const int gsz = min(major_cnt - first, p.group);
+    const int in_group = tile - g * per_group;
+    const int major = first + in_group % gsz;
+    const int minor = in_group / gsz;
+    WorkItem wi;
+    wi.m0 = (p.raster_along_n ? minor : major) * bm;
+    wi.n0 = (p.raster_along_n ? major : minor) * bn;
+    wi.split = split;
+    wi.kb_begin = split * p.kb_per_split;
+    wi.kb_end = min(p.kb_total, wi.kb_begin + p.kb_per_split);
+    return wi;
+}
+
+// Shared-memory matrix descriptor for tcgen05.mma, 128-byte swizzle.
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    uint64_t d = 0;
+    d |= static_cast<uint64_t>((saddr & 0x3FFFFu) >> 4);
+    d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFFu) << 16;
+    d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3FFFu) << 32;
+    d |= 1ull << 46;   // descriptor version for sm_100
+    d |= 2ull << 61;   // SWIZZLE_128B
+    return d;
+}
+
+struct WaitCtl {
+    volatile int* abort;
+    int* status;
+    unsigned long long limit_ns;
+};
+
+// Bounded mbarrier wait.  Returns false when the limit ran out or another thread of the CTA aborted.
+__device__ __forceinline__ bool bounded_wait(uint32_t bar, uint32_t parity, const WaitCtl& ctl, int code) {
+    if (ptx::mbar_try_wait(bar, parity)) return true;
+    const uint64_t t0 = ptx::globaltimer_ns();
+    uint32_t spins = 0;
+    while (true) {
+        if (ptx::mbar_try_wait(bar, parity)) return true;
+        if ((++spins & 31u) == 0) {
+            if (*ctl.abort) return false;
+            if (ptx::globaltimer_ns() - t0 > ctl.limit_ns) {
+                *ctl.abort = 1;
+                *reinterpret_cast<volatile int*>(ctl.status) = code;
+                return false;
+            }
+        }
+    }
+}
+
+__device__ __forceinline__ float apply_epilogue(float v, int kind, float bias, float alpha) {
+    switch (kind) {
+        case EPI_BIAS: return v + bias;
+        case EPI_BIAS_RELU: return fmaxf(v + bias, 0.0f);
+        case EPI_RELU: return fmaxf(v, 0.0f);
+        case EPI_SILU: return v / (1.0f + __expf(-v));
+        case EPI_GELU_SIGMOID: return v / (1.0f + __expf(-1.702f * v));
+        case EPI_SCALE: return v * alpha;
+        case EPI_ABS: return fabsf(v);
+        case EPI_NEG: return -v;
+        default: return v;
+    }
+}
+
+// Store one thread's 32 consecutive output columns of one row.
+__device__ __forceinline__ void store_chunk_f32(float* base, long long ld, int row, int col0, int ncols_valid,
+                                                const float (&v)[32], bool vec_ok) {
+    float* dst = base + static_cast<long long>(row) * ld + col0;
+    if (vec_ok && ncols_valid >= 32) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+            reinterpret_cast<float4*>(dst)[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+    } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+            if (j < ncols_valid) dst[j] = v[j];
+    }
+}
+
+__device__ __forceinline__ void store_chunk_bf16(__nv_bfloat16* base, long long ld, int row, int col0, int ncols_valid,
+                                                 const float (&v)[32], bool vec_ok) {
+    __nv_bfloat16* dst = base + static_cast<long long>(row) * ld + col0;
+    if (vec_ok && ncols_valid >= 32) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            uint4 q;
+            __nv_bfloat162 h0 = __floats2bfloat162_rn(v[8 * j + 0], v[8 * j + 1]);
+            __nv_bfloat162 h1 = __floats2bfloat162_rn(v[8 * j + 2], v[8 * j + 3]);
+            __nv_bfloat162 h2 = __floats2bfloat162_rn(v[8 * j + 4], v[8 * j + 5]);
+            __nv_bfloat162 h3 = __floats2bfloat162_rn(v[8 * j + 6], v[8 * j + 7]);
+            q.x = *reinterpret_cast<uint32_t*>(&h0);
+            q.y = *reinterpret_cast<uint32_t*>(&h1);
+            q.z = *reinterpret_cast<uint32_t*>(&h2);
+            q.w = *reinterpret_cast<uint32_t*>(&h3);
+            reinterpret_cast<uint4*>(dst)[j] = q;
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+            if (j < ncols_valid) dst[j] = __float2bfloat16_rn(v[j]);
+    }
+}
+
+template <int BN, int CG>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                         const GemmParams p) {
+    using T = GemmTraits<BN, CG>;
+    constexpr int S = T::kStages;
+    constexpr int BM = kBmCta * CG;
+
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw_addr = ptx::smem_u32(smem_raw);
+    const uint32_t smem_base = (raw_addr + 1023u) & ~1023u;   // swizzle atoms need 1024-byte alignment
+    uint8_t* smem_gen = smem_raw + (smem_base - raw_addr);
+
+    const uint32_t ctrl = smem_base + S * T::kStageBytes;
+    auto full_bar = [&](int s) { return ctrl + 8u * s; };
+    auto empty_bar = [&](int s) { return ctrl + 8u * (S + s); };
+    auto tfull_bar = [&](int a) { return ctrl + 8u * (2 * S + a); };
+    auto tempty_bar = [&](int a) { return ctrl + 8u * (2 * S + 2 + a); };
+    const uint32_t slot_off = 8u * (2 * S + 4);
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + S * T::kStageBytes + slot_off);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + S * T::kStageBytes + slot_off + 4);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const uint32_t cta_rank = (CG == 2) ? ptx::cluster_ctarank() : 0u;
+    const bool is_leader = cta_rank == 0;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < S; ++s) {
+            ptx::mbar_init(full_bar(s), 1);
+            ptx::mbar_init(empty_bar(s), 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            ptx::mbar_init(tfull_bar(a), 1);
+            ptx::mbar_init(tempty_bar(a), 4 * CG);   // one arrival per epilogue warp of every CTA of the group
+        }
+        *abort_flag = 0;
+        ptx::fence_mbar_init();
+    }
+    if (warp == 0 && lane == 0) {
+        ptx::prefetch_tmap(&tmap_a);
+        ptx::prefetch_tmap(&tmap_b);
+    }
+    if (warp == 1) {
+        ptx::tmem_alloc<CG>(ctrl + slot_off, T::kTmemCols);
+        ptx::tmem_relinquish<CG>();
+    }
+    ptx::tc_fence_before();
+    __syncthreads();
+    if constexpr (CG == 2) {
+        ptx::cluster_arrive();
+        ptx::cluster_wait();
+    }
+    ptx::tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const WaitCtl ctl{abort_flag, p.status, p.wait_limit_ns};
+    const int num_work = p.tiles_m * p.tiles_n * p.split_k;
+    const int cluster_id = blockIdx.x / CG;
+    const int num_clusters = gridDim.x / CG;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            int s = 0;
+            uint32_t ph = 0;
+            bool ok = true;
+            for (int w = cluster_id; w < num_work && ok; w += num_clusters) {
+                const WorkItem wi = decode_work(p, w, BM, BN);
+                const int m0_cta = wi.m0 + static_cast<int>(cta_rank) * kBmCta;
+                const int n0_cta = wi.n0 + static_cast<int>(cta_rank) * T::kBnCta;
+                for (int kb = wi.kb_begin; kb < wi.kb_end; ++kb) {
+                    if (!bounded_wait(empty_bar(s), ph ^ 1u, ctl, DEV_TIMEOUT_EMPTY)) { ok = false; break; }
+                    if (is_leader) ptx::mbar_arrive_expect_tx(full_bar(s), CG * T::kStageBytes);
+                    const uint32_t a_dst = smem_base + s * T::kStageBytes;
+                    const uint32_t b_dst = a_dst + kATileBytes;
+                    const int k0 = kb * kBk;
+                    if constexpr (CG == 1) {
+                        const uint32_t bar = full_bar(s);
+                        if (!p.a_mn_major) {
+                            ptx::tma_load_2d(a_dst, &tmap_a, bar, k0, m0_cta);
+                        } else {
+                            ptx::tma_load_2d(a_dst, &tmap_a, bar, m0_cta, k0);
+                            ptx::tma_load_2d(a_dst + 8192, &tmap_a, bar, m0_cta + 64, k0);
+                        }
+                        if (!p.b_mn_major) {
+                            ptx::tma_load_2d(b_dst, &tmap_b, bar, k0, n0_cta);
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < T::kBnCta / 64; ++j)
+                                ptx::tma_load_2d(b_dst + j * 8192, &tmap_b, bar, n0_cta + j * 64, k0);
+                        }
+                    } else {
+                        const uint32_t bar = ptx::mapa(full_bar(s), 0);   // the pair's barrier lives in CTA 0
+                        if (!p.a_mn_major) {
+                            ptx::tma_load_2d_pair(a_dst, &tmap_a, bar, k0, m0_cta);
+                        } else {
+                            ptx::tma_load_2d_pair(a_dst, &tmap_a, bar, m0_cta, k0);
+                            ptx::tma_load_2d_pair(a_dst + 8192, &tmap_a, bar, m0_cta + 64, k0);
+                        }
+                        if (!p.b_mn_major) {
+                            ptx::tma_load_2d_pair(b_dst, &tmap_b, bar, k0, n0_cta);
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < T::kBnCta / 64; ++j)
+                                ptx::tma_load_2d_pair(b_dst + j * 8192, &tmap_b, bar, n0_cta + j * 64, k0);
+                        }
+                    }
+                    if (++s == S) { s = 0; ph ^= 1u; }
+                }
+            }
+            // Tail: every slot must have been released, so no MMA-completion arrival can target this
+            // CTA's shared memory after it exits.
+            for (int i = 0; i < S && ok; ++i) {
+                if (!bounded_wait(empty_bar(s), ph ^ 1u, ctl, DEV_TIMEOUT_EMPTY)) ok = false;
+                if (++s == S) { s = 0; ph ^= 1u; }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (lane == 0 && is_leader) {
+            const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(p.a_mn_major) << 15) |
+                                   (static_cast<uint32_t>(p.b_mn_major) << 16) | (static_cast<uint32_t>(BN >> 3) << 17) |
+                                   (static_cast<uint32_t>(BM >> 4) << 24);
+            const uint32_t a_lbo = p.a_mn_major ? p.mn_lbo : 16u, a_sbo = p.a_mn_major ? p.mn_sbo : 1024u;
+            const uint32_t b_lbo = p.b_mn_major ? p.mn_lbo : 16u, b_sbo = p.b_mn_major ? p.mn_sbo : 1024u;
+            const uint32_t a_kstep = p.a_mn_major ? p.mn_kstep : 32u;
+            const uint32_t b_kstep = p.b_mn_major ? p.mn_kstep : 32u;
+            int s = 0;
+            uint32_t ph = 0;
+            int acc = 0;
+            uint32_t acc_ph = 0;
+            bool ok = true;
+            for (int w = cluster_id; w < num_work && ok; w += num_clusters) {
+                const WorkItem wi = decode_work(p, w, BM, BN);
+                if (!bounded_wait(tempty_bar(acc), acc_ph ^ 1u, ctl, DEV_TIMEOUT_TMEM_EMPTY)) { ok = false; break; }
+                ptx::tc_fence_after();
+                const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
+                for (int kb = wi.kb_begin; kb < wi.kb_end; ++kb) {
+                    if (!bounded_wait(full_bar(s), ph, ctl, DEV_TIMEOUT_FULL)) { ok = false; break; }
+                    ptx::tc_fence_after();
+                    const uint32_t a_addr = smem_base + s * T::kStageBytes;
+                    const uint32_t b_addr = a_addr + kATileBytes;
+#pragma unroll
+                    for (int k = 0; k < kBk / kUmmaK; ++k) {
+                        const uint64_t adesc = make_smem_desc(a_addr + k * a_kstep, a_lbo, a_sbo);
+                        const uint64_t bdesc = make_smem_desc(b_addr + k * b_kstep, b_lbo, b_sbo);
+                        ptx::mma_f16<CG>(d_tmem, adesc, bdesc, idesc, (kb > wi.kb_begin || k > 0) ? 1u : 0u);
+                    }
+                    if constexpr (CG == 1) ptx::mma_commit(empty_bar(s));
+                    else ptx::mma_commit_pair(empty_bar(s), 0x3);
+                    if (++s == S) { s = 0; ph ^= 1u; }
+                }
+                if (!ok) break;
+                if constexpr (CG == 1) ptx::mma_commit(tfull_bar(acc));
+                else ptx::mma_commit_pair(tfull_bar(acc), 0x3);
+                acc ^= 1;
+                if (acc == 0) acc_ph ^= 1u;
+            }
+        }
+        __syncwarp();
+    } else {
+        // ------------------------------------------------------------------ epilogue (4 warps, 32 TMEM lanes each)
+        const int q = warp & 3;   // TMEM lane quarter this warp may read
+        int acc = 0;
+        uint32_t acc_ph = 0;
+        const bool to_slab = p.split_k > 1;
+        const long long ld_out = to_slab ? p.ld_partial : p.ldc;
+        bool vec_ok;
+        if (to_slab || !p.out_bf16) {
+            vec_ok = (ld_out % 4 == 0);
+            if (to_slab) vec_ok = vec_ok && ((reinterpret_cast<uintptr_t>(p.partial) & 15) == 0) && (p.slab_stride % 4 == 0);
+            else for (int d = 0; d < p.n_dst; ++d) vec_ok = vec_ok && ((reinterpret_cast<uintptr_t>(p.c_dst[d]) & 15) == 0);
+        } else {
+            vec_ok = (ld_out % 8 == 0);
+            for (int d = 0; d < p.n_dst; ++d) vec_ok = vec_ok && ((reinterpret_cast<uintptr_t>(p.c_dst[d]) & 15) == 0);
+        }
+        const int epi = to_slab ? EPI_STORE : p.epilogue;
+        const bool need_bias = (epi == EPI_BIAS || epi == EPI_BIAS_RELU) && p.bias != nullptr;
+        for (int w = cluster_id; w < num_work; w += num_clusters) {
+            const WorkItem wi = decode_work(p, w, BM, BN);
+            if (!bounded_wait(tfull_bar(acc), acc_ph, ctl, DEV_TIMEOUT_TMEM_FULL)) break;
+            ptx::tc_fence_after();
+            const int row = wi.m0 + static_cast<int>(cta_rank) * kBmCta + q * 32 + lane;
+            const uint32_t t_row = tmem_base + static_cast<uint32_t>(acc * BN) + (static_cast<uint32_t>(q * 32) << 16);
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; ++c) {
+                uint32_t raw[32];
+                ptx::tmem_ld_32x32(t_row + c * 32, raw);
+                ptx::tmem_ld_wait();
+                if (c == BN / 32 - 1) {
+                    // All of this warp's reads of the accumulator are done: hand it back to the MMA issuer.
+                    ptx::tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) {
+                        if constexpr (CG == 1) ptx::mbar_arrive(tempty_bar(acc));
+                        else ptx::mbar_arrive_cluster(ptx::mapa(tempty_bar(acc), 0));
+                    }
+                }
+                const int col0 = wi.n0 + c * 32;
+                const int ncols = p.N - col0;
+                if (row < p.M && ncols > 0) {
+                    float v[32];
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(raw[j]);
+                    if (epi != EPI_STORE) {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            float b = 0.0f;
+                            if (need_bias && j < ncols) b = __ldg(p.bias + col0 + j);
+                            v[j] = apply_epilogue(v[j], epi, b, p.alpha);
+                        }
+                    }
+                    if (to_slab) {
+                        store_chunk_f32(p.partial + static_cast<long long>(wi.split) * p.slab_stride, ld_out, row, col0,
+                                        ncols, v, vec_ok);
+                    } else if (p.out_bf16) {
+                        for (int d = 0; d < p.n_dst; ++d)
+                            store_chunk_bf16(static_cast<__nv_bfloat16*>(p.c_dst[d]), ld_out, row, col0, ncols, v, vec_ok);
+                    } else {
+                        for (int d = 0; d < p.n_dst; ++d)
+                            store_chunk_f32(static_cast<float*>(p.c_dst[d]), ld_out, row, col0, ncols, v, vec_ok);
+                    }
+                }
+            }
+            acc ^= 1;
+            if (acc == 0) acc_ph ^= 1u;
+        }
+    }
+
+    // ---------------------------------------------------------------------- teardown (normal and abort paths)
+    ptx::tc_fence_before();
+    __syncthreads();
+    if (*abort_flag) {
+        // Give this CTA's own TMA copies in flight time to land before the shared memory is released.
+        const uint64_t t0 = ptx::globaltimer_ns();
+        while (ptx::globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+    }
+    if constexpr (CG == 2) {
+        // The peer may still read this CTA's tiles / signal its barriers until both are done.
+        ptx::cluster_arrive();
+        ptx::cluster_wait();
+    }
+    if (warp == 1) {
+        ptx::tc_fence_after();
+        ptx::tmem_dealloc<CG>(tmem_base, T::kTmemCols);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// Deterministic split-K reduce: out[i] = epilogue(sum over s = 0..sk-1, in that order, of slab_s[i]),
+// starting from +0.0 -- the order of the reference's host-side slab sum
+// (examples/test_gemm_correctness.rs:203-207).  One thread per 4 consecutive columns.
+// ---------------------------------------------------------------------------------------------------------
+struct ReduceParams {
+    const float* partial;
+    long long slab_stride, ld_partial;
+    void* c;
+    long long ldc;
+    const float* bias;
+    float alpha;
+    int M, N, sk, out_bf16, epilogue;
+};
+
+__global__ void __launch_bounds__(256) splitk_reduce_kernel(const ReduceParams p) {
+    const int n4 = (p.N + 3) / 4;
+    const long long total = static_cast<long long>(p.M) * n4;
+    const bool vec_in = (p.ld_partial % 4 == 0) && (p.slab_stride % 4 == 0) &&
+                        ((reinterpret_cast<uintptr_t>(p.partial) & 15) == 0);
+    const bool vec_out = p.out_bf16 ? false
+                                    : ((p.ldc % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.c) & 15) == 0));
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const int row = static_cast<int>(i / n4);
+        const int col = static_cast<int>(i - static_cast<long long>(row) * n4) * 4;
+        const int nv = min(4, p.N - col);
+        float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        const float* src = p.partial + static_cast<long long>(row) * p.ld_partial + col;
+        for (int s = 0; s < p.sk; ++s) {
+            const float* ps = src + static_cast<long long>(s) * p.slab_stride;
+            if (vec_in && nv == 4) {
+                const float4 v = *reinterpret_cast<const float4*>(ps);
+                acc[0] = acc[0] + v.x; acc[1] = acc[1] + v.y; acc[2] = acc[2] + v.z; acc[3] = acc[3] + v.w;
+            } else {
+                for (int j = 0; j < nv; ++j) acc[j] = acc[j] + ps[j];
+            }
+        }
+        const bool need_bias = (p.epilogue == EPI_BIAS || p.epilogue == EPI_BIAS_RELU) && p.bias != nullptr;
+        for (int j = 0; j < nv; ++j)
+            acc[j] = apply_epilogue(acc[j], p.epilogue, need_bias ? p.bias[col + j] : 0.0f, p.alpha);
+        if (p.out_bf16) {
+            __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.c) + static_cast<long long>(row) * p.ldc + col;
+            for (int j = 0; j < nv; ++j) dst[j] = __float2bfloat16_rn(acc[j]);
+        } else {
+            float* dst = static_cast<float*>(p.c) + static_cast<long long>(row) * p.ldc + col;
+            if (vec_out && nv == 4) *reinterpret_cast<float4*>(dst) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+            else for (int j = 0; j < nv; ++j) dst[j] = acc[j];
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// Plain CUDA-core GEMM for operands TMA cannot address (row pitch not a multiple of 16 bytes, or a base
+// pointer that is not 16-byte aligned).  Correctness path only: 64x64 tile, 16x16 threads, 4x4 per thread.
+// ---------------------------------------------------------------------------------------------------------
+struct SimtParams {
+    const __nv_bfloat16 *a, *b;
+    void* c;
+    const float* bias;
+    float alpha;
+    long long lda, ldb, ldc;
+    int M, N, K, trans_a, trans_b, out_bf16, epilogue;
+    int k_begin, k_end;
+};
+
+__global__ void __launch_bounds__(256) gemm_bf16_simt_kernel(const SimtParams p) {
+    __shared__ float As[16][64 + 1];
+    __shared__ float Bs[16][64 + 1];
+    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+    const int m0 = blockIdx.y * 64, n0 = blockIdx.x * 64;
+    float acc[4][4] = {};
+    for (int k0 = p.k_begin; k0 < p.k_end; k0 += 16) {
+        for (int i = threadIdx.x; i < 16 * 64; i += 256) {
+            const int kk = i & 15, mm = i >> 4;
+            const int gk = k0 + kk, gm = m0 + mm, gn = n0 + mm;
+            float av = 0.0f, bv = 0.0f;
+            if (gk < p.k_end && gm < p.M)
+                av = __bfloat162float(p.trans_a ? p.a[static_cast<long long>(gk) * p.lda + gm]
+                                                : p.a[static_cast<long long>(gm) * p.lda + gk]);
+            if (gk < p.k_end && gn < p.N)
+                bv = __bfloat162float(p.trans_b ? p.b[static_cast<long long>(gn) * p.ldb + gk]
+                                                : p.b[static_cast<long long>(gk) * p.ldb + gn]);
+            As[kk][mm] = av;
+            Bs[kk][mm] = bv;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < 16; ++kk) {
+            float a[4], b[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) { a[i] = As[kk][ty * 4 + i]; b[i] = Bs[kk][tx * 4 + i]; }
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+    const bool need_bias = (p.epilogue == EPI_BIAS || p.epilogue == EPI_BIAS_RELU) && p.bias != nullptr;
+    for (int i = 0; i < 4; ++i)
+        for (int j = 0; j < 4; ++j) {
+            const int gm = m0 + ty * 4 + i, gn = n0 + tx * 4 + j;
+            if (gm < p.M && gn < p.N) {
+                const float v = apply_epilogue(acc[i][j], p.epilogue, need_bias ? p.bias[gn] : 0.0f, p.alpha);
+                if (p.out_bf16) static_cast<__nv_bfloat16*>(p.c)[static_cast<long long>(gm) * p.ldc + gn] = __float2bfloat16_rn(v);
+                else static_cast<float*>(p.c)[static_cast<long long>(gm) * p.ldc + gn] = v;
+            }
+        }
+}
+
+// Bounded-wait self test: one thread waits on a barrier nobody arrives on; the wait must run out, record
+// DEV_TIMEOUT_SELFTEST and return, leaving the context usable.
+__global__ void bounded_wait_selftest_kernel(int* status, unsigned long long limit_ns) {
+    __shared__ uint64_t bar;
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        ptx::mbar_init(ptx::smem_u32(&bar), 1);
+        ptx::fence_mbar_init();
+        const WaitCtl ctl{&abort_flag, status, limit_ns};
+        bounded_wait(ptx::smem_u32(&bar), 0, ctl, DEV_TIMEOUT_SELFTEST);
+    }
+}
+
+}  // namespace t0b

@@ -1,0 +1,545 @@
+// GEMM dispatch: tensor maps, kernel-variant selection, launches, split-K reduce, the kernarg-blob drop-in
+// and the on-device tuner.  Replaces the reference's kernel cache + AQL dispatch
+// (GpuRuntime::ensure_kernel_t0 / dispatch, src/ignis/gpu_context.rs:171-288) and the Ignis GEMM entry
+// points (src/ignis/ops/bf16_matmul.rs:162-308).
+#include <algorithm>
+#include <cstring>
+
+#include "gemm_sm100.cuh"
+#include "t0b_internal.hpp"
+
+using namespace t0b;
+
+namespace {
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// The driver entry point is looked up at run time so the library links against the CUDA runtime only and
+// can be loaded (for symbol checks) on a machine without a GPU driver.
+EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess)
+            p = nullptr;
+        return reinterpret_cast<EncodeTiledFn>(p);
+    }();
+    return fn;
+}
+
+// 2-D bf16 tensor map: inner (contiguous) extent d0, outer extent d1, outer pitch ld elements, box b0 x b1,
+// 128-byte swizzle, out-of-bounds elements read as zero.
+int32_t get_tmap(t0b_ctx* ctx, uint64_t ptr, uint64_t d0, uint64_t d1, uint64_t ld, uint32_t b0, uint32_t b1,
+                 CUtensorMap* out) {
+    t0b_ctx::TmapKey key{ptr, d0, d1, ld, b0, b1};
+    auto it = ctx->tmaps.find(key);
+    if (it != ctx->tmaps.end()) {
+        *out = it->second;
+        return T0B_OK;
+    }
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn) return set_error(ctx, T0B_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+    cuuint64_t dims[2] = {d0, d1};
+    cuuint64_t strides[1] = {ld * 2};
+    cuuint32_t box[2] = {b0, b1};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, reinterpret_cast<void*>(ptr), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+        return set_error(ctx, T0B_ERR_INVALID,
+                         "cuTensorMapEncodeTiled failed (%d) for ptr=%llx dims=(%llu,%llu) ld=%llu box=(%u,%u)",
+                         static_cast<int>(r), static_cast<unsigned long long>(ptr), static_cast<unsigned long long>(d0),
+                         static_cast<unsigned long long>(d1), static_cast<unsigned long long>(ld), b0, b1);
+    if (ctx->tmaps.size() > 8192) ctx->tmaps.clear();
+    ctx->tmaps.emplace(key, *out);
+    return T0B_OK;
+}
+
+template <int BN, int CG>
+int32_t launch_variant(t0b_ctx* ctx, const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int num_work) {
+    using T = GemmTraits<BN, CG>;
+    auto kfn = gemm_bf16_tcgen05_kernel<BN, CG>;
+    static bool configured[64] = {};
+    static int max_clusters[64] = {};
+    const int dev = ctx->device & 63;
+    if (!configured[dev]) {
+        int32_t rc = check_cuda(ctx, cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, T::kSmemBytes),
+                                "cudaFuncSetAttribute(smem)");
+        if (rc != T0B_OK) return rc;
+        if (CG == 2) {
+            rc = check_cuda(ctx, cudaFuncSetAttribute(kfn, cudaFuncAttributeNonPortableClusterSizeAllowed, 0),
+                            "cudaFuncSetAttribute(cluster)");
+            if (rc != T0B_OK) return rc;
+            cudaLaunchConfig_t qc{};
+            qc.gridDim = dim3(ctx->num_sms - (ctx->num_sms % 2), 1, 1);
+            qc.blockDim = dim3(kGemmThreads, 1, 1);
+            qc.dynamicSmemBytes = T::kSmemBytes;
+            cudaLaunchAttribute qa[1];
+            qa[0].id = cudaLaunchAttributeClusterDimension;
+            qa[0].val.clusterDim.x = 2;
+            qa[0].val.clusterDim.y = 1;
+            qa[0].val.clusterDim.z = 1;
+            qc.attrs = qa;
+            qc.numAttrs = 1;
+            int nc = 0;
+            cudaError_t e = cudaOccupancyMaxActiveClusters(&nc, kfn, &qc);
+            if (e != cudaSuccess || nc <= 0) {
+                cudaGetLastError();
+                nc = ctx->num_sms / 2;
+            }
+            max_clusters[dev] = nc;
+        } else {
+            max_clusters[dev] = ctx->num_sms;
+        }
+        configured[dev] = true;
+    }
+    const int clusters = std::max(1, std::min(num_work, max_clusters[dev]));
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(clusters * CG, 1, 1);
+    cfg.blockDim = dim3(kGemmThreads, 1, 1);
+    cfg.dynamicSmemBytes = T::kSmemBytes;
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute attrs[1];
+    attrs[0].id = cudaLaunchAttributeClusterDimension;
+    attrs[0].val.clusterDim.x = CG;
+    attrs[0].val.clusterDim.y = 1;
+    attrs[0].val.clusterDim.z = 1;
+    cfg.attrs = attrs;
+    cfg.numAttrs = 1;
+    return check_cuda(ctx, cudaLaunchKernelEx(&cfg, kfn, ta, tb, p), "cudaLaunchKernelEx(gemm)");
+}
+
+struct GemmCall {
+    const t0b_gemm_config* cfg;
+    int trans_a, trans_b;
+    uint64_t a, b;
+    uint64_t c_dst[kMaxDst];
+    int n_dst;
+    uint32_t m, n, k;
+    uint64_t lda, ldb, ldc;
+    int out_bf16, epilogue;
+    uint64_t bias;
+    float alpha;
+    uint64_t workspace;
+    size_t workspace_bytes;
+    bool slabs_only;        // leave unreduced split-K slabs in c_dst[0] (reference contract)
+    uint32_t force_split;   // for slabs_only: the exact number of slabs the caller expects
+};
+
+int32_t launch_reduce(t0b_ctx* ctx, const float* partial, uint32_t sk, uint32_t m, uint32_t n, uint64_t slab_stride,
+                      uint64_t ld_partial, void* c, uint64_t ldc, int out_bf16, int epilogue, const float* bias,
+                      float alpha) {
+    ReduceParams rp{partial, static_cast<long long>(slab_stride), static_cast<long long>(ld_partial), c,
+                    static_cast<long long>(ldc), bias, alpha, static_cast<int>(m), static_cast<int>(n),
+                    static_cast<int>(sk), out_bf16, epilogue};
+    const long long total = static_cast<long long>(m) * ((n + 3) / 4);
+    const int blocks = static_cast<int>(std::min<long long>((total + 255) / 256, static_cast<long long>(ctx->num_sms) * 8));
+    splitk_reduce_kernel<<<std::max(blocks, 1), 256, 0, ctx->stream>>>(rp);
+    return check_cuda(ctx, cudaGetLastError(), "splitk_reduce launch");
+}
+
+int32_t run_gemm(t0b_ctx* ctx, const GemmCall& g) {
+    if (g.m == 0 || g.n == 0) return T0B_OK;
+    if (!g.a || !g.b || g.n_dst < 1 || g.n_dst > kMaxDst)
+        return set_error(ctx, T0B_ERR_INVALID, "gemm: null operand or bad destination count");
+    for (int d = 0; d < g.n_dst; ++d)
+        if (!g.c_dst[d]) return set_error(ctx, T0B_ERR_INVALID, "gemm: null destination %d", d);
+    const uint64_t min_lda = g.trans_a ? g.m : g.k, min_ldb = g.trans_b ? g.k : g.n;
+    if (g.lda < min_lda || g.ldb < min_ldb || g.ldc < g.n)
+        return set_error(ctx, T0B_ERR_INVALID, "gemm: leading dimension smaller than the row length (lda=%llu ldb=%llu ldc=%llu)",
+                         static_cast<unsigned long long>(g.lda), static_cast<unsigned long long>(g.ldb),
+                         static_cast<unsigned long long>(g.ldc));
+    if (g.epilogue < 0 || g.epilogue > EPI_NEG) return set_error(ctx, T0B_ERR_INVALID, "gemm: unknown epilogue %d", g.epilogue);
+    if ((g.epilogue == EPI_BIAS || g.epilogue == EPI_BIAS_RELU) && !g.bias)
+        return set_error(ctx, T0B_ERR_INVALID, "gemm: bias epilogue without a bias pointer");
+
+    t0b_gemm_config cfg;
+    if (g.cfg) cfg = *g.cfg;
+    else {
+        const std::string key = std::to_string(g.m) + "x" + std::to_string(g.n) + "x" + std::to_string(g.k) + "/" +
+                                std::to_string(g.trans_a) + std::to_string(g.trans_b) + std::to_string(g.out_bf16);
+        auto it = ctx->tuned.find(key);
+        if (it != ctx->tuned.end()) cfg = it->second;
+        else default_b200_config(g.m, g.k, g.n, ctx->num_sms, &cfg);
+    }
+    if (g.slabs_only) cfg.split_k = g.force_split;
+    if (cfg.split_k > 1 && (cfg.split_k & (cfg.split_k - 1)) != 0)
+        return set_error(ctx, T0B_ERR_INVALID, "gemm: split_k=%u must be a power of 2", cfg.split_k);
+
+    t0b_gemm_plan plan;
+    PlanInput pin{g.m, g.n, g.k, g.trans_a, g.trans_b, g.lda, g.ldb, g.a, g.b, ctx->num_sms};
+    resolve_plan(&cfg, pin, &plan);
+
+    const size_t elem = g.out_bf16 ? 2 : 4;
+    if (g.k == 0) {
+        // Empty contraction: the result is epilogue(0); only the plain store is meaningful.
+        for (int d = 0; d < g.n_dst; ++d)
+            for (uint32_t r = 0; r < g.m; ++r) {
+                int32_t rc = check_cuda(ctx, cudaMemsetAsync(reinterpret_cast<char*>(g.c_dst[d]) + r * g.ldc * elem, 0,
+                                                             g.n * elem, ctx->stream), "cudaMemsetAsync(k=0)");
+                if (rc != T0B_OK) return rc;
+            }
+        return T0B_OK;
+    }
+
+    // Where do split-K partials go?
+    float* partial = nullptr;
+    uint64_t slab_stride = static_cast<uint64_t>(g.m) * g.n, ld_partial = g.n;
+    uint32_t sk = plan.split_k;
+    if (g.slabs_only) {
+        partial = reinterpret_cast<float*>(g.c_dst[0]);
+        if (sk < g.force_split) {
+            // K has fewer 64-blocks than slabs were asked for: the trailing slabs carry no K range.
+            int32_t rc = check_cuda(ctx, cudaMemsetAsync(partial + slab_stride * sk, 0,
+                                                         slab_stride * 4 * (g.force_split - sk), ctx->stream),
+                                    "cudaMemsetAsync(empty slabs)");
+            if (rc != T0B_OK) return rc;
+        }
+    } else if (sk > 1) {
+        const size_t need = static_cast<size_t>(sk) * slab_stride * 4;
+        if (g.workspace) {
+            if (g.workspace_bytes < need)
+                return set_error(ctx, T0B_ERR_INVALID, "gemm: split-K workspace too small (%zu < %zu bytes)",
+                                 g.workspace_bytes, need);
+            partial = reinterpret_cast<float*>(g.workspace);
+        } else {
+            if (ctx->ws_bytes < need) {
+                if (ctx->capturing) return set_error(ctx, T0B_ERR_INVALID, "gemm: cannot grow the workspace during graph capture");
+                cudaStreamSynchronize(ctx->stream);
+                if (ctx->ws) cudaFree(ctx->ws);
+                ctx->ws = nullptr;
+                ctx->ws_bytes = 0;
+                int32_t rc = check_cuda(ctx, cudaMalloc(&ctx->ws, need), "cudaMalloc(workspace)");
+                if (rc != T0B_OK) return rc;
+                ctx->ws_bytes = need;
+            }
+            partial = static_cast<float*>(ctx->ws);
+        }
+    }
+    const bool to_slabs = g.slabs_only || sk > 1;
+
+    if (!plan.use_tma) {
+        // Operands TMA cannot address: CUDA-core kernel, one launch per K range.
+        for (uint32_t s = 0; s < sk; ++s) {
+            SimtParams sp{};
+            sp.a = reinterpret_cast<const __nv_bfloat16*>(g.a);
+            sp.b = reinterpret_cast<const __nv_bfloat16*>(g.b);
+            sp.lda = g.lda; sp.ldb = g.ldb;
+            sp.M = g.m; sp.N = g.n; sp.K = g.k;
+            sp.trans_a = g.trans_a; sp.trans_b = g.trans_b;
+            sp.k_begin = static_cast<int>(std::min<uint64_t>(g.k, static_cast<uint64_t>(s) * plan.kb_per_split * 64));
+            sp.k_end = static_cast<int>(std::min<uint64_t>(g.k, static_cast<uint64_t>(s + 1) * plan.kb_per_split * 64));
+            const int ndst = to_slabs ? 1 : g.n_dst;
+            for (int d = 0; d < ndst; ++d) {
+                if (to_slabs) {
+                    sp.c = partial + slab_stride * s; sp.ldc = ld_partial; sp.out_bf16 = 0; sp.epilogue = EPI_STORE;
+                    sp.bias = nullptr; sp.alpha = 1.0f;
+                } else {
+                    sp.c = reinterpret_cast<void*>(g.c_dst[d]); sp.ldc = g.ldc; sp.out_bf16 = g.out_bf16;
+                    sp.epilogue = g.epilogue; sp.bias = reinterpret_cast<const float*>(g.bias); sp.alpha = g.alpha;
+                }
+                dim3 grid((g.n + 63) / 64, (g.m + 63) / 64);
+                gemm_bf16_simt_kernel<<<grid, 256, 0, ctx->stream>>>(sp);
+                int32_t rc = check_cuda(ctx, cudaGetLastError(), "simt gemm launch");
+                if (rc != T0B_OK) return rc;
+                ++ctx->launches;
+            }
+        }
+    } else {
+        CUtensorMap ta, tb;
+        int32_t rc;
+        if (!g.trans_a) rc = get_tmap(ctx, g.a, g.k, g.m, g.lda, 64, 128, &ta);
+        else rc = get_tmap(ctx, g.a, g.m, g.k, g.lda, 64, 64, &ta);
+        if (rc != T0B_OK) return rc;
+        const uint32_t bn_cta = plan.bn / plan.cta_group;
+        if (g.trans_b) rc = get_tmap(ctx, g.b, g.k, g.n, g.ldb, 64, bn_cta, &tb);
+        else rc = get_tmap(ctx, g.b, g.n, g.k, g.ldb, 64, 64, &tb);
+        if (rc != T0B_OK) return rc;
+
+        GemmParams p{};
+        for (int d = 0; d < g.n_dst; ++d) p.c_dst[d] = reinterpret_cast<void*>(g.c_dst[d]);
+        p.n_dst = g.n_dst;
+        p.ldc = static_cast<long long>(g.ldc);
+        p.bias = reinterpret_cast<const float*>(g.bias);
+        p.alpha = g.alpha;
+        p.partial = to_slabs ? partial : nullptr;
+        p.slab_stride = static_cast<long long>(slab_stride);
+        p.ld_partial = static_cast<long long>(ld_partial);
+        p.M = g.m; p.N = g.n; p.K = g.k;
+        p.tiles_m = (g.m + plan.bm - 1) / plan.bm;
+        p.tiles_n = (g.n + plan.bn - 1) / plan.bn;
+        // The kernel routes to the slab path when split_k > 1; a single requested slab is the plain store.
+        p.split_k = static_cast<int>(sk);
+        p.kb_total = (g.k + 63) / 64;
+        p.kb_per_split = plan.kb_per_split;
+        p.a_mn_major = g.trans_a ? 1 : 0;     // A stored [K,M]: M contiguous
+        p.b_mn_major = g.trans_b ? 0 : 1;     // B stored [K,N]: N contiguous
+        p.out_bf16 = g.out_bf16;
+        p.epilogue = g.epilogue;
+        p.raster_along_n = cfg.swap_grid ? 0 : 1;
+        p.group = 8;
+        p.mn_lbo = 8192; p.mn_sbo = 1024; p.mn_kstep = 2048;
+        p.status = ctx->status_dev;
+        p.wait_limit_ns = ctx->wait_limit_ns;
+        if (g.slabs_only && sk == 1) {
+            // One slab: store straight into it as f32.
+            p.out_bf16 = 0; p.epilogue = EPI_STORE; p.n_dst = 1; p.ldc = static_cast<long long>(ld_partial);
+        }
+        const int num_work = p.tiles_m * p.tiles_n * p.split_k;
+        if (plan.cta_group == 2) {
+            if (plan.bn == 256) rc = launch_variant<256, 2>(ctx, ta, tb, p, num_work);
+            else rc = launch_variant<128, 2>(ctx, ta, tb, p, num_work);
+        } else {
+            if (plan.bn == 256) rc = launch_variant<256, 1>(ctx, ta, tb, p, num_work);
+            else if (plan.bn == 128) rc = launch_variant<128, 1>(ctx, ta, tb, p, num_work);
+            else rc = launch_variant<64, 1>(ctx, ta, tb, p, num_work);
+        }
+        if (rc != T0B_OK) return rc;
+        ++ctx->launches;
+    }
+
+    if (!g.slabs_only && sk > 1) {
+        for (int d = 0; d < g.n_dst; ++d) {
+            int32_t rc = launch_reduce(ctx, partial, sk, g.m, g.n, slab_stride, ld_partial, reinterpret_cast<void*>(g.c_dst[d]),
+                                       g.ldc, g.out_bf16, g.epilogue, reinterpret_cast<const float*>(g.bias), g.alpha);
+            if (rc != T0B_OK) return rc;
+            ++ctx->launches;
+        }
+    }
+    return T0B_OK;
+}
+
+uint32_t rd_u32(const uint8_t* p) { return p[0] | (p[1] << 8) | (p[2] << 16) | (static_cast<uint32_t>(p[3]) << 24); }
+uint64_t rd_u64(const uint8_t* p) { return rd_u32(p) | (static_cast<uint64_t>(rd_u32(p + 4)) << 32); }
+
+}  // namespace
+
+extern "C" {
+
+int32_t t0b_gemm(t0b_ctx* ctx, const t0b_gemm_config* cfg, int32_t trans_a, int32_t trans_b, uint64_t a, uint64_t b,
+                 uint64_t c, uint32_t m, uint32_t n, uint32_t k, uint64_t lda, uint64_t ldb, uint64_t ldc,
+                 int32_t out_dtype, int32_t epilogue, uint64_t bias, float alpha, uint64_t workspace,
+                 size_t workspace_bytes, int32_t async) {
+    int32_t rc = precheck(ctx);
+    if (rc != T0B_OK) return rc;
+    std::lock_guard<std::recursive_mutex> lk(ctx->mu);
+    GemmCall g{};
+    g.cfg = cfg; g.trans_a = trans_a != 0; g.trans_b = trans_b != 0; g.a = a; g.b = b;
+    g.c_dst[0] = c; g.n_dst = 1; g.m = m; g.n = n; g.k = k; g.lda = lda; g.ldb = ldb; g.ldc = ldc;
+    g.out_bf16 = out_dtype == T0B_OUT_BF16; g.epilogue = epilogue; g.bias = bias; g.alpha = alpha;
+    g.workspace = workspace; g.workspace_bytes = workspace_bytes;
+    if (out_dtype != T0B_OUT_F32 && out_dtype != T0B_OUT_BF16) return set_error(ctx, T0B_ERR_INVALID, "gemm: unknown out_dtype %d", out_dtype);
+    rc = run_gemm(ctx, g);
+    if (rc != T0B_OK) return rc;
+    return finish(ctx, async, "t0b_gemm");
+}
+
+int32_t t0b_gemm_multi_dst(t0b_ctx* ctx, const t0b_gemm_config* cfg, int32_t trans_a, int32_t trans_b, uint64_t a,
+                           uint64_t b, const uint64_t* c_dsts, int32_t n_dst, uint32_t m, uint32_t n_local, uint32_t k,
+                           uint64_t lda, uint64_t ldb, uint64_t ldc, uint64_t col0, int32_t out_dtype, int32_t async) {
+    int32_t rc = precheck(ctx);
+    if (rc != T0B_OK) return rc;
+    if (!c_dsts || n_dst < 1 || n_dst > kMaxDst) return set_error(ctx, T0B_ERR_INVALID, "gemm_multi_dst: 1..%d destinations", kMaxDst);
+    if (col0 + n_local > ldc) return set_error(ctx, T0B_ERR_INVALID, "gemm_multi_dst: column block exceeds the row pitch");
+    std::lock_guard<std::recursive_mutex> lk(ctx->mu);
+    GemmCall g{};
+    t0b_gemm_config local;
+    if (cfg) {
+        local = *cfg;
+        local.split_k = 0;   // the fused store writes final values; no slab stage
+        g.cfg = &local;
+    } else {
+        default_b200_config(m, k, n_local, ctx->num_sms, &local);
+        local.split_k = 0;
+        g.cfg = &local;
+    }
+    g.trans_a = trans_a != 0; g.trans_b = trans_b != 0; g.a = a; g.b = b;
+    const size_t elem = out_dtype == T0B_OUT_BF16 ? 2 : 4;
+    for (int d = 0; d < n_dst; ++d) g.c_dst[d] = c_dsts[d] ? c_dsts[d] + col0 * elem : 0;
+    g.n_dst = n_dst; g.m = m; g.n = n_local; g.k = k; g.lda = lda; g.ldb = ldb; g.ldc = ldc;
+    g.out_bf16 = out_dtype == T0B_OUT_BF16; g.epilogue = EPI_STORE; g.alpha = 1.0f;
+    rc = run_gemm(ctx, g);
+    if (rc != T0B_OK) return rc;
+    return finish(ctx, async, "t0b_gemm_multi_dst");
+}
+
+int32_t t0b_gemm_slabs(t0b_ctx* ctx, const t0b_gemm_config* cfg, uint64_t x, uint64_t wt, uint64_t y, uint32_t m,
+                       uint32_t n, uint32_t k, uint32_t split_k, int32_t async) {
+    int32_t rc = precheck(ctx);
+    if (rc != T0B_OK) return rc;
+    if (split_k == 0 || (split_k & (split_k - 1)) != 0)
+        return set_error(ctx, T0B_ERR_INVALID, "gemm_slabs: split_k=%u must be a power of 2", split_k);
+    std::lock_guard<std::recursive_mutex> lk(ctx->mu);
+    t0b_gemm_config local;
+    if (cfg) local = *cfg;
+    else default_b200_config(m, k, n, ctx->num_sms, &local);
+    GemmCall g{};
+    g.cfg = &local; g.trans_a = 0; g.trans_b = 1; g.a = x; g.b = wt; g.c_dst[0] = y; g.n_dst = 1;
+    g.m = m; g.n = n; g.k = k; g.lda = k; g.ldb = k; g.ldc = n; g.out_bf16 = 0; g.epilogue = EPI_STORE; g.alpha = 1.0f;
+    g.slabs_only = true; g.force_split = split_k;
+    rc = run_gemm(ctx, g);
+    if (rc != T0B_OK) return rc;
+    return finish(ctx, async, "t0b_gemm_slabs");
+}
+
+int32_t t0b_splitk_reduce(t0b_ctx* ctx, uint64_t partial, uint32_t split_k, uint32_t m, uint32_t n,
+                          uint64_t slab_stride_elems, uint64_t ld_partial, uint64_t c, uint64_t ldc, int32_t out_dtype,
+                          int32_t epilogue, uint64_t bias, float alpha, int32_t async) {
+    int32_t rc = precheck(ctx);
+    if (rc != T0B_OK) return rc;
+    if (!partial || !c || split_k == 0) return set_error(ctx, T0B_ERR_INVALID, "splitk_reduce: null pointer or zero split");
+    if (m == 0 || n == 0) return T0B_OK;
+    if (ld_partial < n || ldc < n) return set_error(ctx, T0B_ERR_INVALID, "splitk_reduce: pitch smaller than n");
+    std::lock_guard<std::recursive_mutex> lk(ctx->mu);
+    rc = launch_reduce(ctx, reinterpret_cast<const float*>(partial), split_k, m, n, slab_stride_elems, ld_partial,
+                       reinterpret_cast<void*>(c), ldc, out_dtype == T0B_OUT_BF16, epilogue,
+                       reinterpret_cast<const float*>(bias), alpha);
+    if (rc != T0B_OK) return rc;
+    return finish(ctx, async, "t0b_splitk_reduce");
+}
+
+int32_t t0b_dispatch_kernargs(t0b_ctx* ctx, const t0b_gemm_config* cfg, uint32_t grid_x, uint32_t grid_y,
+                              const uint8_t* ka, size_t len, int32_t async) {
+    int32_t rc = precheck(ctx);
+    if (rc != T0B_OK) return rc;
+    if (!cfg || !ka) return set_error(ctx, T0B_ERR_INVALID, "dispatch_kernargs: null config or kernargs");
+    if (len != 40 && len != 44 && len != 48)
+        return set_error(ctx, T0B_ERR_INVALID, "dispatch_kernargs: kernarg blob must be 40, 44 or 48 bytes, got %zu", len);
+    if (cfg->wg_size == 0 || cfg->tile_m == 0 || cfg->tile_n == 0)
+        return set_error(ctx, T0B_ERR_INVALID, "dispatch_kernargs: config with zero tile or workgroup size");
+    const uint64_t x = rd_u64(ka), wt = rd_u64(ka + 8), y = rd_u64(ka + 16);
+    const uint32_t k = rd_u32(ka + 24), n_pitch = rd_u32(ka + 28), y_stride = rd_u32(ka + 36);
+    const uint32_t sk = cfg->split_k > 1 ? cfg->split_k : 1;
+    if (grid_x % cfg->wg_size != 0) return set_error(ctx, T0B_ERR_INVALID, "dispatch_kernargs: grid_x is not a multiple of wg_size");
+    const uint32_t fast_tiles = grid_x / cfg->wg_size;
+    if (grid_y % sk != 0) return set_error(ctx, T0B_ERR_INVALID, "dispatch_kernargs: grid_y is not a multiple of split_k");
+    const uint32_t slow_tiles = grid_y / sk;
+    const uint32_t tiles_m = cfg->swap_grid ? slow_tiles : fast_tiles;
+    const uint32_t tiles_n = cfg->swap_grid ? fast_tiles : slow_tiles;
+    const uint32_t eff_n = cfg->tile_n * std::max(1u, cfg->n_col_passes);
+    uint32_t m, n;
+    if (len == 44) {
+        m = rd_u32(ka + 40);                                 // the tile_ir blob carries M
+        n = std::min(n_pitch, tiles_n * eff_n);
+        if (m > tiles_m * cfg->tile_m) return set_error(ctx, T0B_ERR_INVALID, "dispatch_kernargs: M exceeds the grid");
+    } else {
+        m = tiles_m * cfg->tile_m;                           // recovered from the grid
+        n = tiles_n * eff_n;
+        if (n > n_pitch) return set_error(ctx, T0B_ERR_INVALID, "dispatch_kernargs: grid covers more columns than the N kernarg");
+    }
+    std::lock_guard<std::recursive_mutex> lk(ctx->mu);
+    GemmCall g{};
+    t0b_gemm_config local = *cfg;
+    g.cfg = &local; g.trans_a = 0; g.trans_b = 1; g.a = x; g.b = wt; g.c_dst[0] = y; g.n_dst = 1;
+    g.m = m; g.n = n; g.k = k; g.lda = k; g.ldb = k; g.ldc = n_pitch; g.alpha = 1.0f;
+    g.out_bf16 = 0;
+    g.epilogue = cfg->epilogue;
+    g.bias = len == 48 ? rd_u64(ka + 40) : 0;
+    if (g.epilogue != EPI_STORE && (len != 48 || !g.bias)) g.epilogue = EPI_STORE;   // gemm_gen.rs:437: bias 0 = plain store
+    if (sk > 1) {
+        if (y_stride != m * n * 4u)
+            return set_error(ctx, T0B_ERR_INVALID, "dispatch_kernargs: y_split_stride %u does not match M*N*4 = %u", y_stride, m * n * 4u);
+        g.slabs_only = true; g.force_split = sk; g.ldc = n; g.epilogue = EPI_STORE;
+    } else {
+        local.split_k = 0;
+    }
+    rc = run_gemm(ctx, g);
+    if (rc != T0B_OK) return rc;
+    return finish(ctx, async, "t0b_dispatch_kernargs");
+}
+
+int32_t t0b_gemm_time(t0b_ctx* ctx, const t0b_gemm_config* cfg, int32_t trans_a, int32_t trans_b, uint64_t a, uint64_t b,
+                      uint64_t c, uint32_t m, uint32_t n, uint32_t k, uint64_t lda, uint64_t ldb, uint64_t ldc,
+                      int32_t out_dtype, int32_t warmup, int32_t iters, float* ms) {
+    int32_t rc = precheck(ctx);
+    if (rc != T0B_OK) return rc;
+    if (!ms || iters < 1) return set_error(ctx, T0B_ERR_INVALID, "gemm_time: bad arguments");
+    for (int i = 0; i < warmup; ++i) {
+        rc = t0b_gemm(ctx, cfg, trans_a, trans_b, a, b, c, m, n, k, lda, ldb, ldc, out_dtype, 0, 0, 1.0f, 0, 0, 1);
+        if (rc != T0B_OK) return rc;
+    }
+    cudaEvent_t e0, e1;
+    cudaEventCreate(&e0);
+    cudaEventCreate(&e1);
+    cudaStreamSynchronize(ctx->stream);
+    cudaEventRecord(e0, ctx->stream);
+    for (int i = 0; i < iters; ++i) {
+        rc = t0b_gemm(ctx, cfg, trans_a, trans_b, a, b, c, m, n, k, lda, ldb, ldc, out_dtype, 0, 0, 1.0f, 0, 0, 1);
+        if (rc != T0B_OK) break;
+    }
+    cudaEventRecord(e1, ctx->stream);
+    cudaError_t e = cudaEventSynchronize(e1);
+    float total = 0.0f;
+    if (e == cudaSuccess) cudaEventElapsedTime(&total, e0, e1);
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+    if (rc != T0B_OK) return rc;
+    if (e != cudaSuccess) return check_cuda(ctx, e, "gemm_time");
+    const int st = t0b_device_status(ctx, 0);
+    if (st != 0) return set_error(ctx, T0B_ERR_DEVICE, "gemm_time: device status %d", st);
+    *ms = total / static_cast<float>(iters);
+    return T0B_OK;
+}
+
+int32_t t0b_tune(t0b_ctx* ctx, uint32_t m, uint32_t n, uint32_t k, int32_t trans_a, int32_t trans_b, int32_t out_dtype,
+                 t0b_gemm_config* best, float* best_tflops) {
+    int32_t rc = precheck(ctx);
+    if (rc != T0B_OK) return rc;
+    if (!best || m == 0 || n == 0 || k == 0) return set_error(ctx, T0B_ERR_INVALID, "tune: bad arguments");
+    const size_t elem = out_dtype == T0B_OUT_BF16 ? 2 : 4;
+    uint64_t a = 0, b = 0, c = 0;
+    rc = t0b_alloc_zero(ctx, static_cast<size_t>(m) * k * 2, &a);
+    if (rc == T0B_OK) rc = t0b_alloc_zero(ctx, static_cast<size_t>(n) * k * 2, &b);
+    if (rc == T0B_OK) rc = t0b_alloc(ctx, static_cast<size_t>(m) * n * elem, &c);
+    if (rc != T0B_OK) return rc;
+    const uint64_t lda = trans_a ? m : k, ldb = trans_b ? k : n;
+    static const char* tiles[] = {"b200_256x256", "b200_256x128", "b200_128x256", "b200_128x128", "b200_128x64"};
+    const uint32_t kb_total = (k + 63) / 64;
+    float best_ms = 1e30f;
+    for (const char* t : tiles) {
+        for (uint32_t sk = 1; sk <= 16; sk *= 2) {
+            if (sk > 1 && kb_total / sk < 2) break;
+            t0b_gemm_config cfg;
+            t0b_config_preset(t, &cfg);
+            cfg.wgp_mode = cfg.tile_m >= 256;
+            cfg.split_k = sk > 1 ? sk : 0;
+            t0b_gemm_plan plan;
+            PlanInput pin{m, n, k, trans_a, trans_b, lda, ldb, a, b, ctx->num_sms};
+            resolve_plan(&cfg, pin, &plan);
+            const uint64_t work = static_cast<uint64_t>((m + plan.bm - 1) / plan.bm) * ((n + plan.bn - 1) / plan.bn);
+            if (sk > 1 && work * (sk / 2) >= static_cast<uint64_t>(ctx->num_sms) / plan.cta_group) break;   // already full
+            for (uint32_t swap = 0; swap < 2; ++swap) {
+                cfg.swap_grid = swap;
+                float ms = 0.0f;
+                rc = t0b_gemm_time(ctx, &cfg, trans_a, trans_b, a, b, c, m, n, k, lda, ldb, n, out_dtype, 2, 5, &ms);
+                if (rc != T0B_OK) goto done;
+                if (ms < best_ms) { best_ms = ms; *best = cfg; }
+            }
+        }
+    }
+done:
+    t0b_recycle(ctx, a);
+    t0b_recycle(ctx, b);
+    t0b_recycle(ctx, c);
+    if (rc != T0B_OK) return rc;
+    if (best_tflops) *best_tflops = 2.0f * m * n * static_cast<float>(k) / (best_ms * 1e-3f) / 1e12f;
+    const std::string key = std::to_string(m) + "x" + std::to_string(n) + "x" + std::to_string(k) + "/" +
+                            std::to_string(trans_a != 0) + std::to_string(trans_b != 0) + std::to_string(out_dtype == T0B_OUT_BF16);
+    ctx->tuned[key] = *best;
+    return T0B_OK;
+}
+
+int32_t t0b_selftest_bounded_wait(t0b_ctx* ctx, uint64_t limit_ns) {
+    int32_t rc = precheck(ctx);
+    if (rc != T0B_OK) return rc;
+    if (limit_ns == 0 || limit_ns > 5000000000ull) return set_error(ctx, T0B_ERR_INVALID, "selftest: limit must be in (0, 5e9] ns");
+    bounded_wait_selftest_kernel<<<1, 32, 0, ctx->stream>>>(ctx->status_dev, limit_ns);
+    rc = finish(ctx, 0, "bounded-wait self test");
+    return rc;
+}
+
+}  // extern "C"

@@ -1,0 +1,381 @@
+// Host-side GEMM front-end: GemmConfig presets, names, grids, kernarg blobs, auto_select and the mapping of a
+// GemmConfig onto the sm_100a kernel family.  Mirrors the public functions of src/t0/gemm_gen.rs (reference
+// project paths); the RDNA3 code generator behind them is replaced by precompiled tcgen05 kernels.
+#include <algorithm>
+#include <cmath>
+#include <cstring>
+#include <string>
+
+#include "t0b_internal.hpp"
+
+namespace {
+
+t0b_gemm_config make_cfg(uint32_t tm, uint32_t tn, uint32_t tk, uint32_t wg, bool lds, bool db, uint32_t passes = 1) {
+    t0b_gemm_config c{};
+    c.tile_m = tm;
+    c.tile_n = tn;
+    c.tile_k = tk;
+    c.wg_size = wg;
+    c.use_lds = lds;
+    c.double_buffer = db;
+    c.split_k = 0;
+    c.lds_pad = 0;
+    c.n_col_passes = passes;
+    c.swap_grid = 1;
+    c.wgp_mode = 1;
+    c.transpose = T0B_TRANSPOSE_NT;
+    c.epilogue = T0B_EPI_STORE_F32;
+    return c;
+}
+
+struct Preset {
+    const char* name;
+    t0b_gemm_config cfg;
+};
+
+// The reference's presets (gemm_gen.rs:86-145) followed by the B200-native tiles.
+const Preset* presets(int* count) {
+    static const Preset table[] = {
+        {"16x64_k16", make_cfg(16, 64, 16, 32, true, true)},
+        {"32x64_direct", make_cfg(32, 64, 16, 64, false, false)},
+        {"32x64_k16", make_cfg(32, 64, 16, 64, true, true)},
+        {"32x64_k32", make_cfg(32, 64, 32, 64, true, true)},
+        {"32x128_k16", make_cfg(32, 128, 16, 64, true, true)},
+        {"64x64_k16", make_cfg(64, 64, 16, 64, true, true)},
+        {"64x64_k32", make_cfg(64, 64, 32, 64, true, true)},
+        {"128x64_k16", make_cfg(128, 64, 16, 128, true, true)},
+        {"64x128_k16", make_cfg(64, 128, 16, 64, true, true)},
+        {"128x64_k32", make_cfg(128, 64, 32, 128, true, true)},
+        {"128x128_k16", make_cfg(128, 128, 16, 128, true, true)},
+        {"64x64_k64", make_cfg(64, 64, 64, 64, true, true)},
+        {"128x128_2pass", make_cfg(128, 64, 16, 128, true, true, 2)},
+        {"64x128_2pass", make_cfg(64, 64, 16, 64, true, true, 2)},
+        {"b200_128x64", make_cfg(128, 64, 64, 192, true, true)},
+        {"b200_128x128", make_cfg(128, 128, 64, 192, true, true)},
+        {"b200_128x256", make_cfg(128, 256, 64, 192, true, true)},
+        {"b200_256x128", make_cfg(256, 128, 64, 192, true, true)},
+        {"b200_256x256", make_cfg(256, 256, 64, 192, true, true)},
+    };
+    *count = static_cast<int>(sizeof(table) / sizeof(table[0]));
+    return table;
+}
+
+t0b_gemm_config preset_or_die(const char* name) {
+    int n;
+    const Preset* t = presets(&n);
+    for (int i = 0; i < n; ++i)
+        if (std::strcmp(t[i].name, name) == 0) return t[i].cfg;
+    return make_cfg(64, 64, 16, 64, true, true);
+}
+
+uint32_t sk_of(const t0b_gemm_config* c) { return c->split_k == 0 ? 1u : c->split_k; }
+
+void put_u64(uint8_t* p, uint64_t v) {
+    for (int i = 0; i < 8; ++i) p[i] = static_cast<uint8_t>(v >> (8 * i));
+}
+void put_u32(uint8_t* p, uint32_t v) {
+    for (int i = 0; i < 4; ++i) p[i] = static_cast<uint8_t>(v >> (8 * i));
+}
+
+int stages_for(uint32_t bn, uint32_t cg) {
+    const int bn_cta = static_cast<int>(bn / cg);
+    const int stage = 128 * 64 * 2 + bn_cta * 64 * 2;
+    const int budget = 227 * 1024 - 1024 - 512;
+    return std::min(8, budget / stage);
+}
+
+}  // namespace
+
+namespace t0b {
+
+// Pick the B200 tile for a shape.  Score = wave efficiency x padding efficiency x a per-tile throughput
+// factor (larger tiles re-use more of each shared-memory byte); small grids get a power-of-two split-K.
+void default_b200_config(uint32_t m, uint32_t k, uint32_t n, int num_sms, t0b_gemm_config* out) {
+    struct Cand {
+        uint32_t cg, bn;
+        double factor;
+    };
+    static const Cand cands[] = {{2, 256, 1.00}, {2, 128, 0.90}, {1, 256, 0.93}, {1, 128, 0.82}, {1, 64, 0.62}};
+    if (num_sms <= 0) num_sms = 148;
+    double best = -1.0;
+    Cand pick = cands[3];
+    uint64_t pick_tiles = 1;
+    for (const Cand& c : cands) {
+        const uint64_t bm = 128ull * c.cg;
+        const uint64_t tiles = ((m + bm - 1) / bm) * ((n + c.bn - 1) / c.bn);
+        const uint64_t clusters = static_cast<uint64_t>(num_sms) / c.cg;
+        const uint64_t waves = (tiles + clusters - 1) / clusters;
+        const double eff_wave = static_cast<double>(tiles) / static_cast<double>(waves * clusters);
+        const double eff_tile = (static_cast<double>(m) * n) / (static_cast<double>(tiles) * bm * c.bn);
+        const double score = eff_wave * eff_tile * c.factor;
+        if (score > best) {
+            best = score;
+            pick = c;
+            pick_tiles = tiles;
+        }
+    }
+    t0b_gemm_config cfg = make_cfg(128 * pick.cg, pick.bn, 64, 192, true, true);
+    cfg.wgp_mode = pick.cg == 2;
+    cfg.swap_grid = (m >= n) ? 1 : 0;
+    const uint64_t clusters = static_cast<uint64_t>(num_sms) / pick.cg;
+    const uint32_t kb_total = (k + 63) / 64;
+    if (pick_tiles * 2 <= clusters && kb_total >= 8) {
+        uint32_t sk = 1;
+        while (sk * 2 * pick_tiles <= clusters && kb_total / (sk * 2) >= 4 && sk < 16) sk *= 2;
+        if (sk > 1) cfg.split_k = sk;
+    }
+    *out = cfg;
+}
+
+void resolve_plan(const t0b_gemm_config* cfg_in, const PlanInput& in, t0b_gemm_plan* out) {
+    t0b_gemm_config cfg;
+    if (cfg_in) cfg = *cfg_in;
+    else default_b200_config(in.m, in.k, in.n, in.num_sms, &cfg);
+    const int num_sms = in.num_sms > 0 ? in.num_sms : 148;
+    t0b_gemm_plan p{};
+    p.cta_group = cfg.tile_m >= 256 ? 2 : 1;
+    const uint32_t want_n = cfg.tile_n * std::max(1u, cfg.n_col_passes);
+    p.bn = want_n <= 64 ? 64 : (want_n <= 128 ? 128 : 256);
+    if (p.cta_group == 2 && p.bn < 128) p.bn = 128;
+    p.bm = 128 * p.cta_group;
+    p.bk = 64;
+    p.stages = static_cast<uint32_t>(stages_for(p.bn, p.cta_group));
+    const uint32_t kb_total = (in.k + 63) / 64;
+    uint32_t sk = std::max(1u, sk_of(&cfg));
+    sk = std::min(sk, std::max(1u, kb_total));
+    const uint32_t kbps = kb_total == 0 ? 0 : (kb_total + sk - 1) / sk;
+    p.kb_per_split = kbps;
+    p.split_k = kbps == 0 ? 1 : (kb_total + kbps - 1) / kbps;
+    p.use_tma = (in.a_ptr % 16 == 0) && (in.b_ptr % 16 == 0) && ((in.lda * 2) % 16 == 0) && ((in.ldb * 2) % 16 == 0) &&
+                in.lda > 0 && in.ldb > 0;
+    const uint64_t tiles = static_cast<uint64_t>((in.m + p.bm - 1) / p.bm) * ((in.n + p.bn - 1) / p.bn) * p.split_k;
+    const uint64_t clusters = static_cast<uint64_t>(num_sms) / p.cta_group;
+    p.grid = static_cast<uint32_t>(std::min<uint64_t>(tiles, clusters) * p.cta_group);
+    p.smem_bytes = p.stages * (128 * 64 * 2 + (p.bn / p.cta_group) * 64 * 2) + 1024 + 512;
+    *out = p;
+}
+
+}  // namespace t0b
+
+extern "C" {
+
+int32_t t0b_config_preset(const char* name, t0b_gemm_config* out) {
+    if (!name || !out) return T0B_ERR_INVALID;
+    std::string s(name);
+    if (s.rfind("tile_", 0) == 0) s = s.substr(5);
+    int n;
+    const Preset* t = presets(&n);
+    for (int i = 0; i < n; ++i)
+        if (s == t[i].name) {
+            *out = t[i].cfg;
+            return T0B_OK;
+        }
+    return T0B_ERR_INVALID;
+}
+
+int32_t t0b_config_name(const t0b_gemm_config* c, char* buf, size_t cap) {
+    if (!c || !buf || cap == 0) return T0B_ERR_INVALID;
+    std::string s = "t0_gemm_" + std::to_string(c->tile_m) + "x" + std::to_string(c->tile_n) + "_k" +
+                    std::to_string(c->tile_k);
+    s += c->use_lds ? (c->double_buffer ? "_ldsdb" : "_lds") : "_direct";
+    if (c->split_k > 1) s += "_sk" + std::to_string(c->split_k);
+    if (c->n_col_passes > 1) s += "_" + std::to_string(c->n_col_passes) + "p";
+    if (!c->swap_grid) s += "_mg";
+    if (c->wgp_mode) s += "_wgp";
+    if (c->transpose == T0B_TRANSPOSE_NN) s += "_nn";
+    if (c->epilogue == T0B_EPI_BIAS_ADD) s += "_bias";
+    else if (c->epilogue == T0B_EPI_BIAS_ADD_RELU) s += "_bias_relu";
+    const size_t len = std::min(s.size(), cap - 1);
+    std::memcpy(buf, s.data(), len);
+    buf[len] = 0;
+    return static_cast<int32_t>(len);
+}
+
+int32_t t0b_sweep_configs(t0b_gemm_config* out, int32_t cap) {
+    static const char* names[] = {"16x64_k16", "32x64_k16",  "32x64_k32",  "32x128_k16", "64x64_k16",
+                                  "64x64_k32", "128x64_k16", "64x128_k16", "128x64_k32"};
+    const int32_t n = 9;
+    for (int32_t i = 0; i < n && i < cap && out; ++i) out[i] = preset_or_die(names[i]);
+    return n;
+}
+
+int32_t t0b_standard_configs(t0b_gemm_config* out, int32_t cap) {
+    struct E {
+        const char* name;
+        uint32_t sk;
+    };
+    static const E list[] = {{"16x64_k16", 0},  {"32x64_k16", 0}, {"32x64_k32", 0}, {"32x128_k16", 0}, {"64x64_k16", 0},
+                             {"64x64_k32", 0},  {"128x64_k32", 0}, {"32x64_k32", 2}, {"16x64_k16", 4},  {"64x64_k32", 2},
+                             {"64x64_k16", 4},  {"64x64_k32", 4},  {"64x64_k16", 8}, {"128x64_k32", 2}};
+    const int32_t n = 14;
+    for (int32_t i = 0; i < n && i < cap && out; ++i) {
+        out[i] = preset_or_die(list[i].name);
+        out[i].split_k = list[i].sk;
+    }
+    return n;
+}
+
+uint32_t t0b_config_lds_total(const t0b_gemm_config* c) {
+    if (!c) return 0;
+    const uint32_t per = c->tile_m * c->tile_k * 2 + c->tile_n * c->tile_k * 2;
+    return c->double_buffer ? per * 2 : per;
+}
+
+uint32_t t0b_config_estimated_vgprs(const t0b_gemm_config* c) {
+    if (!c || c->wg_size < 32) return 0;
+    const uint32_t n_waves = c->wg_size / 32;
+    const uint32_t nrb = (c->tile_m / n_waves) / 16;
+    const uint32_t nct = c->tile_n / 16;
+    const uint32_t x_lpt = (c->tile_m * c->tile_k * 2 / c->wg_size) / 16;
+    const uint32_t wt_lpt = (c->tile_n * c->tile_k * 2 / c->wg_size) / 16;
+    return nrb * nct * 8 + nrb * 8 + nct * 8 + x_lpt * 4 + wt_lpt * 4 + 49;
+}
+
+// The reference rejects configs whose RDNA3 register estimate exceeds 256 (gemm_gen.rs:189-205).  On B200 the
+// accumulators live in TMEM, so every config that maps onto the kernel family is feasible.
+int32_t t0b_config_is_feasible(const t0b_gemm_config* c) {
+    if (!c) return 0;
+    return c->tile_m >= 1 && c->tile_n >= 1 && c->tile_k >= 1 && (c->split_k == 0 || (c->split_k & (c->split_k - 1)) == 0);
+}
+
+int32_t t0b_auto_select(uint32_t m, uint32_t k, uint32_t n, t0b_gemm_config* out) {
+    if (!out || m == 0 || n == 0 || k == 0) return T0B_ERR_INVALID;
+    t0b::default_b200_config(m, k, n, 148, out);
+    return T0B_OK;
+}
+
+int32_t t0b_auto_select_legacy(uint32_t m, uint32_t k, uint32_t n, t0b_gemm_config* out) {
+    if (!out || m == 0 || n == 0 || k == 0) return T0B_ERR_INVALID;
+    const uint64_t mn = static_cast<uint64_t>(m) * n;
+    // Largest power-of-two split <= desired that keeps K a multiple of tile_k * split.
+    auto clamp_sk = [k](uint32_t tile_k, uint32_t desired) -> uint32_t {
+        uint32_t sk = std::min(desired, k / tile_k);
+        while (sk > 1 && k % (tile_k * sk) != 0) sk /= 2;
+        return sk > 1 ? sk : 0;
+    };
+    const bool m128 = (m % 128 == 0) && m >= 128;
+    const bool m64 = (m % 64 == 0);
+    const bool wide = k >= 512 && n >= 1024 && m128;
+    t0b_gemm_config c;
+    if (m <= 256 && wide) {
+        c = preset_or_die("128x64_k16"); c.swap_grid = 0; c.split_k = clamp_sk(16, 4);
+    } else if (m <= 512 && wide) {
+        c = preset_or_die("128x64_k16"); c.swap_grid = 0; c.split_k = clamp_sk(16, 8);
+    } else if (mn <= 512ull * 512ull) {
+        c = preset_or_die("64x64_k16"); c.swap_grid = 0; c.split_k = clamp_sk(16, 8);
+    } else if (mn <= 1024ull * 1024ull && m128) {
+        c = preset_or_die("128x64_k16"); c.swap_grid = 0; c.split_k = clamp_sk(16, 2);
+    } else if (m128) {
+        c = preset_or_die("128x64_k16"); c.split_k = clamp_sk(16, 8);
+    } else if (m64) {
+        c = preset_or_die("64x64_k16"); c.split_k = clamp_sk(16, 4);
+    } else {
+        c = preset_or_die("32x64_k16"); c.split_k = clamp_sk(16, 4);
+    }
+    *out = c;
+    return T0B_OK;
+}
+
+int32_t t0b_auto_select_backward_data(uint32_t m, uint32_t n_orig, uint32_t k_orig, t0b_gemm_config* out) {
+    return t0b_auto_select(m, n_orig, k_orig, out);   // dX[M,K] = dY[M,N] * W: contraction over N_orig
+}
+int32_t t0b_auto_select_backward_weight(uint32_t m, uint32_t n_orig, uint32_t k_orig, t0b_gemm_config* out) {
+    return t0b_auto_select(n_orig, m, k_orig, out);   // dW[N,K] = dY^T * X: contraction over M
+}
+
+int32_t t0b_compute_grid(const t0b_gemm_config* c, uint32_t m, uint32_t n, uint32_t* gx, uint32_t* gy) {
+    if (!c || !gx || !gy || c->tile_m == 0 || c->tile_n == 0) return T0B_ERR_INVALID;
+    const uint32_t eff_n = c->tile_n * std::max(1u, c->n_col_passes);
+    const uint32_t tiles_m = (m + c->tile_m - 1) / c->tile_m;
+    const uint32_t tiles_n = (n + eff_n - 1) / eff_n;
+    if (c->swap_grid) { *gx = tiles_n * c->wg_size; *gy = tiles_m; }
+    else { *gx = tiles_m * c->wg_size; *gy = tiles_n; }
+    return T0B_OK;
+}
+
+int32_t t0b_compute_grid_split_k(const t0b_gemm_config* c, uint32_t m, uint32_t n, uint32_t sk, uint32_t* gx,
+                                 uint32_t* gy) {
+    if (sk == 0 || (sk & (sk - 1)) != 0) return T0B_ERR_INVALID;   // the reference asserts a power of two
+    const int32_t rc = t0b_compute_grid(c, m, n, gx, gy);
+    if (rc != T0B_OK) return rc;
+    *gy *= sk;
+    return T0B_OK;
+}
+
+int32_t t0b_compute_grid_auto(const t0b_gemm_config* c, uint32_t m, uint32_t n, uint32_t* gx, uint32_t* gy) {
+    if (!c) return T0B_ERR_INVALID;
+    const uint32_t sk = sk_of(c);
+    return sk > 1 ? t0b_compute_grid_split_k(c, m, n, sk, gx, gy) : t0b_compute_grid(c, m, n, gx, gy);
+}
+
+int32_t t0b_compute_grid_backward_data(const t0b_gemm_config* c, uint32_t m, uint32_t k_orig, uint32_t* gx,
+                                       uint32_t* gy) {
+    return t0b_compute_grid_auto(c, m, k_orig, gx, gy);
+}
+int32_t t0b_compute_grid_backward_weight(const t0b_gemm_config* c, uint32_t n_orig, uint32_t k_orig, uint32_t* gx,
+                                         uint32_t* gy) {
+    return t0b_compute_grid_auto(c, n_orig, k_orig, gx, gy);
+}
+
+int32_t t0b_build_kernargs(uint64_t x, uint64_t wt, uint64_t y, uint32_t k, uint32_t n, uint32_t m,
+                           const t0b_gemm_config* c, uint8_t out[40]) {
+    if (!c || !out) return T0B_ERR_INVALID;
+    const uint32_t y_stride = sk_of(c) > 1 ? m * n * 4u : 0u;
+    put_u64(out + 0, x);
+    put_u64(out + 8, wt);
+    put_u64(out + 16, y);
+    put_u32(out + 24, k);
+    put_u32(out + 28, n);
+    put_u32(out + 32, 0);
+    put_u32(out + 36, y_stride);
+    return T0B_OK;
+}
+
+int32_t t0b_build_kernargs_with_bias(uint64_t x, uint64_t wt, uint64_t y, uint32_t k, uint32_t n, uint32_t m,
+                                     const t0b_gemm_config* c, uint64_t bias, uint8_t out[48]) {
+    const int32_t rc = t0b_build_kernargs(x, wt, y, k, n, m, c, out);
+    if (rc != T0B_OK) return rc;
+    put_u64(out + 40, bias);
+    return T0B_OK;
+}
+
+int32_t t0b_build_kernargs_m(uint64_t x, uint64_t wt, uint64_t y, uint32_t k, uint32_t n, uint32_t m, uint8_t out[44]) {
+    if (!out) return T0B_ERR_INVALID;
+    put_u64(out + 0, x);
+    put_u64(out + 8, wt);
+    put_u64(out + 16, y);
+    put_u32(out + 24, k);
+    put_u32(out + 28, n);
+    put_u32(out + 32, 0);
+    put_u32(out + 36, 0);
+    put_u32(out + 40, m);
+    return T0B_OK;
+}
+
+int32_t t0b_build_kernargs_backward_data(uint64_t dy, uint64_t w, uint64_t dx, uint32_t m, uint32_t n_orig,
+                                         uint32_t k_orig, const t0b_gemm_config* c, uint8_t out[40]) {
+    return t0b_build_kernargs(dy, w, dx, n_orig, k_orig, m, c, out);
+}
+int32_t t0b_build_kernargs_backward_weight(uint64_t dy_t, uint64_t x_t, uint64_t dw, uint32_t m, uint32_t n_orig,
+                                           uint32_t k_orig, const t0b_gemm_config* c, uint8_t out[40]) {
+    return t0b_build_kernargs(dy_t, x_t, dw, m, k_orig, n_orig, c, out);
+}
+
+int32_t t0b_resolve_plan(const t0b_gemm_config* cfg, uint32_t m, uint32_t n, uint32_t k, int32_t trans_a,
+                         int32_t trans_b, uint64_t lda, uint64_t ldb, int32_t num_sms, t0b_gemm_plan* out) {
+    if (!out) return T0B_ERR_INVALID;
+    t0b::PlanInput in{m, n, k, trans_a, trans_b, lda, ldb, 0, 0, num_sms};
+    t0b::resolve_plan(cfg, in, out);
+    return T0B_OK;
+}
+
+size_t t0b_gemm_workspace_bytes(const t0b_gemm_config* cfg, uint32_t m, uint32_t n, uint32_t k) {
+    t0b_gemm_plan p;
+    t0b::PlanInput in{m, n, k, 0, 1, k, k, 0, 0, 148};
+    t0b::resolve_plan(cfg, in, &p);
+    return p.split_k > 1 ? static_cast<size_t>(p.split_k) * m * n * 4 : 0;
+}
+
+const char* t0b_version(void) { return "t0b200 0.1 (sm_100a)"; }
+
+}  // extern "C"

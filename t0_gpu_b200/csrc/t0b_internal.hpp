@@ -1,0 +1,84 @@
+// Internal declarations shared by the translation units of libt0b200.so.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+#include <map>
+#include <mutex>
+#include <string>
+#include <unordered_map>
+#include <vector>
+
+#include "../../include/t0b200.h"
+
+struct t0b_ctx {
+    int device = 0;
+    int num_sms = 148;
+    cudaStream_t own_stream = nullptr;
+    cudaStream_t stream = nullptr;
+    std::recursive_mutex mu;
+    std::string last_error;
+    bool poisoned = false;
+    // Device status word: pinned host memory mapped into the device, so a kernel can report that one of its
+    // bounded waits ran out without any copy.
+    int* status_host = nullptr;
+    int* status_dev = nullptr;
+    unsigned long long wait_limit_ns = 2000000000ull;
+    // Buffer pool keyed by 4 KiB-rounded size.
+    std::multimap<size_t, void*> pool_free;
+    std::unordered_map<void*, size_t> live;
+    uint64_t pool_cached = 0, pool_hits = 0, pool_misses = 0;
+    // Grow-only split-K workspace.
+    void* ws = nullptr;
+    size_t ws_bytes = 0;
+    // Tensor-map cache.
+    struct TmapKey {
+        uint64_t ptr, d0, d1, ld;
+        uint32_t b0, b1;
+        bool operator==(const TmapKey& o) const {
+            return ptr == o.ptr && d0 == o.d0 && d1 == o.d1 && ld == o.ld && b0 == o.b0 && b1 == o.b1;
+        }
+    };
+    struct TmapHash {
+        size_t operator()(const TmapKey& k) const {
+            uint64_t h = k.ptr * 0x9E3779B97F4A7C15ull;
+            h ^= (k.d0 + 0x9E3779B97F4A7C15ull + (h << 6) + (h >> 2));
+            h ^= (k.d1 + 0x9E3779B97F4A7C15ull + (h << 6) + (h >> 2));
+            h ^= (k.ld + 0x9E3779B97F4A7C15ull + (h << 6) + (h >> 2));
+            h ^= ((static_cast<uint64_t>(k.b0) << 32 | k.b1) + (h << 6) + (h >> 2));
+            return static_cast<size_t>(h);
+        }
+    };
+    std::unordered_map<TmapKey, CUtensorMap, TmapHash> tmaps;
+    // Graph capture.
+    bool capturing = false;
+    std::unordered_map<uint64_t, cudaGraphExec_t> graphs;
+    uint64_t next_graph = 1;
+    uint64_t launches = 0;
+    // In-memory autotune results keyed by "MxNxK/ta/tb/out".
+    std::unordered_map<std::string, t0b_gemm_config> tuned;
+};
+
+namespace t0b {
+
+int32_t set_error(t0b_ctx* ctx, int32_t code, const char* fmt, ...);
+int32_t check_cuda(t0b_ctx* ctx, cudaError_t e, const char* what);
+int32_t precheck(t0b_ctx* ctx);                 // null / poisoned checks, sets the device
+int32_t finish(t0b_ctx* ctx, int32_t async, const char* what);   // launch-error check (+ sync when !async)
+
+// Host-side GemmConfig logic (t0b_gemm_gen.cpp).
+void default_b200_config(uint32_t m, uint32_t k, uint32_t n, int num_sms, t0b_gemm_config* out);
+
+struct PlanInput {
+    uint32_t m, n, k;
+    int trans_a, trans_b;
+    uint64_t lda, ldb;
+    uint64_t a_ptr, b_ptr;
+    int num_sms;
+};
+void resolve_plan(const t0b_gemm_config* cfg, const PlanInput& in, t0b_gemm_plan* out);
+
+}  // namespace t0b

@@ -1,0 +1,586 @@
+// Memory-bound kernels around the GEMMs: casts, RMSNorm, softmax, fused softmax cross-entropy, SiLU gate,
+// gradient accumulate, AdamW.  All are HBM-bound: 128-bit accesses, one global read of each input where the
+// row fits on chip, warp-shuffle + shared-memory block reductions, fixed reduction orders (no atomics).
+// Reference kernels these stand in for: src/t0/rmsnorm_kernels.rs, src/ignis/ops/rmsnorm.rs,
+// src/t0/softmax_kernels.rs, src/t0/ce_loss_kernels.rs, examples/kernels/softmax_ce_loss.rs,
+// src/ignis/ops/silu.rs, src/t0/elementwise_kernels.rs, src/t0/adamw_kernels.rs.
+#include <cuda_bf16.h>
+
+#include <algorithm>
+#include <cfloat>
+
+#include "t0b_internal.hpp"
+
+using namespace t0b;
+
+namespace {
+
+constexpr int kRowThreads = 512;
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Block-wide sum of up to two values; every thread receives the totals.  `red` holds 2 * 32 floats.
+__device__ __forceinline__ void block_sum2(float& a, float& b, float* red) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    a = warp_sum(a);
+    b = warp_sum(b);
+    __syncthreads();   // protect `red` against the previous use
+    if (lane == 0) { red[warp] = a; red[32 + warp] = b; }
+    __syncthreads();
+    float x = lane < nwarps ? red[lane] : 0.0f;
+    float y = lane < nwarps ? red[32 + lane] : 0.0f;
+    a = warp_sum(x);
+    b = warp_sum(y);
+}
+
+// Online softmax statistics (running max m, running sum s of exp(x - m)).
+__device__ __forceinline__ void online_add(float& m, float& s, float x) {
+    if (x > m) { s = s * expf(m - x) + 1.0f; m = x; }
+    else s += expf(x - m);
+}
+__device__ __forceinline__ void online_merge(float& m, float& s, float m2, float s2) {
+    const float mm = fmaxf(m, m2);
+    const float a = (m == -INFINITY) ? 0.0f : s * expf(m - mm);
+    const float b = (m2 == -INFINITY) ? 0.0f : s2 * expf(m2 - mm);
+    m = mm;
+    s = a + b;
+}
+__device__ __forceinline__ void block_online(float& m, float& s, float* red) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float m2 = __shfl_xor_sync(0xffffffffu, m, o), s2 = __shfl_xor_sync(0xffffffffu, s, o);
+        online_merge(m, s, m2, s2);
+    }
+    __syncthreads();
+    if (lane == 0) { red[warp] = m; red[32 + warp] = s; }
+    __syncthreads();
+    m = lane < nwarps ? red[lane] : -INFINITY;
+    s = lane < nwarps ? red[32 + lane] : 0.0f;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float m2 = __shfl_xor_sync(0xffffffffu, m, o), s2 = __shfl_xor_sync(0xffffffffu, s, o);
+        online_merge(m, s, m2, s2);
+    }
+}
+
+// ------------------------------------------------------------------------------------------------ casts
+
+__global__ void __launch_bounds__(256) cast_f32_bf16_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst,
+                                                            size_t n) {
+    const size_t n4 = n / 4;
+    const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+    const bool vec = ((reinterpret_cast<uintptr_t>(src) & 15) == 0) && ((reinterpret_cast<uintptr_t>(dst) & 7) == 0);
+    size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x;
+    if (vec) {
+        for (size_t j = i; j < n4; j += stride) {
+            const float4 v = reinterpret_cast<const float4*>(src)[j];
+            __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+            uint2 o;
+            o.x = *reinterpret_cast<uint32_t*>(&lo);
+            o.y = *reinterpret_cast<uint32_t*>(&hi);
+            reinterpret_cast<uint2*>(dst)[j] = o;
+        }
+        for (size_t j = n4 * 4 + i; j < n; j += stride) dst[j] = __float2bfloat16_rn(src[j]);
+    } else {
+        for (size_t j = i; j < n; j += stride) dst[j] = __float2bfloat16_rn(src[j]);
+    }
+}
+
+// src f32 [rows, cols] -> dst bf16 [cols, rows]; 32x32 tiles through shared memory, both sides coalesced.
+__global__ void __launch_bounds__(256) cast_transpose_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst,
+                                                             uint32_t rows, uint32_t cols) {
+    __shared__ float tile[32][33];
+    const uint32_t c0 = blockIdx.x * 32, r0 = blockIdx.y * 32;
+    const uint32_t tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+    for (uint32_t j = ty; j < 32; j += 8) {
+        const uint32_t r = r0 + j, c = c0 + tx;
+        tile[j][tx] = (r < rows && c < cols) ? src[static_cast<size_t>(r) * cols + c] : 0.0f;
+    }
+    __syncthreads();
+    for (uint32_t j = ty; j < 32; j += 8) {
+        const uint32_t c = c0 + j, r = r0 + tx;
+        if (r < rows && c < cols) dst[static_cast<size_t>(c) * rows + r] = __float2bfloat16_rn(tile[tx][j]);
+    }
+}
+
+// ------------------------------------------------------------------------------------------------ RMSNorm
+
+// One block per row.  The row is read once from HBM (second sweep hits L1/L2: a row is at most tens of KB).
+__global__ void __launch_bounds__(kRowThreads) rmsnorm_fwd_kernel(const float* __restrict__ x, const float* __restrict__ w,
+                                                                  float* __restrict__ y, float* __restrict__ inv_rms,
+                                                                  uint32_t cols, float eps) {
+    __shared__ float red[64];
+    const size_t row = blockIdx.x;
+    const float* xr = x + row * cols;
+    float* yr = y + row * cols;
+    const bool vec = (cols % 4 == 0) && ((reinterpret_cast<uintptr_t>(x) & 15) == 0) &&
+                     ((reinterpret_cast<uintptr_t>(y) & 15) == 0) && ((reinterpret_cast<uintptr_t>(w) & 15) == 0);
+    float ss = 0.0f, unused = 0.0f;
+    if (vec) {
+        for (uint32_t i = threadIdx.x; i < cols / 4; i += blockDim.x) {
+            const float4 v = reinterpret_cast<const float4*>(xr)[i];
+            ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+        }
+    } else {
+        for (uint32_t i = threadIdx.x; i < cols; i += blockDim.x) ss += xr[i] * xr[i];
+    }
+    block_sum2(ss, unused, red);
+    const float rstd = 1.0f / sqrtf(ss / static_cast<float>(cols) + eps);
+    if (threadIdx.x == 0 && inv_rms) inv_rms[row] = rstd;
+    if (vec) {
+        for (uint32_t i = threadIdx.x; i < cols / 4; i += blockDim.x) {
+            const float4 v = reinterpret_cast<const float4*>(xr)[i];
+            const float4 g = reinterpret_cast<const float4*>(w)[i];
+            reinterpret_cast<float4*>(yr)[i] = make_float4(v.x * rstd * g.x, v.y * rstd * g.y, v.z * rstd * g.z, v.w * rstd * g.w);
+        }
+    } else {
+        for (uint32_t i = threadIdx.x; i < cols; i += blockDim.x) yr[i] = xr[i] * rstd * w[i];
+    }
+}
+
+// dx = rstd * (dy*w - x * rstd^2 * mean(x * dy*w)); also stores rstd per row for the dgamma stage.
+__global__ void __launch_bounds__(kRowThreads) rmsnorm_bwd_dx_kernel(const float* __restrict__ dy, const float* __restrict__ x,
+                                                                     const float* __restrict__ w, float* __restrict__ dx,
+                                                                     float* __restrict__ inv_rms, uint32_t cols, float eps) {
+    __shared__ float red[64];
+    const size_t row = blockIdx.x;
+    const float* xr = x + row * cols;
+    const float* dyr = dy + row * cols;
+    float* dxr = dx ? dx + row * cols : nullptr;
+    const bool vec = (cols % 4 == 0) && ((reinterpret_cast<uintptr_t>(x) & 15) == 0) &&
+                     ((reinterpret_cast<uintptr_t>(dy) & 15) == 0) && ((reinterpret_cast<uintptr_t>(w) & 15) == 0) &&
+                     ((reinterpret_cast<uintptr_t>(dx) & 15) == 0);
+    float ss = 0.0f, dot = 0.0f;
+    if (vec) {
+        for (uint32_t i = threadIdx.x; i < cols / 4; i += blockDim.x) {
+            const float4 v = reinterpret_cast<const float4*>(xr)[i];
+            const float4 d = reinterpret_cast<const float4*>(dyr)[i];
+            const float4 g = reinterpret_cast<const float4*>(w)[i];
+            ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+            dot += v.x * d.x * g.x + v.y * d.y * g.y + v.z * d.z * g.z + v.w * d.w * g.w;
+        }
+    } else {
+        for (uint32_t i = threadIdx.x; i < cols; i += blockDim.x) {
+            ss += xr[i] * xr[i];
+            dot += xr[i] * dyr[i] * w[i];
+        }
+    }
+    block_sum2(ss, dot, red);
+    const float rstd = 1.0f / sqrtf(ss / static_cast<float>(cols) + eps);
+    const float coef = rstd * rstd * (dot / static_cast<float>(cols));
+    if (threadIdx.x == 0 && inv_rms) inv_rms[row] = rstd;
+    if (!dxr) return;
+    if (vec) {
+        for (uint32_t i = threadIdx.x; i < cols / 4; i += blockDim.x) {
+            const float4 v = reinterpret_cast<const float4*>(xr)[i];
+            const float4 d = reinterpret_cast<const float4*>(dyr)[i];
+            const float4 g = reinterpret_cast<const float4*>(w)[i];
+            reinterpret_cast<float4*>(dxr)[i] =
+                make_float4(rstd * (d.x * g.x - v.x * coef), rstd * (d.y * g.y - v.y * coef),
+                            rstd * (d.z * g.z - v.z * coef), rstd * (d.w * g.w - v.w * coef));
+        }
+    } else {
+        for (uint32_t i = threadIdx.x; i < cols; i += blockDim.x) dxr[i] = rstd * (dyr[i] * w[i] - xr[i] * coef);
+    }
+}
+
+// dgamma stage 1: block (cb, rb) sums dy*x*inv_rms over its row range, rows ascending, one column per thread.
+__global__ void __launch_bounds__(256) rmsnorm_dgamma_partial_kernel(const float* __restrict__ dy, const float* __restrict__ x,
+                                                                     const float* __restrict__ inv_rms,
+                                                                     float* __restrict__ partial, uint32_t rows,
+                                                                     uint32_t cols, uint32_t rows_per_block) {
+    const uint32_t c = blockIdx.x * 256 + threadIdx.x;
+    const uint32_t r0 = blockIdx.y * rows_per_block;
+    const uint32_t r1 = min(rows, r0 + rows_per_block);
+    if (c >= cols) return;
+    float acc = 0.0f;
+    for (uint32_t r = r0; r < r1; ++r) {
+        const size_t i = static_cast<size_t>(r) * cols + c;
+        acc += dy[i] * x[i] * inv_rms[r];
+    }
+    partial[static_cast<size_t>(blockIdx.y) * cols + c] = acc;
+}
+// dgamma stage 2: sum the row-block partials in block order.
+__global__ void __launch_bounds__(256) rmsnorm_dgamma_final_kernel(const float* __restrict__ partial, float* __restrict__ dgamma,
+                                                                   uint32_t cols, uint32_t nblocks) {
+    const uint32_t c = blockIdx.x * 256 + threadIdx.x;
+    if (c >= cols) return;
+    float acc = 0.0f;
+    for (uint32_t b = 0; b < nblocks; ++b) acc += partial[static_cast<size_t>(b) * cols + c];
+    dgamma[c] = acc;
+}
+
+constexpr uint32_t kDgammaRowBlocks = 64;
+
+// ------------------------------------------------------------------------------------------------ softmax / CE
+
+// Row statistics with the row cached in shared memory when it fits (one HBM read), else re-read.
+template <bool CACHE>
+__device__ __forceinline__ void row_stats(const float* __restrict__ xr, uint32_t cols, float* cache, float* red, float& m,
+                                          float& s) {
+    m = -INFINITY;
+    s = 0.0f;
+    const bool vec = (cols % 4 == 0) && ((reinterpret_cast<uintptr_t>(xr) & 15) == 0);
+    if (vec) {
+        for (uint32_t i = threadIdx.x; i < cols / 4; i += blockDim.x) {
+            const float4 v = reinterpret_cast<const float4*>(xr)[i];
+            if (CACHE) reinterpret_cast<float4*>(cache)[i] = v;
+            const float lm = fmaxf(fmaxf(v.x, v.y), fmaxf(v.z, v.w));
+            if (lm > m) { s *= expf(m - lm); m = lm; }
+            s += expf(v.x - m) + expf(v.y - m) + expf(v.z - m) + expf(v.w - m);
+        }
+    } else {
+        for (uint32_t i = threadIdx.x; i < cols; i += blockDim.x) {
+            const float v = xr[i];
+            if (CACHE) cache[i] = v;
+            online_add(m, s, v);
+        }
+    }
+    block_online(m, s, red);
+}
+
+template <bool CACHE>
+__global__ void __launch_bounds__(kRowThreads) softmax_fwd_kernel(const float* __restrict__ x, float* __restrict__ y,
+                                                                  uint32_t cols) {
+    extern __shared__ __align__(16) float cache[];
+    __shared__ float red[64];
+    const size_t row = blockIdx.x;
+    const float* xr = x + row * cols;
+    float* yr = y + row * cols;
+    float m, s;
+    row_stats<CACHE>(xr, cols, cache, red, m, s);
+    const float inv = 1.0f / s;
+    const float* src = CACHE ? cache : xr;
+    const bool vec = (cols % 4 == 0) && ((reinterpret_cast<uintptr_t>(xr) & 15) == 0) && ((reinterpret_cast<uintptr_t>(yr) & 15) == 0);
+    if (vec) {
+        for (uint32_t i = threadIdx.x; i < cols / 4; i += blockDim.x) {
+            const float4 v = reinterpret_cast<const float4*>(src)[i];
+            reinterpret_cast<float4*>(yr)[i] = make_float4(expf(v.x - m) * inv, expf(v.y - m) * inv, expf(v.z - m) * inv, expf(v.w - m) * inv);
+        }
+    } else {
+        for (uint32_t i = threadIdx.x; i < cols; i += blockDim.x) yr[i] = expf(src[i] - m) * inv;
+    }
+}
+
+__global__ void __launch_bounds__(kRowThreads) softmax_bwd_kernel(const float* __restrict__ dy, const float* __restrict__ y,
+                                                                  float* __restrict__ dx, uint32_t cols) {
+    __shared__ float red[64];
+    const size_t row = blockIdx.x;
+    const float* dyr = dy + row * cols;
+    const float* yr = y + row * cols;
+    float* dxr = dx + row * cols;
+    float dot = 0.0f, unused = 0.0f;
+    for (uint32_t i = threadIdx.x; i < cols; i += blockDim.x) dot += dyr[i] * yr[i];
+    block_sum2(dot, unused, red);
+    for (uint32_t i = threadIdx.x; i < cols; i += blockDim.x) dxr[i] = yr[i] * (dyr[i] - dot);
+}
+
+// Fused softmax cross-entropy over one row per block: loss = log(sum exp(x - max)) + max - x[target];
+// dlogits = (exp(x - max) / sum - onehot) * scale.
+template <bool CACHE>
+__global__ void __launch_bounds__(kRowThreads) softmax_ce_kernel(const float* __restrict__ logits,
+                                                                 const uint32_t* __restrict__ targets,
+                                                                 float* __restrict__ losses, float* __restrict__ dlogits,
+                                                                 uint32_t cols, size_t ld, float scale) {
+    extern __shared__ __align__(16) float cache[];
+    __shared__ float red[64];
+    const size_t row = blockIdx.x;
+    const float* xr = logits + row * ld;
+    float m, s;
+    row_stats<CACHE>(xr, cols, cache, red, m, s);
+    const uint32_t t = targets[row];
+    if (threadIdx.x == 0 && losses) losses[row] = (t < cols) ? (logf(s) + m - xr[t]) : 0.0f;
+    if (!dlogits) return;
+    float* dr = dlogits + row * ld;
+    const float inv = 1.0f / s;
+    const float* src = CACHE ? cache : xr;
+    const bool vec = (cols % 4 == 0) && ((reinterpret_cast<uintptr_t>(xr) & 15) == 0) && ((reinterpret_cast<uintptr_t>(dr) & 15) == 0);
+    if (vec) {
+        for (uint32_t i = threadIdx.x; i < cols / 4; i += blockDim.x) {
+            const float4 v = reinterpret_cast<const float4*>(src)[i];
+            float4 o = make_float4(expf(v.x - m) * inv, expf(v.y - m) * inv, expf(v.z - m) * inv, expf(v.w - m) * inv);
+            const uint32_t c = i * 4;
+            if (t - c < 4u) {
+                if (t == c) o.x -= 1.0f;
+                else if (t == c + 1) o.y -= 1.0f;
+                else if (t == c + 2) o.z -= 1.0f;
+                else o.w -= 1.0f;
+            }
+            reinterpret_cast<float4*>(dr)[i] = make_float4(o.x * scale, o.y * scale, o.z * scale, o.w * scale);
+        }
+    } else {
+        for (uint32_t i = threadIdx.x; i < cols; i += blockDim.x)
+            dr[i] = (expf(src[i] - m) * inv - (i == t ? 1.0f : 0.0f)) * scale;
+    }
+}
+
+// ------------------------------------------------------------------------------------------------ element-wise
+
+__global__ void __launch_bounds__(256) silu_gate_fwd_kernel(const float* __restrict__ gate, const float* __restrict__ up,
+                                                            float* __restrict__ out, size_t n) {
+    const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < n; i += stride) {
+        const float g = gate[i];
+        const float sig = 1.0f / (1.0f + expf(-g));
+        out[i] = g * sig * (up ? up[i] : 1.0f);
+    }
+}
+
+__global__ void __launch_bounds__(256) silu_gate_bwd_kernel(const float* __restrict__ grad, const float* __restrict__ gate,
+                                                            const float* __restrict__ up, float* __restrict__ dgate,
+                                                            float* __restrict__ dup, size_t n) {
+    const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < n; i += stride) {
+        const float g = gate[i], gr = grad[i], u = up ? up[i] : 1.0f;
+        const float sig = 1.0f / (1.0f + expf(-g));
+        if (dup) dup[i] = gr * g * sig;
+        dgate[i] = gr * u * sig * (1.0f + g * (1.0f - sig));
+    }
+}
+
+__global__ void __launch_bounds__(256) residual_add_kernel(float* __restrict__ y, const float* __restrict__ x, size_t n) {
+    const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+    const bool vec = ((reinterpret_cast<uintptr_t>(y) & 15) == 0) && ((reinterpret_cast<uintptr_t>(x) & 15) == 0);
+    const size_t i0 = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x;
+    if (vec) {
+        const size_t n4 = n / 4;
+        for (size_t i = i0; i < n4; i += stride) {
+            float4 a = reinterpret_cast<float4*>(y)[i];
+            const float4 b = reinterpret_cast<const float4*>(x)[i];
+            a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
+            reinterpret_cast<float4*>(y)[i] = a;
+        }
+        for (size_t i = n4 * 4 + i0; i < n; i += stride) y[i] += x[i];
+    } else {
+        for (size_t i = i0; i < n; i += stride) y[i] += x[i];
+    }
+}
+
+__global__ void __launch_bounds__(256) adamw_kernel(float* __restrict__ p, const float* __restrict__ g, float* __restrict__ m,
+                                                    float* __restrict__ v, __nv_bfloat16* __restrict__ p_bf16, size_t n,
+                                                    float lr, float beta1, float beta2, float eps, float wd, float bc1,
+                                                    float bc2, float grad_scale) {
+    const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < n; i += stride) {
+        const float gi = g[i] * grad_scale;
+        const float mi = beta1 * m[i] + (1.0f - beta1) * gi;
+        const float vi = beta2 * v[i] + (1.0f - beta2) * gi * gi;
+        m[i] = mi;
+        v[i] = vi;
+        const float pn = p[i] * (1.0f - lr * wd) - lr * (mi * bc1) / (sqrtf(vi * bc2) + eps);
+        p[i] = pn;
+        if (p_bf16) p_bf16[i] = __float2bfloat16_rn(pn);
+    }
+}
+
+int grid_for(t0b_ctx* ctx, size_t n, int per_block) {
+    const size_t blocks = (n + per_block - 1) / per_block;
+    return static_cast<int>(std::max<size_t>(1, std::min<size_t>(blocks, static_cast<size_t>(ctx->num_sms) * 16)));
+}
+
+constexpr size_t kRowCacheMax = 200 * 1024;
+
+}  // namespace
+
+extern "C" {
+
+int32_t t0b_cast_f32_to_bf16(t0b_ctx* ctx, uint64_t src, uint64_t dst, size_t n, int32_t async) {
+    int32_t rc = precheck(ctx);
+    if (rc != T0B_OK) return rc;
+    if (n == 0) return T0B_OK;
+    if (!src || !dst) return set_error(ctx, T0B_ERR_INVALID, "cast: null pointer");
+    cast_f32_bf16_kernel<<<grid_for(ctx, n / 4 + 1, 256), 256, 0, ctx->stream>>>(reinterpret_cast<const float*>(src),
+                                                                              reinterpret_cast<__nv_bfloat16*>(dst), n);
+    return finish(ctx, async, "cast_f32_to_bf16");
+}
+
+int32_t t0b_cast_f32_to_bf16_transpose(t0b_ctx* ctx, uint64_t src, uint64_t dst, uint32_t rows, uint32_t cols,
+                                       int32_t async) {
+    int32_t rc = precheck(ctx);
+    if (rc != T0B_OK) return rc;
+    if (rows == 0 || cols == 0) return T0B_OK;
+    if (!src || !dst) return set_error(ctx, T0B_ERR_INVALID, "cast_transpose: null pointer");
+    dim3 grid((cols + 31) / 32, (rows + 31) / 32);
+    if (grid.y > 65535) return set_error(ctx, T0B_ERR_INVALID, "cast_transpose: too many rows (%u)", rows);
+    cast_transpose_kernel<<<grid, 256, 0, ctx->stream>>>(reinterpret_cast<const float*>(src),
+                                                         reinterpret_cast<__nv_bfloat16*>(dst), rows, cols);
+    return finish(ctx, async, "cast_f32_to_bf16_transpose");
+}
+
+int32_t t0b_rmsnorm_fwd(t0b_ctx* ctx, uint64_t x, uint64_t weight, uint64_t y, uint64_t inv_rms, uint32_t rows,
+                        uint32_t cols, float eps, int32_t async) {
+    int32_t rc = precheck(ctx);
+    if (rc != T0B_OK) return rc;
+    if (rows == 0) return T0B_OK;
+    if (cols == 0 || !x || !weight || !y) return set_error(ctx, T0B_ERR_INVALID, "rmsnorm_fwd: null pointer or zero cols");
+    const int threads = cols >= 2048 ? kRowThreads : (cols >= 512 ? 128 : 32);
+    rmsnorm_fwd_kernel<<<rows, threads, 0, ctx->stream>>>(reinterpret_cast<const float*>(x), reinterpret_cast<const float*>(weight),
+                                                          reinterpret_cast<float*>(y), reinterpret_cast<float*>(inv_rms), cols, eps);
+    return finish(ctx, async, "rmsnorm_fwd");
+}
+
+size_t t0b_rmsnorm_bwd_scratch_bytes(uint32_t rows, uint32_t cols) {
+    return (static_cast<size_t>(rows) + static_cast<size_t>(kDgammaRowBlocks) * cols) * sizeof(float);
+}
+
+int32_t t0b_rmsnorm_bwd(t0b_ctx* ctx, uint64_t dy, uint64_t x, uint64_t weight, uint64_t dx, uint64_t dgamma,
+                        uint64_t scratch, size_t scratch_bytes, uint32_t rows, uint32_t cols, float eps, int32_t async) {
+    int32_t rc = precheck(ctx);
+    if (rc != T0B_OK) return rc;
+    if (rows == 0) {
+        if (dgamma && cols) return t0b_memset0(ctx, dgamma, static_cast<size_t>(cols) * 4);
+        return T0B_OK;
+    }
+    if (cols == 0 || !dy || !x || !weight || (!dx && !dgamma)) return set_error(ctx, T0B_ERR_INVALID, "rmsnorm_bwd: null pointer or zero cols");
+    float* inv = nullptr;
+    float* partial = nullptr;
+    if (dgamma) {
+        if (!scratch || scratch_bytes < t0b_rmsnorm_bwd_scratch_bytes(rows, cols))
+            return set_error(ctx, T0B_ERR_INVALID, "rmsnorm_bwd: dgamma needs %zu bytes of scratch, got %zu",
+                             t0b_rmsnorm_bwd_scratch_bytes(rows, cols), scratch_bytes);
+        inv = reinterpret_cast<float*>(scratch);
+        partial = inv + rows;
+    }
+    const int threads = cols >= 2048 ? kRowThreads : (cols >= 512 ? 128 : 32);
+    rmsnorm_bwd_dx_kernel<<<rows, threads, 0, ctx->stream>>>(reinterpret_cast<const float*>(dy), reinterpret_cast<const float*>(x),
+                                                             reinterpret_cast<const float*>(weight), reinterpret_cast<float*>(dx),
+                                                             inv, cols, eps);
+    rc = check_cuda(ctx, cudaGetLastError(), "rmsnorm_bwd_dx launch");
+    if (rc != T0B_OK) return rc;
+    if (dgamma) {
+        ++ctx->launches;
+        const uint32_t nblocks = std::min(kDgammaRowBlocks, rows);
+        const uint32_t rpb = (rows + nblocks - 1) / nblocks;
+        const uint32_t used = (rows + rpb - 1) / rpb;
+        dim3 grid((cols + 255) / 256, used);
+        rmsnorm_dgamma_partial_kernel<<<grid, 256, 0, ctx->stream>>>(reinterpret_cast<const float*>(dy), reinterpret_cast<const float*>(x),
+                                                                     inv, partial, rows, cols, rpb);
+        rc = check_cuda(ctx, cudaGetLastError(), "rmsnorm_dgamma_partial launch");
+        if (rc != T0B_OK) return rc;
+        ++ctx->launches;
+        rmsnorm_dgamma_final_kernel<<<(cols + 255) / 256, 256, 0, ctx->stream>>>(partial, reinterpret_cast<float*>(dgamma), cols, used);
+    }
+    return finish(ctx, async, "rmsnorm_bwd");
+}
+
+int32_t t0b_softmax_fwd(t0b_ctx* ctx, uint64_t x, uint64_t y, uint32_t rows, uint32_t cols, int32_t async) {
+    int32_t rc = precheck(ctx);
+    if (rc != T0B_OK) return rc;
+    if (rows == 0) return T0B_OK;
+    if (cols == 0 || !x || !y) return set_error(ctx, T0B_ERR_INVALID, "softmax_fwd: null pointer or zero cols");
+    const int threads = cols >= 2048 ? kRowThreads : (cols >= 512 ? 128 : 32);
+    const size_t bytes = static_cast<size_t>(cols) * 4;
+    if (bytes <= kRowCacheMax && cols >= 2048) {
+        static bool set[64] = {};
+        if (!set[ctx->device & 63]) {
+            rc = check_cuda(ctx, cudaFuncSetAttribute(softmax_fwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                      static_cast<int>(kRowCacheMax)), "cudaFuncSetAttribute(softmax)");
+            if (rc != T0B_OK) return rc;
+            set[ctx->device & 63] = true;
+        }
+        softmax_fwd_kernel<true><<<rows, threads, bytes, ctx->stream>>>(reinterpret_cast<const float*>(x), reinterpret_cast<float*>(y), cols);
+    } else {
+        softmax_fwd_kernel<false><<<rows, threads, 0, ctx->stream>>>(reinterpret_cast<const float*>(x), reinterpret_cast<float*>(y), cols);
+    }
+    return finish(ctx, async, "softmax_fwd");
+}
+
+int32_t t0b_softmax_bwd(t0b_ctx* ctx, uint64_t dy, uint64_t y, uint64_t dx, uint32_t rows, uint32_t cols, int32_t async) {
+    int32_t rc = precheck(ctx);
+    if (rc != T0B_OK) return rc;
+    if (rows == 0) return T0B_OK;
+    if (cols == 0 || !dy || !y || !dx) return set_error(ctx, T0B_ERR_INVALID, "softmax_bwd: null pointer or zero cols");
+    const int threads = cols >= 2048 ? kRowThreads : (cols >= 512 ? 128 : 32);
+    softmax_bwd_kernel<<<rows, threads, 0, ctx->stream>>>(reinterpret_cast<const float*>(dy), reinterpret_cast<const float*>(y),
+                                                          reinterpret_cast<float*>(dx), cols);
+    return finish(ctx, async, "softmax_bwd");
+}
+
+int32_t t0b_softmax_ce(t0b_ctx* ctx, uint64_t logits, uint64_t targets, uint64_t losses, uint64_t dlogits, uint32_t rows,
+                       uint32_t cols, uint64_t ld, float scale, int32_t async) {
+    int32_t rc = precheck(ctx);
+    if (rc != T0B_OK) return rc;
+    if (rows == 0) return T0B_OK;
+    if (cols == 0 || !logits || !targets || (!losses && !dlogits) || ld < cols)
+        return set_error(ctx, T0B_ERR_INVALID, "softmax_ce: null pointer, zero cols or pitch < cols");
+    const int threads = cols >= 2048 ? kRowThreads : (cols >= 512 ? 128 : 32);
+    const size_t bytes = static_cast<size_t>(cols) * 4;
+    if (bytes <= kRowCacheMax && cols >= 2048) {
+        static bool set[64] = {};
+        if (!set[ctx->device & 63]) {
+            rc = check_cuda(ctx, cudaFuncSetAttribute(softmax_ce_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                      static_cast<int>(kRowCacheMax)), "cudaFuncSetAttribute(softmax_ce)");
+            if (rc != T0B_OK) return rc;
+            set[ctx->device & 63] = true;
+        }
+        softmax_ce_kernel<true><<<rows, threads, bytes, ctx->stream>>>(reinterpret_cast<const float*>(logits),
+                                                                       reinterpret_cast<const uint32_t*>(targets),
+                                                                       reinterpret_cast<float*>(losses), reinterpret_cast<float*>(dlogits),
+                                                                       cols, ld, scale);
+    } else {
+        softmax_ce_kernel<false><<<rows, threads, 0, ctx->stream>>>(reinterpret_cast<const float*>(logits),
+                                                                    reinterpret_cast<const uint32_t*>(targets),
+                                                                    reinterpret_cast<float*>(losses), reinterpret_cast<float*>(dlogits),
+                                                                    cols, ld, scale);
+    }
+    return finish(ctx, async, "softmax_ce");
+}
+
+int32_t t0b_silu_gate_fwd(t0b_ctx* ctx, uint64_t gate, uint64_t up, uint64_t out, size_t n, int32_t async) {
+    int32_t rc = precheck(ctx);
+    if (rc != T0B_OK) return rc;
+    if (n == 0) return T0B_OK;
+    if (!gate || !out) return set_error(ctx, T0B_ERR_INVALID, "silu_gate_fwd: null pointer");
+    silu_gate_fwd_kernel<<<grid_for(ctx, n, 1024), 256, 0, ctx->stream>>>(reinterpret_cast<const float*>(gate), reinterpret_cast<const float*>(up),
+                                                                         reinterpret_cast<float*>(out), n);
+    return finish(ctx, async, "silu_gate_fwd");
+}
+
+int32_t t0b_silu_gate_bwd(t0b_ctx* ctx, uint64_t grad, uint64_t gate, uint64_t up, uint64_t dgate, uint64_t dup, size_t n,
+                          int32_t async) {
+    int32_t rc = precheck(ctx);
+    if (rc != T0B_OK) return rc;
+    if (n == 0) return T0B_OK;
+    if (!grad || !gate || !dgate) return set_error(ctx, T0B_ERR_INVALID, "silu_gate_bwd: null pointer");
+    silu_gate_bwd_kernel<<<grid_for(ctx, n, 1024), 256, 0, ctx->stream>>>(reinterpret_cast<const float*>(grad), reinterpret_cast<const float*>(gate),
+                                                                         reinterpret_cast<const float*>(up), reinterpret_cast<float*>(dgate),
+                                                                         reinterpret_cast<float*>(dup), n);
+    return finish(ctx, async, "silu_gate_bwd");
+}
+
+int32_t t0b_residual_add(t0b_ctx* ctx, uint64_t y, uint64_t x, size_t n, int32_t async) {
+    int32_t rc = precheck(ctx);
+    if (rc != T0B_OK) return rc;
+    if (n == 0) return T0B_OK;
+    if (!x || !y) return set_error(ctx, T0B_ERR_INVALID, "residual_add: null pointer");
+    residual_add_kernel<<<grid_for(ctx, n / 4 + 1, 256), 256, 0, ctx->stream>>>(reinterpret_cast<float*>(y), reinterpret_cast<const float*>(x), n);
+    return finish(ctx, async, "residual_add");
+}
+
+int32_t t0b_adamw_step(t0b_ctx* ctx, uint64_t params, uint64_t grads, uint64_t m, uint64_t v, uint64_t params_bf16, size_t n,
+                       float lr, float beta1, float beta2, float eps, float weight_decay, uint32_t t, float grad_scale,
+                       int32_t async) {
+    int32_t rc = precheck(ctx);
+    if (rc != T0B_OK) return rc;
+    if (n == 0) return T0B_OK;
+    if (!params || !grads || !m || !v || t == 0) return set_error(ctx, T0B_ERR_INVALID, "adamw_step: null pointer or t == 0");
+    const float bc1 = 1.0f / (1.0f - powf(beta1, static_cast<float>(t)));
+    const float bc2 = 1.0f / (1.0f - powf(beta2, static_cast<float>(t)));
+    adamw_kernel<<<grid_for(ctx, n, 1024), 256, 0, ctx->stream>>>(reinterpret_cast<float*>(params), reinterpret_cast<const float*>(grads),
+                                                                 reinterpret_cast<float*>(m), reinterpret_cast<float*>(v),
+                                                                 reinterpret_cast<__nv_bfloat16*>(params_bf16), n, lr, beta1, beta2, eps,
+                                                                 weight_decay, bc1, bc2, grad_scale);
+    return finish(ctx, async, "adamw_step");
+}
+
+}  // extern "C"

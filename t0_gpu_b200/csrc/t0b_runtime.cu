@@ -1,0 +1,310 @@
+// Runtime of libt0b200.so: context, stream, buffer pool, copies, status word, CUDA graphs.
+// Stands where the reference has GpuRuntime + BufferPool (src/ignis/gpu_context.rs:30-106, 113-483) on top of
+// the KFD queue/VRAM layer (src/kfd/mod.rs): a CUDA stream replaces the AQL queue and doorbell, cudaMalloc
+// the VRAM mmap, a mapped status word the queue-timeout detection.
+#include <cstring>
+
+#include "t0b_internal.hpp"
+
+namespace t0b {
+
+int32_t set_error(t0b_ctx* ctx, int32_t code, const char* fmt, ...) {
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof(buf), fmt, ap);
+    va_end(ap);
+    if (ctx) {
+        std::lock_guard<std::recursive_mutex> lk(ctx->mu);
+        ctx->last_error = buf;
+        if (code == T0B_ERR_CUDA) ctx->poisoned = true;
+    }
+    return code;
+}
+
+int32_t check_cuda(t0b_ctx* ctx, cudaError_t e, const char* what) {
+    if (e == cudaSuccess) return T0B_OK;
+    return set_error(ctx, T0B_ERR_CUDA, "%s: %s (%s)", what, cudaGetErrorString(e), cudaGetErrorName(e));
+}
+
+int32_t precheck(t0b_ctx* ctx) {
+    if (!ctx) return T0B_ERR_INVALID;
+    if (ctx->poisoned) {
+        // Keep the message of the error that poisoned the context.
+        return T0B_ERR_POISONED;
+    }
+    cudaError_t e = cudaSetDevice(ctx->device);
+    if (e != cudaSuccess) return check_cuda(ctx, e, "cudaSetDevice");
+    return T0B_OK;
+}
+
+int32_t finish(t0b_ctx* ctx, int32_t async, const char* what) {
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return check_cuda(ctx, e, what);
+    ++ctx->launches;
+    if (async || ctx->capturing) return T0B_OK;
+    e = cudaStreamSynchronize(ctx->stream);
+    if (e != cudaSuccess) return check_cuda(ctx, e, what);
+    const int st = *reinterpret_cast<volatile int*>(ctx->status_host);
+    if (st != 0) return set_error(ctx, T0B_ERR_DEVICE, "%s: device status %d (a bounded in-kernel wait ran out)", what, st);
+    return T0B_OK;
+}
+
+}  // namespace t0b
+
+using namespace t0b;
+
+static size_t round4k(size_t b) { return (b + 4095) & ~static_cast<size_t>(4095); }
+
+extern "C" {
+
+int32_t t0b_ctx_create(int32_t device, t0b_ctx** out) {
+    if (!out) return T0B_ERR_INVALID;
+    *out = nullptr;
+    int count = 0;
+    cudaError_t e = cudaGetDeviceCount(&count);
+    if (e != cudaSuccess || count <= 0 || device < 0 || device >= count) {
+        cudaGetLastError();
+        return T0B_ERR_CUDA;   // no CPU fallback: without a usable CUDA device there is no context
+    }
+    t0b_ctx* ctx = new t0b_ctx();
+    ctx->device = device;
+    int32_t rc = check_cuda(ctx, cudaSetDevice(device), "cudaSetDevice");
+    cudaDeviceProp prop{};
+    if (rc == T0B_OK) rc = check_cuda(ctx, cudaGetDeviceProperties(&prop, device), "cudaGetDeviceProperties");
+    if (rc == T0B_OK && prop.major != 10) {
+        rc = set_error(ctx, T0B_ERR_UNSUPPORTED, "device %d is sm_%d%d; this library is built for sm_100a only", device,
+                       prop.major, prop.minor);
+    }
+    if (rc == T0B_OK) {
+        ctx->num_sms = prop.multiProcessorCount;
+        rc = check_cuda(ctx, cudaStreamCreateWithFlags(&ctx->own_stream, cudaStreamNonBlocking), "cudaStreamCreate");
+        ctx->stream = ctx->own_stream;
+    }
+    if (rc == T0B_OK) {
+        rc = check_cuda(ctx, cudaHostAlloc(reinterpret_cast<void**>(&ctx->status_host), 64, cudaHostAllocMapped),
+                        "cudaHostAlloc(status)");
+        if (rc == T0B_OK) {
+            std::memset(ctx->status_host, 0, 64);
+            rc = check_cuda(ctx, cudaHostGetDevicePointer(reinterpret_cast<void**>(&ctx->status_dev), ctx->status_host, 0),
+                            "cudaHostGetDevicePointer");
+        }
+    }
+    if (rc != T0B_OK) {
+        t0b_ctx_destroy(ctx);
+        return rc;
+    }
+    *out = ctx;
+    return T0B_OK;
+}
+
+void t0b_ctx_destroy(t0b_ctx* ctx) {
+    if (!ctx) return;
+    cudaSetDevice(ctx->device);
+    if (ctx->own_stream) cudaStreamSynchronize(ctx->own_stream);
+    for (auto& g : ctx->graphs) cudaGraphExecDestroy(g.second);
+    for (auto& kv : ctx->pool_free) cudaFree(kv.second);
+    for (auto& kv : ctx->live) cudaFree(kv.first);
+    if (ctx->ws) cudaFree(ctx->ws);
+    if (ctx->status_host) cudaFreeHost(ctx->status_host);
+    if (ctx->own_stream) cudaStreamDestroy(ctx->own_stream);
+    delete ctx;
+}
+
+int32_t t0b_ctx_set_stream(t0b_ctx* ctx, void* s) {
+    if (!ctx) return T0B_ERR_INVALID;
+    std::lock_guard<std::recursive_mutex> lk(ctx->mu);
+    ctx->stream = s ? static_cast<cudaStream_t>(s) : ctx->own_stream;
+    return T0B_OK;
+}
+
+void* t0b_ctx_stream(t0b_ctx* ctx) { return ctx ? static_cast<void*>(ctx->stream) : nullptr; }
+
+const char* t0b_last_error(t0b_ctx* ctx) { return ctx ? ctx->last_error.c_str() : "null context"; }
+
+int32_t t0b_is_poisoned(t0b_ctx* ctx) { return ctx && ctx->poisoned ? 1 : 0; }
+
+int32_t t0b_num_sms(t0b_ctx* ctx) { return ctx ? ctx->num_sms : 0; }
+
+int32_t t0b_device_status(t0b_ctx* ctx, int32_t clear) {
+    if (!ctx || !ctx->status_host) return 0;
+    const int st = *reinterpret_cast<volatile int*>(ctx->status_host);
+    if (clear) *reinterpret_cast<volatile int*>(ctx->status_host) = 0;
+    return st;
+}
+
+int32_t t0b_set_wait_limit_ns(t0b_ctx* ctx, uint64_t ns) {
+    if (!ctx || ns == 0) return T0B_ERR_INVALID;
+    ctx->wait_limit_ns = ns;
+    return T0B_OK;
+}
+
+int32_t t0b_alloc(t0b_ctx* ctx, size_t bytes, uint64_t* dptr) {
+    int32_t rc = precheck(ctx);
+    if (rc != T0B_OK) return rc;
+    if (!dptr) return set_error(ctx, T0B_ERR_INVALID, "t0b_alloc: null out pointer");
+    std::lock_guard<std::recursive_mutex> lk(ctx->mu);
+    const size_t key = round4k(bytes == 0 ? 1 : bytes);
+    auto it = ctx->pool_free.find(key);
+    void* p = nullptr;
+    if (it != ctx->pool_free.end()) {
+        p = it->second;
+        ctx->pool_free.erase(it);
+        ctx->pool_cached -= key;
+        ++ctx->pool_hits;
+    } else {
+        ++ctx->pool_misses;
+        cudaError_t e = cudaMalloc(&p, key);
+        if (e == cudaErrorMemoryAllocation) {
+            cudaGetLastError();
+            // Give cached buffers back to the driver and retry once before reporting out-of-memory.
+            for (auto& kv : ctx->pool_free) cudaFree(kv.second);
+            ctx->pool_free.clear();
+            ctx->pool_cached = 0;
+            e = cudaMalloc(&p, key);
+            if (e == cudaErrorMemoryAllocation) {
+                cudaGetLastError();
+                return set_error(ctx, T0B_ERR_NOMEM, "t0b_alloc: out of device memory for %zu bytes", key);
+            }
+        }
+        if (e != cudaSuccess) return check_cuda(ctx, e, "cudaMalloc");
+    }
+    ctx->live[p] = key;
+    *dptr = reinterpret_cast<uint64_t>(p);
+    return T0B_OK;
+}
+
+int32_t t0b_alloc_zero(t0b_ctx* ctx, size_t bytes, uint64_t* dptr) {
+    int32_t rc = t0b_alloc(ctx, bytes, dptr);
+    if (rc != T0B_OK) return rc;
+    return t0b_memset0(ctx, *dptr, bytes);
+}
+
+int32_t t0b_recycle(t0b_ctx* ctx, uint64_t dptr) {
+    if (!ctx) return T0B_ERR_INVALID;
+    std::lock_guard<std::recursive_mutex> lk(ctx->mu);
+    void* p = reinterpret_cast<void*>(dptr);
+    auto it = ctx->live.find(p);
+    if (it == ctx->live.end()) return set_error(ctx, T0B_ERR_INVALID, "t0b_recycle: unknown buffer %p", p);
+    ctx->pool_free.emplace(it->second, p);
+    ctx->pool_cached += it->second;
+    ctx->live.erase(it);
+    return T0B_OK;
+}
+
+int32_t t0b_free(t0b_ctx* ctx, uint64_t dptr) {
+    if (!ctx) return T0B_ERR_INVALID;
+    std::lock_guard<std::recursive_mutex> lk(ctx->mu);
+    void* p = reinterpret_cast<void*>(dptr);
+    auto it = ctx->live.find(p);
+    if (it == ctx->live.end()) return set_error(ctx, T0B_ERR_INVALID, "t0b_free: unknown buffer %p", p);
+    ctx->live.erase(it);
+    // Tensor maps that point into this buffer must not outlive it.
+    ctx->tmaps.clear();
+    cudaSetDevice(ctx->device);
+    cudaStreamSynchronize(ctx->stream);
+    cudaError_t e = cudaFree(p);
+    if (e != cudaSuccess && !ctx->poisoned) return check_cuda(ctx, e, "cudaFree");
+    return T0B_OK;
+}
+
+int32_t t0b_pool_stats(t0b_ctx* ctx, uint64_t* cached, uint64_t* hits, uint64_t* misses) {
+    if (!ctx) return T0B_ERR_INVALID;
+    std::lock_guard<std::recursive_mutex> lk(ctx->mu);
+    if (cached) *cached = ctx->pool_cached;
+    if (hits) *hits = ctx->pool_hits;
+    if (misses) *misses = ctx->pool_misses;
+    return T0B_OK;
+}
+
+int32_t t0b_memcpy_h2d(t0b_ctx* ctx, uint64_t dst, const void* src, size_t bytes) {
+    int32_t rc = precheck(ctx);
+    if (rc != T0B_OK) return rc;
+    if (bytes == 0) return T0B_OK;
+    if (!dst || !src) return set_error(ctx, T0B_ERR_INVALID, "t0b_memcpy_h2d: null pointer");
+    rc = check_cuda(ctx, cudaMemcpyAsync(reinterpret_cast<void*>(dst), src, bytes, cudaMemcpyHostToDevice, ctx->stream),
+                    "cudaMemcpyAsync(h2d)");
+    if (rc != T0B_OK) return rc;
+    return check_cuda(ctx, cudaStreamSynchronize(ctx->stream), "cudaStreamSynchronize(h2d)");
+}
+
+int32_t t0b_memcpy_d2h(t0b_ctx* ctx, void* dst, uint64_t src, size_t bytes) {
+    int32_t rc = precheck(ctx);
+    if (rc != T0B_OK) return rc;
+    if (bytes == 0) return T0B_OK;
+    if (!dst || !src) return set_error(ctx, T0B_ERR_INVALID, "t0b_memcpy_d2h: null pointer");
+    rc = check_cuda(ctx, cudaMemcpyAsync(dst, reinterpret_cast<void*>(src), bytes, cudaMemcpyDeviceToHost, ctx->stream),
+                    "cudaMemcpyAsync(d2h)");
+    if (rc != T0B_OK) return rc;
+    return check_cuda(ctx, cudaStreamSynchronize(ctx->stream), "cudaStreamSynchronize(d2h)");
+}
+
+int32_t t0b_memset0(t0b_ctx* ctx, uint64_t dst, size_t bytes) {
+    int32_t rc = precheck(ctx);
+    if (rc != T0B_OK) return rc;
+    if (bytes == 0) return T0B_OK;
+    if (!dst) return set_error(ctx, T0B_ERR_INVALID, "t0b_memset0: null pointer");
+    return check_cuda(ctx, cudaMemsetAsync(reinterpret_cast<void*>(dst), 0, bytes, ctx->stream), "cudaMemsetAsync");
+}
+
+int32_t t0b_sync(t0b_ctx* ctx) {
+    int32_t rc = precheck(ctx);
+    if (rc != T0B_OK) return rc;
+    rc = check_cuda(ctx, cudaStreamSynchronize(ctx->stream), "cudaStreamSynchronize");
+    if (rc != T0B_OK) return rc;
+    const int st = *reinterpret_cast<volatile int*>(ctx->status_host);
+    if (st != 0) return set_error(ctx, T0B_ERR_DEVICE, "device status %d (a bounded in-kernel wait ran out)", st);
+    return T0B_OK;
+}
+
+uint64_t t0b_launch_count(t0b_ctx* ctx) { return ctx ? ctx->launches : 0; }
+
+// ------------------------------------------------------------------------------------------------ graphs
+
+int32_t t0b_graph_begin(t0b_ctx* ctx) {
+    int32_t rc = precheck(ctx);
+    if (rc != T0B_OK) return rc;
+    if (ctx->capturing) return set_error(ctx, T0B_ERR_INVALID, "t0b_graph_begin: already capturing");
+    rc = check_cuda(ctx, cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal), "cudaStreamBeginCapture");
+    if (rc == T0B_OK) ctx->capturing = true;
+    return rc;
+}
+
+int32_t t0b_graph_end(t0b_ctx* ctx, uint64_t* handle) {
+    if (!ctx || !handle) return T0B_ERR_INVALID;
+    if (!ctx->capturing) return set_error(ctx, T0B_ERR_INVALID, "t0b_graph_end: not capturing");
+    ctx->capturing = false;
+    cudaGraph_t g = nullptr;
+    int32_t rc = check_cuda(ctx, cudaStreamEndCapture(ctx->stream, &g), "cudaStreamEndCapture");
+    if (rc != T0B_OK) return rc;
+    cudaGraphExec_t ge = nullptr;
+    rc = check_cuda(ctx, cudaGraphInstantiate(&ge, g, 0), "cudaGraphInstantiate");
+    cudaGraphDestroy(g);
+    if (rc != T0B_OK) return rc;
+    const uint64_t id = ctx->next_graph++;
+    ctx->graphs[id] = ge;
+    *handle = id;
+    return T0B_OK;
+}
+
+int32_t t0b_graph_launch(t0b_ctx* ctx, uint64_t handle, int32_t async) {
+    int32_t rc = precheck(ctx);
+    if (rc != T0B_OK) return rc;
+    auto it = ctx->graphs.find(handle);
+    if (it == ctx->graphs.end()) return set_error(ctx, T0B_ERR_INVALID, "t0b_graph_launch: unknown graph %llu",
+                                                  static_cast<unsigned long long>(handle));
+    rc = check_cuda(ctx, cudaGraphLaunch(it->second, ctx->stream), "cudaGraphLaunch");
+    if (rc != T0B_OK) return rc;
+    return finish(ctx, async, "graph launch");
+}
+
+int32_t t0b_graph_destroy(t0b_ctx* ctx, uint64_t handle) {
+    if (!ctx) return T0B_ERR_INVALID;
+    auto it = ctx->graphs.find(handle);
+    if (it == ctx->graphs.end()) return T0B_ERR_INVALID;
+    cudaGraphExecDestroy(it->second);
+    ctx->graphs.erase(it);
+    return T0B_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,230 @@
+"""Host-side mirror of the reference runtime objects callers touch on the GEMM path:
+`GpuRuntime` (src/ignis/gpu_context.rs:30-106, 113-483) and `GpuBuffer` (src/kfd/mod.rs:947-1061),
+over the C ABI.  Errors surface as `T0Error` carrying the library's message (the reference returns
+`Result<_, String>`); a CUDA error poisons the runtime like a queue timeout does in the reference."""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional
+
+import numpy as np
+
+from ._lib import lib
+from .gemm_gen import GemmConfig
+
+
+class T0Error(RuntimeError):
+    def __init__(self, code: int, message: str):
+        super().__init__(f"[t0b {code}] {message}")
+        self.code = code
+        self.message = message
+
+
+OUT_F32, OUT_BF16 = 0, 1
+
+
+class GpuBuffer:
+    """Device memory handle.  `write`/`read` are explicit copies (the reference maps VRAM into the host and
+    tests read results through `host_ptr`); dropping the last reference frees the memory."""
+
+    def __init__(self, rt: "GpuRuntime", addr: int, size: int, owned: bool = True):
+        self._rt = rt
+        self._addr = addr
+        self._size = size
+        self._owned = owned
+
+    def gpu_addr(self) -> int:
+        return self._addr
+
+    def size(self) -> int:
+        return self._size
+
+    def write(self, data) -> None:
+        buf = np.ascontiguousarray(data)
+        if buf.nbytes > self._size:
+            raise AssertionError(f"GpuBuffer.write: {buf.nbytes} bytes into a {self._size}-byte buffer")
+        self._rt._check(lib().t0b_memcpy_h2d(self._rt._ctx, self._addr, buf.ctypes.data, buf.nbytes))
+
+    def read(self, out: np.ndarray) -> np.ndarray:
+        if out.nbytes > self._size:
+            raise AssertionError(f"GpuBuffer.read: {out.nbytes} bytes from a {self._size}-byte buffer")
+        assert out.flags["C_CONTIGUOUS"]
+        self._rt._check(lib().t0b_memcpy_d2h(self._rt._ctx, out.ctypes.data, self._addr, out.nbytes))
+        return out
+
+    def read_as(self, dtype, count: int) -> np.ndarray:
+        return self.read(np.empty(count, dtype=dtype))
+
+    def zero(self) -> None:
+        self._rt._check(lib().t0b_memset0(self._rt._ctx, self._addr, self._size))
+        self._rt.synchronize()
+
+    def release(self) -> None:
+        if self._owned and self._addr and self._rt._ctx:
+            lib().t0b_free(self._rt._ctx, self._addr)
+        self._addr = 0
+
+    def __del__(self):
+        try:
+            self.release()
+        except Exception:
+            pass
+
+
+class GpuRuntime:
+    """One device + one in-order stream + a size-keyed buffer pool."""
+
+    def __init__(self, device: int = 0):
+        self._ctx = C.c_void_p()
+        rc = lib().t0b_ctx_create(device, C.byref(self._ctx))
+        if rc != 0:
+            self._ctx = None
+            raise T0Error(rc, "GPU init failed: no usable sm_100a CUDA device (there is no CPU fallback)")
+
+    @staticmethod
+    def new(device: int = 0) -> "GpuRuntime":
+        return GpuRuntime(device)
+
+    # ------------------------------------------------------------------ plumbing
+    def _check(self, rc: int) -> None:
+        if rc != 0:
+            raise T0Error(rc, lib().t0b_last_error(self._ctx).decode())
+
+    @property
+    def handle(self):
+        return self._ctx
+
+    def close(self) -> None:
+        if self._ctx:
+            lib().t0b_ctx_destroy(self._ctx)
+            self._ctx = None
+
+    def set_stream(self, cuda_stream: int) -> None:
+        self._check(lib().t0b_ctx_set_stream(self._ctx, C.c_void_p(cuda_stream)))
+
+    def num_sms(self) -> int:
+        return lib().t0b_num_sms(self._ctx)
+
+    def is_poisoned(self) -> bool:
+        return bool(lib().t0b_is_poisoned(self._ctx))
+
+    def device_status(self, clear: bool = False) -> int:
+        return lib().t0b_device_status(self._ctx, int(clear))
+
+    def launch_count(self) -> int:
+        return lib().t0b_launch_count(self._ctx)
+
+    # ------------------------------------------------------------------ memory (gpu_context.rs:437-483)
+    def alloc(self, size: int) -> GpuBuffer:
+        p = C.c_uint64()
+        self._check(lib().t0b_alloc(self._ctx, size, C.byref(p)))
+        return GpuBuffer(self, p.value, size)
+
+    def alloc_zero(self, size: int) -> GpuBuffer:
+        p = C.c_uint64()
+        self._check(lib().t0b_alloc_zero(self._ctx, size, C.byref(p)))
+        return GpuBuffer(self, p.value, size)
+
+    def alloc_f32(self, n: int) -> GpuBuffer:
+        """n floats, at least 512 bytes, zero-filled (gpu_context.rs:449-454)."""
+        return self.alloc_zero(max(n * 4, 512))
+
+    def recycle(self, buf: GpuBuffer) -> None:
+        self._check(lib().t0b_recycle(self._ctx, buf._addr))
+        buf._addr = 0
+
+    def upload(self, data) -> GpuBuffer:
+        arr = np.ascontiguousarray(data)
+        b = self.alloc(max(arr.nbytes, 16))
+        b.write(arr)
+        return b
+
+    def upload_f32(self, data) -> GpuBuffer:
+        return self.upload(np.ascontiguousarray(data, dtype=np.float32))
+
+    def write_f32(self, buf: GpuBuffer, data) -> None:
+        buf.write(np.ascontiguousarray(data, dtype=np.float32))
+
+    def read_f32(self, buf: GpuBuffer, n: int) -> np.ndarray:
+        return buf.read_as(np.float32, n)
+
+    def pool_stats(self) -> dict:
+        a, b, c = C.c_uint64(), C.c_uint64(), C.c_uint64()
+        lib().t0b_pool_stats(self._ctx, C.byref(a), C.byref(b), C.byref(c))
+        return {"cached_bytes": a.value, "hits": b.value, "misses": c.value}
+
+    # ------------------------------------------------------------------ sync (gpu_context.rs:297-332)
+    def synchronize(self) -> None:
+        self._check(lib().t0b_sync(self._ctx))
+
+    wait_idle = synchronize
+
+    # ------------------------------------------------------------------ GEMM
+    def gemm(self, a: GpuBuffer, b: GpuBuffer, c: GpuBuffer, m: int, n: int, k: int, *, cfg: Optional[GemmConfig] = None,
+             trans_a: bool = False, trans_b: bool = True, lda: Optional[int] = None, ldb: Optional[int] = None,
+             ldc: Optional[int] = None, out_dtype: int = OUT_F32, epilogue: int = 0, bias: Optional[GpuBuffer] = None,
+             alpha: float = 1.0, workspace: Optional[GpuBuffer] = None, async_: bool = False) -> None:
+        lda = lda if lda is not None else (m if trans_a else k)
+        ldb = ldb if ldb is not None else (k if trans_b else n)
+        ldc = ldc if ldc is not None else n
+        cp = C.byref(cfg.to_c()) if cfg is not None else None
+        self._check(lib().t0b_gemm(self._ctx, cp, int(trans_a), int(trans_b), _addr(a), _addr(b), _addr(c), m, n, k,
+                                   lda, ldb, ldc, out_dtype, epilogue, _addr(bias), alpha, _addr(workspace),
+                                   workspace.size() if workspace is not None else 0, int(async_)))
+
+    def gemm_slabs(self, x: GpuBuffer, wt: GpuBuffer, y: GpuBuffer, m: int, n: int, k: int, split_k: int,
+                   cfg: Optional[GemmConfig] = None, async_: bool = False) -> None:
+        cp = C.byref(cfg.to_c()) if cfg is not None else None
+        self._check(lib().t0b_gemm_slabs(self._ctx, cp, _addr(x), _addr(wt), _addr(y), m, n, k, split_k, int(async_)))
+
+    def splitk_reduce(self, partial: GpuBuffer, split_k: int, m: int, n: int, c: GpuBuffer, out_dtype: int = OUT_F32,
+                      epilogue: int = 0, bias: Optional[GpuBuffer] = None, async_: bool = False) -> None:
+        self._check(lib().t0b_splitk_reduce(self._ctx, _addr(partial), split_k, m, n, m * n, n, _addr(c), n, out_dtype,
+                                            epilogue, _addr(bias), 1.0, int(async_)))
+
+    def dispatch(self, cfg: GemmConfig, grid, kernargs: bytes) -> None:
+        """`GpuRuntime::dispatch(kernel, grid, kernargs)` for GEMM kernels: synchronous (gpu_context.rs:264-288)."""
+        self._dispatch(cfg, grid, kernargs, False)
+
+    def dispatch_async(self, cfg: GemmConfig, grid, kernargs: bytes) -> None:
+        self._dispatch(cfg, grid, kernargs, True)
+
+    def _dispatch(self, cfg, grid, kernargs, async_):
+        blob = (C.c_uint8 * len(kernargs)).from_buffer_copy(kernargs)
+        self._check(lib().t0b_dispatch_kernargs(self._ctx, C.byref(cfg.to_c()), grid[0], grid[1], blob, len(kernargs),
+                                                int(async_)))
+
+    def gemm_time(self, a: GpuBuffer, b: GpuBuffer, c: GpuBuffer, m: int, n: int, k: int, *, cfg=None, trans_a=False,
+                  trans_b=True, out_dtype=OUT_F32, warmup=3, iters=10) -> float:
+        lda = m if trans_a else k
+        ldb = k if trans_b else n
+        ms = C.c_float()
+        cp = C.byref(cfg.to_c()) if cfg is not None else None
+        self._check(lib().t0b_gemm_time(self._ctx, cp, int(trans_a), int(trans_b), _addr(a), _addr(b), _addr(c), m, n, k,
+                                        lda, ldb, n, out_dtype, warmup, iters, C.byref(ms)))
+        return ms.value
+
+    def tune(self, m: int, n: int, k: int, trans_a=False, trans_b=True, out_dtype=OUT_F32):
+        """GemmTuner::tune(rt, m, n, k) (src/t0/auto_gemm.rs:82): returns (best config, TFLOP/s)."""
+        from ._lib import GemmConfigC
+        out = GemmConfigC()
+        tf = C.c_float()
+        self._check(lib().t0b_tune(self._ctx, m, n, k, int(trans_a), int(trans_b), out_dtype, C.byref(out), C.byref(tf)))
+        return GemmConfig.from_c(out), tf.value
+
+    def selftest_bounded_wait(self, limit_ns: int) -> int:
+        return lib().t0b_selftest_bounded_wait(self._ctx, limit_ns)
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def _addr(b) -> int:
+    if b is None:
+        return 0
+    if isinstance(b, int):
+        return b
+    return b.gpu_addr()
