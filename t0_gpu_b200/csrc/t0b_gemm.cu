@@ -335,7 +335,7 @@ int32_t t0b_gemm(t0b_ctx* ctx, const t0b_gemm_config* cfg, int32_t trans_a, int3
     if (out_dtype != T0B_OUT_F32 && out_dtype != T0B_OUT_BF16) return set_error(ctx, T0B_ERR_INVALID, "gemm: unknown out_dtype %d", out_dtype);
     rc = run_gemm(ctx, g);
     if (rc != T0B_OK) return rc;
-    return finish(ctx, async, "t0b_gemm");
+    return finish(ctx, async, "t0b_gemm", 0);
 }
 
 int32_t t0b_gemm_multi_dst(t0b_ctx* ctx, const t0b_gemm_config* cfg, int32_t trans_a, int32_t trans_b, uint64_t a,
@@ -364,7 +364,7 @@ int32_t t0b_gemm_multi_dst(t0b_ctx* ctx, const t0b_gemm_config* cfg, int32_t tra
     g.out_bf16 = out_dtype == T0B_OUT_BF16; g.epilogue = EPI_STORE; g.alpha = 1.0f;
     rc = run_gemm(ctx, g);
     if (rc != T0B_OK) return rc;
-    return finish(ctx, async, "t0b_gemm_multi_dst");
+    return finish(ctx, async, "t0b_gemm_multi_dst", 0);
 }
 
 int32_t t0b_gemm_slabs(t0b_ctx* ctx, const t0b_gemm_config* cfg, uint64_t x, uint64_t wt, uint64_t y, uint32_t m,
@@ -383,7 +383,7 @@ int32_t t0b_gemm_slabs(t0b_ctx* ctx, const t0b_gemm_config* cfg, uint64_t x, uin
     g.slabs_only = true; g.force_split = split_k;
     rc = run_gemm(ctx, g);
     if (rc != T0B_OK) return rc;
-    return finish(ctx, async, "t0b_gemm_slabs");
+    return finish(ctx, async, "t0b_gemm_slabs", 0);
 }
 
 int32_t t0b_splitk_reduce(t0b_ctx* ctx, uint64_t partial, uint32_t split_k, uint32_t m, uint32_t n,
@@ -399,7 +399,7 @@ int32_t t0b_splitk_reduce(t0b_ctx* ctx, uint64_t partial, uint32_t split_k, uint
                        reinterpret_cast<void*>(c), ldc, out_dtype == T0B_OUT_BF16, epilogue,
                        reinterpret_cast<const float*>(bias), alpha);
     if (rc != T0B_OK) return rc;
-    return finish(ctx, async, "t0b_splitk_reduce");
+    return finish(ctx, async, "t0b_splitk_reduce", 1);
 }
 
 int32_t t0b_dispatch_kernargs(t0b_ctx* ctx, const t0b_gemm_config* cfg, uint32_t grid_x, uint32_t grid_y,
@@ -449,7 +449,7 @@ int32_t t0b_dispatch_kernargs(t0b_ctx* ctx, const t0b_gemm_config* cfg, uint32_t
     }
     rc = run_gemm(ctx, g);
     if (rc != T0B_OK) return rc;
-    return finish(ctx, async, "t0b_dispatch_kernargs");
+    return finish(ctx, async, "t0b_dispatch_kernargs", 0);
 }
 
 int32_t t0b_gemm_time(t0b_ctx* ctx, const t0b_gemm_config* cfg, int32_t trans_a, int32_t trans_b, uint64_t a, uint64_t b,

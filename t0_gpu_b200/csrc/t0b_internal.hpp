@@ -67,7 +67,8 @@ namespace t0b {
 int32_t set_error(t0b_ctx* ctx, int32_t code, const char* fmt, ...);
 int32_t check_cuda(t0b_ctx* ctx, cudaError_t e, const char* what);
 int32_t precheck(t0b_ctx* ctx);                 // null / poisoned checks, sets the device
-int32_t finish(t0b_ctx* ctx, int32_t async, const char* what);   // launch-error check (+ sync when !async)
+// Launch-error check (+ sync and status-word check when !async). `count` kernels are added to the launch counter.
+int32_t finish(t0b_ctx* ctx, int32_t async, const char* what, int count = 1);
 
 // Host-side GemmConfig logic (t0b_gemm_gen.cpp).
 void default_b200_config(uint32_t m, uint32_t k, uint32_t n, int num_sms, t0b_gemm_config* out);

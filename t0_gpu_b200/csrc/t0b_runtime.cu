@@ -38,10 +38,10 @@ int32_t precheck(t0b_ctx* ctx) {
     return T0B_OK;
 }
 
-int32_t finish(t0b_ctx* ctx, int32_t async, const char* what) {
+int32_t finish(t0b_ctx* ctx, int32_t async, const char* what, int count) {
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return check_cuda(ctx, e, what);
-    ++ctx->launches;
+    ctx->launches += static_cast<uint64_t>(count);
     if (async || ctx->capturing) return T0B_OK;
     e = cudaStreamSynchronize(ctx->stream);
     if (e != cudaSuccess) return check_cuda(ctx, e, what);

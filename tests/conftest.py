@@ -28,3 +28,14 @@ def pytest_collection_modifyitems(config, items):
     for item in items:
         if "gpu" in item.keywords:
             item.add_marker(skip)
+
+
+@pytest.fixture(scope="session")
+def rt():
+    """One runtime per test process, like the reference's shared `OnceLock<GpuRuntime>`
+    (src/t0/tile_ir.rs:3483-3497)."""
+    import t0_gpu_b200 as t
+
+    r = t.GpuRuntime()
+    yield r
+    r.close()

@@ -1,0 +1,171 @@
+"""Host-side GEMM front-end (no GPU): the reference's own unit tests for this layer, restated against the
+C ABI -- src/t0/gemm_gen.rs:544-631 (auto_select sanity, legacy heuristic pins, epilogue name tags,
+kernarg layout) -- plus grid arithmetic, presets, the plan resolver and the library's exported symbols."""
+import ctypes as C
+import os
+import re
+import struct
+
+import pytest
+
+import t0_gpu_b200 as t
+from t0_gpu_b200 import _lib
+from t0_gpu_b200.gemm_gen import EpilogueOp, GemmConfig, GemmTranspose
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_library_exports_every_declared_symbol():
+    with open(os.path.join(ROOT, "include", "t0b200.h")) as f:
+        text = f.read()
+    declared = set(re.findall(r"T0B_API\s+[\w\s\*]+?\b(t0b_\w+)\s*\(", text))
+    assert len(declared) >= 60
+    lib = C.CDLL(_lib.LIB_PATH)
+    missing = [n for n in sorted(declared) if not hasattr(lib, n)]
+    assert not missing, missing
+    # the Python binding declares exactly the header's functions
+    assert declared == set(_lib.SIGNATURES), declared ^ set(_lib.SIGNATURES)
+
+
+def test_no_gpu_means_loud_failure():
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present")
+    with pytest.raises(t.T0Error):
+        t.GpuRuntime()
+
+
+def test_auto_select_sizes():
+    """gemm_gen.rs:549-572.  tile_k is 64 on B200 (one 128-byte swizzle row), where the reference pins 16."""
+    c = t.auto_select(256, 256, 256)
+    assert 16 <= c.tile_m <= 256 and 32 <= c.tile_n <= 128 and c.wg_size >= 32
+    c = t.auto_select(1024, 1024, 1024)
+    assert c.tile_m >= 64 and c.tile_k == 64
+    c = t.auto_select(8192, 8192, 8192)
+    assert c.tile_m >= 64
+    c = t.auto_select(128, 4096, 4096)
+    assert 128 % c.tile_m == 0
+    with pytest.raises(ValueError):
+        t.auto_select(0, 16, 16)
+
+
+def test_auto_select_legacy_preserved():
+    """gemm_gen.rs:575-584."""
+    c = t.auto_select_legacy(256, 256, 256)
+    assert (c.split_k or 1) > 1 and c.tile_m == 64
+    c = t.auto_select_legacy(1024, 1024, 1024)
+    assert c.tile_m == 128 and c.wgp_mode
+    # remaining branches of the 7-branch heuristic
+    c = t.auto_select_legacy(128, 4096, 4096)
+    assert (c.tile_m, c.tile_n, c.split_k, c.swap_grid) == (128, 64, 4, False)
+    c = t.auto_select_legacy(512, 4096, 4096)
+    assert (c.tile_m, c.split_k, c.swap_grid) == (128, 8, False)
+    c = t.auto_select_legacy(4096, 4096, 4096)
+    assert (c.tile_m, c.split_k, c.swap_grid) == (128, 8, True)
+    c = t.auto_select_legacy(4032, 4096, 4096)     # 64 | M, 128 does not
+    assert (c.tile_m, c.tile_n, c.split_k) == (64, 64, 4)
+    c = t.auto_select_legacy(4000, 4096, 4096)     # only 32 | M
+    assert (c.tile_m, c.tile_n) == (32, 64)
+    # clamp_sk keeps K % (tile_k * sk) == 0
+    c = t.auto_select_legacy(256, 48, 256)
+    sk = c.split_k or 1
+    assert 48 % (16 * sk) == 0
+
+
+def test_backward_selectors_permute_dims():
+    assert t.auto_select_backward_data(1024, 32000, 4096).name() == t.auto_select(1024, 32000, 4096).name()
+    assert t.auto_select_backward_weight(1024, 32000, 4096).name() == t.auto_select(32000, 1024, 4096).name()
+
+
+def test_epilogue_name_tags():
+    """gemm_gen.rs:591-602."""
+    cfg = GemmConfig.tile_32x64_k16()
+    assert "t0_gemm_32x64_k16" in cfg.name() and "_bias" not in cfg.name()
+    cfg.epilogue = EpilogueOp.BiasAddStoreF32
+    assert cfg.name().endswith("_bias")
+    cfg.epilogue = EpilogueOp.BiasAddReluStoreF32
+    assert cfg.name().endswith("_bias_relu")
+
+
+def test_config_names_match_reference_format():
+    assert GemmConfig.tile_64x64_k16().name() == "t0_gemm_64x64_k16_ldsdb_wgp"
+    assert GemmConfig.tile_32x64_direct().name() == "t0_gemm_32x64_k16_direct_wgp"
+    c = GemmConfig.tile_128x128_2pass().with_(split_k=4, swap_grid=False, wgp_mode=False, transpose=GemmTranspose.NN)
+    assert c.name() == "t0_gemm_128x64_k16_ldsdb_sk4_2p_mg_nn"
+    assert GemmConfig.tile_64x64_k16().with_(split_k=1).name() == "t0_gemm_64x64_k16_ldsdb_wgp"
+
+
+def test_presets_and_getters():
+    c = GemmConfig.tile_128x64_k32()
+    assert (c.tile_m, c.tile_n, c.tile_k, c.wg_size) == (128, 64, 32, 128)
+    assert c.n_waves() == 4 and c.rows_per_wave() == 32 and c.n_row_blocks() == 2 and c.n_col_tiles() == 4
+    assert c.k_sub_steps() == 2 and c.lds_per_buffer() == (128 + 64) * 32 * 2 and c.lds_total() == 2 * c.lds_per_buffer()
+    # estimated_vgprs: acc 2*4*8 + x_frag 16 + wt_frag 32 + gmem (4+2... per thread loads) + 49
+    assert c.estimated_vgprs() == 2 * 4 * 8 + 2 * 8 + 4 * 8 + (128 * 32 * 2 // 128 // 16) * 4 + (64 * 32 * 2 // 128 // 16) * 4 + 49
+    assert c.is_feasible()
+    assert len(t.sweep_configs()) == 9 and len(t.standard_configs()) == 14
+    assert t.standard_configs()[8].split_k == 4 and t.standard_configs()[8].tile_m == 16
+    with pytest.raises(ValueError):
+        GemmConfig.preset("nope")
+
+
+def test_kernargs_layouts():
+    """gemm_gen.rs:414-456, 619-630; tile_ir.rs:3173-3190."""
+    cfg = GemmConfig.tile_32x64_k16()
+    ka = t.build_kernargs_with_bias(0x1000, 0x2000, 0x3000, 64, 64, 128, cfg, 0x4000)
+    assert len(ka) == 48 and struct.unpack_from("<Q", ka, 40)[0] == 0x4000
+    ka = t.build_kernargs(0x1122334455667788, 0x2000, 0x3000, 96, 160, 128, cfg)
+    x, wt, y, k, n, z, stride = struct.unpack("<QQQIIII", ka)
+    assert (x, wt, y, k, n, z, stride) == (0x1122334455667788, 0x2000, 0x3000, 96, 160, 0, 0)
+    ka = t.build_kernargs(1, 2, 3, 96, 160, 128, cfg.with_(split_k=4))
+    assert struct.unpack_from("<I", ka, 36)[0] == 128 * 160 * 4
+    ka = t.build_kernargs_m(1, 2, 3, 96, 160, 33)
+    assert len(ka) == 44 and struct.unpack_from("<III", ka, 32) == (0, 0, 33)
+    # backward helpers permute (k, n, m)
+    ka = t.build_kernargs_backward_data(1, 2, 3, 128, 512, 256, cfg)       # K_contract = N_orig, N_out = K_orig
+    assert struct.unpack_from("<II", ka, 24) == (512, 256)
+    ka = t.build_kernargs_backward_weight(1, 2, 3, 128, 512, 256, cfg)     # K_contract = M, N_out = K_orig
+    assert struct.unpack_from("<II", ka, 24) == (128, 256)
+
+
+def test_grids():
+    """gemm_gen.rs:286-309, 402-409: x is in threads, split-K multiplies the slow axis."""
+    c = GemmConfig.tile_128x64_k16()
+    assert t.compute_grid(c, 256, 256) == (4 * 128, 2)
+    assert t.compute_grid(c.with_(swap_grid=False), 256, 256) == (2 * 128, 4)
+    assert t.compute_grid(c, 129, 65) == (2 * 128, 2)                       # ceiling division
+    assert t.compute_grid(GemmConfig.tile_128x128_2pass(), 256, 256) == (2 * 128, 2)   # 2 column passes
+    assert t.compute_grid_split_k(c, 256, 256, 4) == (4 * 128, 8)
+    assert t.compute_grid_auto(c.with_(split_k=8), 256, 256) == (4 * 128, 16)
+    assert t.compute_grid_auto(c, 256, 256) == t.compute_grid(c, 256, 256)
+    with pytest.raises(AssertionError):
+        t.compute_grid_split_k(c, 256, 256, 3)                               # the reference asserts a power of 2
+    assert t.compute_grid_backward_data(c, 256, 512) == t.compute_grid_auto(c, 256, 512)
+    assert t.compute_grid_backward_weight(c, 1024, 512) == t.compute_grid_auto(c, 1024, 512)
+
+
+def test_plan_resolution():
+    p = t.resolve_plan(None, 8192, 8192, 8192)
+    assert (p.bm, p.bn, p.bk, p.cta_group) == (256, 256, 64, 2) and p.use_tma and p.smem_bytes <= 227 * 1024
+    # reference presets run as single-CTA 128-row tiles
+    p = t.resolve_plan(GemmConfig.tile_64x64_k16().with_(split_k=4), 256, 256, 256)
+    assert (p.bm, p.bn, p.cta_group, p.split_k, p.kb_per_split) == (128, 64, 1, 4, 1)
+    # more slabs than 64-wide K blocks: effective split shrinks
+    p = t.resolve_plan(GemmConfig.tile_64x64_k16().with_(split_k=8), 64, 64, 256)
+    assert p.split_k == 4
+    # a row pitch that is not a multiple of 16 bytes cannot be addressed by TMA
+    assert not t.resolve_plan(None, 33, 50, 100, lda=100, ldb=100).use_tma
+    assert t.resolve_plan(None, 33, 50, 100, lda=104, ldb=104).use_tma
+    # B200-native presets
+    p = t.resolve_plan(GemmConfig.preset("b200_128x256"), 4096, 4096, 4096)
+    assert (p.bm, p.bn, p.cta_group, p.stages) == (128, 256, 1, 4)
+    for name in ("b200_128x64", "b200_128x128", "b200_128x256", "b200_256x128", "b200_256x256"):
+        p = t.resolve_plan(GemmConfig.preset(name), 4096, 4096, 4096)
+        assert p.smem_bytes <= 227 * 1024 and p.stages >= 4
+
+
+def test_split_k_selected_for_small_grids():
+    c = t.auto_select(512, 16384, 512)
+    assert (c.split_k or 1) >= 4
+    assert t.auto_select(8192, 8192, 8192).split_k is None
+    assert _lib.lib().t0b_gemm_workspace_bytes(C.byref(c.to_c()), 512, 512, 16384) == (c.split_k) * 512 * 512 * 4

@@ -1,0 +1,86 @@
+"""Runtime behaviour on the GPU: buffer pool, explicit copies, bounded in-kernel waits (failure detection
+without faulting the device), CUDA-graph replay of a launch-bound GEMM, on-device tuning."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+import oracle
+import t0_gpu_b200 as t
+from t0_gpu_b200._lib import lib
+
+pytestmark = pytest.mark.gpu
+
+
+def test_pool_recycles_by_rounded_size(rt):
+    before = rt.pool_stats()
+    a = rt.alloc(5000)          # rounds to 8192
+    addr = a.gpu_addr()
+    rt.recycle(a)
+    assert rt.pool_stats()["cached_bytes"] == before["cached_bytes"] + 8192
+    b = rt.alloc(8000)          # same 4 KiB class: comes back from the pool
+    assert b.gpu_addr() == addr
+    assert rt.pool_stats()["hits"] == before["hits"] + 1
+    data = np.arange(2000, dtype=np.float32)
+    b.write(data)
+    assert np.array_equal(b.read_as(np.float32, 2000), data)
+    with pytest.raises(AssertionError):
+        b.write(np.zeros(4000, np.float32))        # larger than the buffer (bounds assert, kfd/mod.rs:962)
+    z = rt.alloc_f32(10)
+    assert z.size() >= 512 and np.all(z.read_as(np.float32, 10) == 0.0)
+
+
+def test_bounded_wait_times_out_and_context_survives(rt):
+    """A wait on a barrier nothing signals runs out after its limit, the kernel records a status code and
+    returns; the context is not poisoned and the next GEMM works."""
+    rc = rt.selftest_bounded_wait(20_000_000)       # 20 ms
+    assert rc == -4                                  # T0B_ERR_DEVICE
+    assert rt.device_status(clear=True) == 105       # DEV_TIMEOUT_SELFTEST
+    assert rt.device_status() == 0 and not rt.is_poisoned()
+    ones = rt.upload(np.full(64 * 64, 0x3F80, np.uint16))
+    c = rt.alloc(64 * 64 * 4)
+    rt.gemm(ones, ones, c, 64, 64, 64)
+    assert np.all(c.read_as(np.float32, 64 * 64) == 64.0)
+
+
+def test_graph_replay_of_small_gemm(rt):
+    """256^3 is launch-bound; a captured graph of 8 GEMMs replays with one submission."""
+    m = n = k = 256
+    A = oracle.rand_bf16(m * k, 256 * 1000 + 256)
+    B = oracle.rand_bf16(n * k, 256 * 2000 + 256)
+    da, db = rt.upload(A), rt.upload(B)
+    outs = [rt.alloc(m * n * 4) for _ in range(8)]
+    rt.gemm(da, db, outs[0], m, n, k)                 # warm (function attributes, tensor maps) outside capture
+    ref = outs[0].read_as(np.float32, m * n)
+    rt._check(lib().t0b_graph_begin(rt.handle))
+    for o in outs:
+        rt.gemm(da, db, o, m, n, k, async_=True)
+    h = C.c_uint64()
+    rt._check(lib().t0b_graph_end(rt.handle, C.byref(h)))
+    for o in outs:
+        o.zero()
+    rt._check(lib().t0b_graph_launch(rt.handle, h.value, 0))
+    for o in outs:
+        assert np.array_equal(o.read_as(np.float32, m * n), ref)
+    rt._check(lib().t0b_graph_destroy(rt.handle, h.value))
+
+
+def test_tuner_returns_a_valid_config(rt):
+    cfg, tflops = rt.tune(1024, 1024, 1024)
+    assert cfg.tile_m in (128, 256) and cfg.tile_n in (64, 128, 256) and tflops > 1.0
+    # the tuned choice is what a config-less call now uses, and it is still correct
+    A = oracle.rand_bf16(1024 * 1024, 1).reshape(1024, 1024)
+    da = rt.upload(A)
+    c = rt.alloc(1024 * 1024 * 4)
+    rt.gemm(da, da, c, 1024, 1024, 1024)
+    ref = oracle.gemm_bf16(A, A, 1024, 1024, 1024, row_begin=5, row_end=6)[5]
+    assert np.abs(c.read_as(np.float32, 1024 * 1024).reshape(1024, 1024)[5] - ref).max() < 2 ** -7 * 32
+
+
+def test_launch_counter_counts_kernels(rt):
+    a = rt.alloc(64 * 64 * 2); c = rt.alloc(64 * 64 * 4)
+    n0 = rt.launch_count()
+    rt.gemm(a, a, c, 64, 64, 64, cfg=t.GemmConfig.preset("b200_128x64"))
+    assert rt.launch_count() == n0 + 1
+    rt.gemm(a, a, c, 64, 64, 256, cfg=t.GemmConfig.preset("b200_128x64").with_(split_k=2))
+    assert rt.launch_count() == n0 + 3      # GEMM + reduce
