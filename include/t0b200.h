@@ -168,8 +168,18 @@ T0B_API int32_t t0b_pool_stats(t0b_ctx* ctx, uint64_t* cached_bytes, uint64_t* h
 T0B_API int32_t t0b_memcpy_h2d(t0b_ctx* ctx, uint64_t dst, const void* src, size_t bytes);
 T0B_API int32_t t0b_memcpy_d2h(t0b_ctx* ctx, void* dst, uint64_t src, size_t bytes);
 T0B_API int32_t t0b_memset0(t0b_ctx* ctx, uint64_t dst, size_t bytes);
+/* Strided device -> host copy of `height` rows of `width_bytes` (a column block of a row-major matrix). */
+T0B_API int32_t t0b_memcpy2d_d2h(t0b_ctx* ctx, void* dst, size_t dst_pitch, uint64_t src, size_t src_pitch,
+                                 size_t width_bytes, size_t height);
 /* GpuRuntime::synchronize / wait_idle, gpu_context.rs:297-332.  Also checks the device status word. */
 T0B_API int32_t t0b_sync(t0b_ctx* ctx);
+
+/* Share a device allocation between the one-process-per-GPU ranks of a node: export gives a 64-byte handle
+ * (cudaIpcMemHandle_t) for a buffer obtained from t0b_alloc; open maps a peer's buffer into this process and
+ * enables peer access over NVLink; close unmaps it.  No counterpart in the reference (single GPU). */
+T0B_API int32_t t0b_ipc_export(t0b_ctx* ctx, uint64_t dptr, uint8_t handle[64]);
+T0B_API int32_t t0b_ipc_open(t0b_ctx* ctx, const uint8_t handle[64], uint64_t* dptr);
+T0B_API int32_t t0b_ipc_close(t0b_ctx* ctx, uint64_t dptr);
 
 /* ------------------------------------------------------------------------------------------------
  * GEMM dispatch

@@ -67,7 +67,11 @@ SIGNATURES = {
     "t0b_memcpy_h2d": (_i32, [_ctx, _u64, C.c_void_p, _sz]),
     "t0b_memcpy_d2h": (_i32, [_ctx, C.c_void_p, _u64, _sz]),
     "t0b_memset0": (_i32, [_ctx, _u64, _sz]),
+    "t0b_memcpy2d_d2h": (_i32, [_ctx, C.c_void_p, _sz, _u64, _sz, _sz, _sz]),
     "t0b_sync": (_i32, [_ctx]),
+    "t0b_ipc_export": (_i32, [_ctx, _u64, _u8p]),
+    "t0b_ipc_open": (_i32, [_ctx, _u8p, C.POINTER(_u64)]),
+    "t0b_ipc_close": (_i32, [_ctx, _u64]),
     "t0b_gemm": (_i32, [_ctx, _cfgp, _i32, _i32, _u64, _u64, _u64, _u32, _u32, _u32, _u64, _u64, _u64, _i32, _i32,
                         _u64, _f, _u64, _sz, _i32]),
     "t0b_gemm_workspace_bytes": (_sz, [_cfgp, _u32, _u32, _u32]),

@@ -239,6 +239,19 @@ int32_t t0b_memcpy_d2h(t0b_ctx* ctx, void* dst, uint64_t src, size_t bytes) {
     return check_cuda(ctx, cudaStreamSynchronize(ctx->stream), "cudaStreamSynchronize(d2h)");
 }
 
+int32_t t0b_memcpy2d_d2h(t0b_ctx* ctx, void* dst, size_t dst_pitch, uint64_t src, size_t src_pitch, size_t width_bytes,
+                         size_t height) {
+    int32_t rc = precheck(ctx);
+    if (rc != T0B_OK) return rc;
+    if (width_bytes == 0 || height == 0) return T0B_OK;
+    if (!dst || !src || dst_pitch < width_bytes || src_pitch < width_bytes)
+        return set_error(ctx, T0B_ERR_INVALID, "t0b_memcpy2d_d2h: null pointer or pitch smaller than the row");
+    rc = check_cuda(ctx, cudaMemcpy2DAsync(dst, dst_pitch, reinterpret_cast<void*>(src), src_pitch, width_bytes, height,
+                                           cudaMemcpyDeviceToHost, ctx->stream), "cudaMemcpy2DAsync(d2h)");
+    if (rc != T0B_OK) return rc;
+    return check_cuda(ctx, cudaStreamSynchronize(ctx->stream), "cudaStreamSynchronize(d2h 2d)");
+}
+
 int32_t t0b_memset0(t0b_ctx* ctx, uint64_t dst, size_t bytes) {
     int32_t rc = precheck(ctx);
     if (rc != T0B_OK) return rc;
@@ -258,6 +271,42 @@ int32_t t0b_sync(t0b_ctx* ctx) {
 }
 
 uint64_t t0b_launch_count(t0b_ctx* ctx) { return ctx ? ctx->launches : 0; }
+
+// ------------------------------------------------------------------------------------------------ IPC
+
+int32_t t0b_ipc_export(t0b_ctx* ctx, uint64_t dptr, uint8_t handle[64]) {
+    int32_t rc = precheck(ctx);
+    if (rc != T0B_OK) return rc;
+    if (!dptr || !handle) return set_error(ctx, T0B_ERR_INVALID, "ipc_export: null pointer");
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size");
+    cudaIpcMemHandle_t h;
+    rc = check_cuda(ctx, cudaIpcGetMemHandle(&h, reinterpret_cast<void*>(dptr)), "cudaIpcGetMemHandle");
+    if (rc != T0B_OK) return rc;
+    std::memcpy(handle, &h, 64);
+    return T0B_OK;
+}
+
+int32_t t0b_ipc_open(t0b_ctx* ctx, const uint8_t handle[64], uint64_t* dptr) {
+    int32_t rc = precheck(ctx);
+    if (rc != T0B_OK) return rc;
+    if (!dptr || !handle) return set_error(ctx, T0B_ERR_INVALID, "ipc_open: null pointer");
+    cudaIpcMemHandle_t h;
+    std::memcpy(&h, handle, 64);
+    void* p = nullptr;
+    rc = check_cuda(ctx, cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess), "cudaIpcOpenMemHandle");
+    if (rc != T0B_OK) return rc;
+    *dptr = reinterpret_cast<uint64_t>(p);
+    return T0B_OK;
+}
+
+int32_t t0b_ipc_close(t0b_ctx* ctx, uint64_t dptr) {
+    if (!ctx || !dptr) return T0B_ERR_INVALID;
+    cudaSetDevice(ctx->device);
+    cudaStreamSynchronize(ctx->stream);
+    cudaError_t e = cudaIpcCloseMemHandle(reinterpret_cast<void*>(dptr));
+    if (e != cudaSuccess && !ctx->poisoned) return check_cuda(ctx, e, "cudaIpcCloseMemHandle");
+    return T0B_OK;
+}
 
 // ------------------------------------------------------------------------------------------------ graphs
 

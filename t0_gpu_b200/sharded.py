@@ -1,0 +1,114 @@
+"""Column-sharded large GEMM over the GPUs of one node, one process per GPU.
+
+B is split into contiguous N-column blocks, A is replicated, rank g computes C[:, block g].  The output
+all-gather is folded into the GEMM epilogue: every rank holds a full row-major C[M, N] buffer that its peers
+map through CUDA IPC, and the kernel stores each finished tile into its own buffer and straight into every
+peer's buffer over NVLink (plain peer stores from the epilogue warps), so the transfer overlaps the math
+tile by tile and no separate collective runs.  `torch.distributed` is used for the rendezvous only
+(exchange of the 64-byte IPC handles, barriers).
+
+There is no counterpart in the reference (single GPU; multi-GPU is a roadmap item there).
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+from typing import List, Optional, Sequence
+
+from ._lib import lib
+from .gemm_gen import GemmConfig
+from .gpu_context import OUT_BF16, OUT_F32, GpuBuffer, GpuRuntime
+
+
+@dataclass(frozen=True)
+class ColumnShard:
+    rank: int
+    world: int
+    col0: int       # first column of this rank's block
+    n_local: int    # width of the block
+
+
+def column_shard(n: int, world: int, rank: int, align: int = 64) -> ColumnShard:
+    """Contiguous column blocks, widths multiples of `align` except possibly the last non-empty one.
+
+    Blocks are as even as the alignment allows; with N a multiple of world*align every block is N/world.
+    Trailing ranks may get an empty block when N is small."""
+    if world < 1 or not (0 <= rank < world) or n < 0 or align < 1:
+        raise ValueError(f"column_shard: bad arguments n={n} world={world} rank={rank} align={align}")
+    units = (n + align - 1) // align            # aligned units, the last may be partial
+    base, extra = divmod(units, world)
+    u0 = rank * base + min(rank, extra)
+    u1 = u0 + base + (1 if rank < extra else 0)
+    col0 = min(u0 * align, n)
+    col1 = min(u1 * align, n)
+    return ColumnShard(rank, world, col0, col1 - col0)
+
+
+def exchange_handles(handle: bytes, group=None) -> List[bytes]:
+    """All-gather one small byte string per rank over torch.distributed (any backend)."""
+    import torch.distributed as dist
+
+    world = dist.get_world_size(group)
+    out: List[Optional[bytes]] = [None] * world
+    dist.all_gather_object(out, handle, group=group)
+    return [bytes(h) for h in out]
+
+
+class ColumnShardedGemm:
+    """C[M, N] = A[M, K] * B[K, N] with B column-sharded; each rank ends with the full C.
+
+    a:        this rank's copy of A (bf16, [M, K] row-major)
+    b_shard:  B[:, col0 : col0 + n_local] as its own row-major [K, n_local] buffer (bf16)
+    c:        this rank's full output buffer [M, N] (bf16 or f32), from GpuRuntime.alloc
+    """
+
+    def __init__(self, rt: GpuRuntime, m: int, n: int, k: int, out_dtype: int = OUT_BF16, group=None,
+                 cfg: Optional[GemmConfig] = None):
+        import torch.distributed as dist
+
+        self.rt, self.m, self.n, self.k, self.out_dtype, self.group, self.cfg = rt, m, n, k, out_dtype, group, cfg
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.shard = column_shard(n, self.world, self.rank)
+        elem = 2 if out_dtype == OUT_BF16 else 4
+        self.c = rt.alloc(m * n * elem)
+        self._peer_ptrs: List[int] = []
+        self._opened: List[int] = []
+        self._map_peers()
+
+    def _map_peers(self) -> None:
+        if self.world == 1:
+            self._peer_ptrs = [self.c.gpu_addr()]
+            return
+        h = (C.c_uint8 * 64)()
+        self.rt._check(lib().t0b_ipc_export(self.rt.handle, self.c.gpu_addr(), h))
+        handles = exchange_handles(bytes(h), self.group)
+        ptrs = []
+        for r, hb in enumerate(handles):
+            if r == self.rank:
+                ptrs.append(self.c.gpu_addr())
+                continue
+            p = C.c_uint64()
+            blob = (C.c_uint8 * 64).from_buffer_copy(hb)
+            self.rt._check(lib().t0b_ipc_open(self.rt.handle, blob, C.byref(p)))
+            ptrs.append(p.value)
+            self._opened.append(p.value)
+        # Own buffer first: destination 0 is the local store.
+        self._peer_ptrs = [ptrs[self.rank]] + [p for r, p in enumerate(ptrs) if r != self.rank]
+
+    def run(self, a: GpuBuffer, b_shard: GpuBuffer, async_: bool = True, gather: bool = True) -> None:
+        """Launch this rank's GEMM.  With gather=False only the local C is written (GEMM-only timing)."""
+        s = self.shard
+        if s.n_local == 0:
+            return
+        dsts = self._peer_ptrs if gather else self._peer_ptrs[:1]
+        arr = (C.c_uint64 * len(dsts))(*dsts)
+        cp = C.byref(self.cfg.to_c()) if self.cfg is not None else None
+        self.rt._check(lib().t0b_gemm_multi_dst(self.rt.handle, cp, 0, 0, a.gpu_addr(), b_shard.gpu_addr(), arr,
+                                                len(dsts), self.m, s.n_local, self.k, self.k, s.n_local, self.n,
+                                                s.col0, self.out_dtype, int(async_)))
+
+    def close(self) -> None:
+        for p in self._opened:
+            lib().t0b_ipc_close(self.rt.handle, p)
+        self._opened = []
