@@ -198,7 +198,9 @@ def run_single(args, local_rank):
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     rt = t.GpuRuntime(local_rank)
-    stream = torch.cuda.current_stream()
+    # A dedicated (non-default) torch stream carries both the library's launches and the timing events.
+    stream = torch.cuda.Stream(device=dev)
+    torch.cuda.set_stream(stream)
     rt.set_stream(stream.cuda_stream)
     L = lib()
 
@@ -316,7 +318,8 @@ def run_multi(args, rank, local_rank, world):
     dev = torch.device("cuda", local_rank)
     dist.init_process_group("nccl", device_id=dev)
     rt = t.GpuRuntime(local_rank)
-    stream = torch.cuda.current_stream()
+    stream = torch.cuda.Stream(device=dev)
+    torch.cuda.set_stream(stream)
     rt.set_stream(stream.cuda_stream)
     L = lib()
 
