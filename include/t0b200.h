@@ -253,6 +253,19 @@ T0B_API int32_t t0b_rmsnorm_bwd(t0b_ctx* ctx, uint64_t dy, uint64_t x, uint64_t 
                                 uint64_t scratch, size_t scratch_bytes, uint32_t rows, uint32_t cols, float eps,
                                 int32_t async);
 T0B_API size_t t0b_rmsnorm_bwd_scratch_bytes(uint32_t rows, uint32_t cols);
+/* RMSNorm backward (dx and dgamma, same results as t0b_rmsnorm_bwd) for callers that cannot allocate device
+ * memory -- a host runtime that handed its whole device budget to fixed buffers at start-up, or a step loop that
+ * must avoid the device-wide synchronisation cudaMalloc / cudaFree bring -- and so have no scratch to pass.
+ * Has no counterpart in the reference.  The dgamma scratch lives in a 2 MiB array inside the library image
+ * (resident on every GPU that loads the library until the process exits); nothing is allocated or freed by this
+ * call.  Limit: rows + 64 * cols <= 524288 floats (for example 1024 x 4096, or 8192 x 8064); larger problems are
+ * rejected with T0B_ERR_INVALID and must use t0b_rmsnorm_bwd.  The first call on a device looks up the array's
+ * device address; make that first call outside any stream capture.  All calls on one GPU share the array
+ * (whatever the context or stream): two calls that overlap on the GPU race on it, so keep them ordered.  The
+ * array keeps the previous call's contents; every value read is rewritten first, so no clearing is needed.
+ * dx may be 0 (dgamma only). */
+T0B_API int32_t t0b_rmsnorm_bwd_noalloc(t0b_ctx* ctx, uint64_t dy, uint64_t x, uint64_t weight, uint64_t dx,
+                                        uint64_t dgamma, uint32_t rows, uint32_t cols, float eps, int32_t async);
 /* Row softmax forward / backward, any column count (src/t0/softmax_kernels.rs:38-146; cols <= 256 there). */
 T0B_API int32_t t0b_softmax_fwd(t0b_ctx* ctx, uint64_t x, uint64_t y, uint32_t rows, uint32_t cols, int32_t async);
 T0B_API int32_t t0b_softmax_bwd(t0b_ctx* ctx, uint64_t dy, uint64_t y, uint64_t dx, uint32_t rows, uint32_t cols,

@@ -86,6 +86,7 @@ SIGNATURES = {
     "t0b_rmsnorm_fwd": (_i32, [_ctx, _u64, _u64, _u64, _u64, _u32, _u32, _f, _i32]),
     "t0b_rmsnorm_bwd": (_i32, [_ctx, _u64, _u64, _u64, _u64, _u64, _u64, _sz, _u32, _u32, _f, _i32]),
     "t0b_rmsnorm_bwd_scratch_bytes": (_sz, [_u32, _u32]),
+    "t0b_rmsnorm_bwd_noalloc": (_i32, [_ctx, _u64, _u64, _u64, _u64, _u64, _u32, _u32, _f, _i32]),
     "t0b_softmax_fwd": (_i32, [_ctx, _u64, _u64, _u32, _u32, _i32]),
     "t0b_softmax_bwd": (_i32, [_ctx, _u64, _u64, _u64, _u32, _u32, _i32]),
     "t0b_softmax_ce": (_i32, [_ctx, _u64, _u64, _u64, _u64, _u32, _u32, _u64, _f, _i32]),

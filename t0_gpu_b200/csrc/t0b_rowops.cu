@@ -473,6 +473,72 @@ int32_t t0b_rmsnorm_bwd(t0b_ctx* ctx, uint64_t dy, uint64_t x, uint64_t weight, 
     return finish(ctx, async, "rmsnorm_bwd");
 }
 
+// ------------------------------------------------------------------------------------------------
+// RMSNorm backward for callers that cannot allocate device memory.
+//
+// Some users of this library own no allocator they may call at this point: a host runtime that reserved its
+// whole device budget at start-up and hands out fixed buffers only (the reference's runtime keeps such a VRAM
+// pool), or a training loop that must not hit the device-wide synchronisation cudaMalloc / cudaFree imply in
+// the middle of a step.  They can pass inputs and outputs, but have nowhere to get the dgamma scratch from.
+// This entry point keeps that scratch inside the library image instead: a fixed array in device global
+// memory, 2 MiB, present on every GPU that loads the library until the process exits.
+//
+// The array's name is only a host-side stand-in for the symbol; the device address is looked up with
+// cudaGetSymbolAddress, once per device, with that device current, on the first call for that device.
+// Make that first call outside any stream capture.
+constexpr size_t kNoAllocScratchFloats = 512u * 1024u;   // 2 MiB
+static __device__ __align__(256) float g_rmsnorm_bwd_scratch[kNoAllocScratchFloats];
+static float* g_rmsnorm_bwd_scratch_addr[64] = {};
+
+int32_t t0b_rmsnorm_bwd_noalloc(t0b_ctx* ctx, uint64_t dy, uint64_t x, uint64_t weight, uint64_t dx, uint64_t dgamma,
+                                uint32_t rows, uint32_t cols, float eps, int32_t async) {
+    int32_t rc = precheck(ctx);   // makes ctx->device the current device
+    if (rc != T0B_OK) return rc;
+    if (cols == 0 || !dy || !x || !weight || !dgamma)
+        return set_error(ctx, T0B_ERR_INVALID, "rmsnorm_bwd_noalloc: null pointer or zero cols");
+    const size_t need = static_cast<size_t>(rows) + static_cast<size_t>(kDgammaRowBlocks) * cols;
+    if (need > kNoAllocScratchFloats)
+        return set_error(ctx, T0B_ERR_INVALID,
+                         "rmsnorm_bwd_noalloc: rows + %u*cols = %zu floats exceeds the built-in scratch of %zu floats "
+                         "(2 MiB); use t0b_rmsnorm_bwd with caller-provided scratch",
+                         kDgammaRowBlocks, need, kNoAllocScratchFloats);
+    if (ctx->device < 0 || ctx->device >= 64) return set_error(ctx, T0B_ERR_INVALID, "rmsnorm_bwd_noalloc: device index out of range");
+    if (rows == 0) return check_cuda(ctx, cudaMemsetAsync(reinterpret_cast<void*>(dgamma), 0, static_cast<size_t>(cols) * 4, ctx->stream),
+                                     "cudaMemsetAsync(dgamma)");
+    float* scratch = nullptr;
+    {
+        std::lock_guard<std::recursive_mutex> lk(ctx->mu);
+        scratch = g_rmsnorm_bwd_scratch_addr[ctx->device];
+        if (!scratch) {
+            rc = check_cuda(ctx, cudaGetSymbolAddress(reinterpret_cast<void**>(&scratch), g_rmsnorm_bwd_scratch),
+                            "cudaGetSymbolAddress(rmsnorm scratch)");
+            if (rc != T0B_OK) return rc;
+            g_rmsnorm_bwd_scratch_addr[ctx->device] = scratch;
+        }
+    }
+    // Every float the later stages read is written first by an earlier stage of this same call (inv_rms by the
+    // dx stage, the used partial rows by the partial stage), so nothing left over from a previous call is seen
+    // and nothing needs clearing.
+    float* inv = scratch;
+    float* partial = scratch + rows;
+    const int threads = cols >= 2048 ? kRowThreads : (cols >= 512 ? 128 : 32);
+    rmsnorm_bwd_dx_kernel<<<rows, threads, 0, ctx->stream>>>(reinterpret_cast<const float*>(dy), reinterpret_cast<const float*>(x),
+                                                             reinterpret_cast<const float*>(weight), reinterpret_cast<float*>(dx),
+                                                             inv, cols, eps);
+    rc = check_cuda(ctx, cudaGetLastError(), "rmsnorm_bwd_noalloc dx launch");
+    if (rc != T0B_OK) return rc;
+    const uint32_t nblocks = std::min(kDgammaRowBlocks, rows);
+    const uint32_t rpb = (rows + nblocks - 1) / nblocks;
+    const uint32_t used = (rows + rpb - 1) / rpb;
+    dim3 grid((cols + 255) / 256, used);
+    rmsnorm_dgamma_partial_kernel<<<grid, 256, 0, ctx->stream>>>(reinterpret_cast<const float*>(dy), reinterpret_cast<const float*>(x),
+                                                                 inv, partial, rows, cols, rpb);
+    rc = check_cuda(ctx, cudaGetLastError(), "rmsnorm_bwd_noalloc partial launch");
+    if (rc != T0B_OK) return rc;
+    rmsnorm_dgamma_final_kernel<<<(cols + 255) / 256, 256, 0, ctx->stream>>>(partial, reinterpret_cast<float*>(dgamma), cols, used);
+    return finish(ctx, async, "rmsnorm_bwd_noalloc", 3);
+}
+
 int32_t t0b_softmax_fwd(t0b_ctx* ctx, uint64_t x, uint64_t y, uint32_t rows, uint32_t cols, int32_t async) {
     int32_t rc = precheck(ctx);
     if (rc != T0B_OK) return rc;
