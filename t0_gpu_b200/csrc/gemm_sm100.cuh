@@ -8,8 +8,8 @@
 // the K tail contributes zeros, :768-787) -- here the zero fill is TMA's out-of-bounds fill, so callers
 // do not have to pad.
 //
-// Roles per CTA (192 threads): warp 0 = TMA producer, warp 1 = TMEM owner + MMA issuer,
-// warps 2..5 = epilogue (TMEM -> registers -> global).  Every wait is bounded: when a wait runs out the
+// Roles per CTA: warp 0 = TMA producer, warp 1 = TMEM owner + MMA issuer, then one group of 4 epilogue
+// warps per accumulator owner (TMEM -> registers -> global); 192 threads, or 320 for the 2-A-tile variant.  Every wait is bounded: when a wait runs out the
 // CTA records a status code, raises its abort flag, drains, frees its TMEM and returns.
 #pragma once
 #include <cuda_bf16.h>
@@ -66,28 +66,39 @@ struct GemmParams {
     unsigned mn_lbo, mn_sbo, mn_kstep;  // descriptor byte offsets for M/N-contiguous operands
     int* status;
     unsigned long long wait_limit_ns;
+    int diag;               // 0 normal; diagnostics only (results are garbage): 1 = loads without MMA, 2 = MMA without loads
 };
 
-constexpr int kBmCta = 128;   // accumulator rows per CTA (TMEM lanes)
+constexpr int kBmCta = 128;   // accumulator rows per MMA per CTA (TMEM lanes)
 constexpr int kBk = 64;       // K block: 64 bf16 = one 128-byte swizzle row
 constexpr int kUmmaK = 16;
-constexpr int kATileBytes = kBmCta * kBk * 2;
-constexpr int kGemmThreads = 192;
+constexpr int kASubTileBytes = kBmCta * kBk * 2;   // one 128-row A tile of a stage
 
-template <int BN, int CG>
+// BN: MMA N (tile width).  CG: CTAs sharing one MMA (1, or 2 = cta_group::2 pair).  MT: 128-row A tiles per CTA.
+//   MT = 1: the two TMEM accumulator slots double-buffer consecutive tiles (epilogue of tile i overlaps the main
+//           loop of tile i+1); tile = (128*CG) x BN.
+//   MT = 2: both slots belong to the same tile, which is (256*CG) x BN: every B tile is used by two MMAs, so the
+//           shared-memory fill traffic per FLOP drops by a quarter; each slot has its own epilogue warp group and
+//           the slots drain in parallel.
+template <int BN, int CG, int MT>
 struct GemmTraits {
     static_assert(BN == 64 || BN == 128 || BN == 256, "BN");
     static_assert(CG == 1 || CG == 2, "CG");
+    static_assert(MT == 1 || MT == 2, "MT");
     static constexpr int kBnCta = BN / CG;               // B rows this CTA loads
     static_assert(kBnCta % 64 == 0, "each CTA's B slice must be whole 64-column swizzle blocks");
+    static constexpr int kATileBytes = MT * kASubTileBytes;
     static constexpr int kBTileBytes = kBnCta * kBk * 2;
     static constexpr int kStageBytes = kATileBytes + kBTileBytes;
     static constexpr int kCtrlBytes = 512;
     static constexpr int kBudget = 227 * 1024 - 1024 - kCtrlBytes;
     static constexpr int kStagesRaw = kBudget / kStageBytes;
     static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
-    static constexpr int kTmemCols = 2 * BN;             // two accumulator buffers
+    static constexpr int kTmemCols = 2 * BN;             // two accumulator slots
     static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + kCtrlBytes;
+    static constexpr int kEpiWarps = 4 * MT;
+    static constexpr int kThreads = 64 + 32 * kEpiWarps;
+    static constexpr int kBm = kBmCta * CG * MT;         // rows of the cluster tile
 };
 
 struct WorkItem {
@@ -204,13 +215,14 @@ __device__ __forceinline__ void store_chunk_bf16(__nv_bfloat16* base, long long 
     }
 }
 
-template <int BN, int CG>
-__global__ void __launch_bounds__(kGemmThreads, 1)
+template <int BN, int CG, int MT>
+__global__ void __launch_bounds__(GemmTraits<BN, CG, MT>::kThreads, 1)
 gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                          const GemmParams p) {
-    using T = GemmTraits<BN, CG>;
+    using T = GemmTraits<BN, CG, MT>;
     constexpr int S = T::kStages;
-    constexpr int BM = kBmCta * CG;
+    constexpr int BM = T::kBm;
+    constexpr int kMmaM = kBmCta * CG;    // rows of one MMA (128 or 256)
 
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw_addr = ptx::smem_u32(smem_raw);
@@ -238,7 +250,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
         }
         for (int a = 0; a < 2; ++a) {
             ptx::mbar_init(tfull_bar(a), 1);
-            ptx::mbar_init(tempty_bar(a), 4 * CG);   // one arrival per epilogue warp of every CTA of the group
+            ptx::mbar_init(tempty_bar(a), 4 * CG);   // one arrival per epilogue warp of the slot, from every CTA of the group
         }
         *abort_flag = 0;
         ptx::fence_mbar_init();
@@ -267,50 +279,44 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
 
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
-        if (lane == 0) {
+        if (lane == 0 && p.diag != 2) {
             int s = 0;
             uint32_t ph = 0;
             bool ok = true;
             for (int w = cluster_id; w < num_work && ok; w += num_clusters) {
                 const WorkItem wi = decode_work(p, w, BM, BN);
-                const int m0_cta = wi.m0 + static_cast<int>(cta_rank) * kBmCta;
-                const int n0_cta = wi.n0 + static_cast<int>(cta_rank) * T::kBnCta;
+                int m0_cta = wi.m0 + static_cast<int>(cta_rank) * kBmCta;
+                int n0_cta = wi.n0 + static_cast<int>(cta_rank) * T::kBnCta;
+                if (p.diag == 3) { m0_cta = static_cast<int>(cta_rank) * kBmCta; n0_cta = static_cast<int>(cta_rank) * T::kBnCta; }
                 for (int kb = wi.kb_begin; kb < wi.kb_end; ++kb) {
                     if (!bounded_wait(empty_bar(s), ph ^ 1u, ctl, DEV_TIMEOUT_EMPTY)) { ok = false; break; }
-                    if (is_leader) ptx::mbar_arrive_expect_tx(full_bar(s), CG * T::kStageBytes);
+                    if (is_leader) ptx::mbar_arrive_expect_tx(full_bar(s), p.diag == 4 ? CG * T::kATileBytes : CG * T::kStageBytes);
                     const uint32_t a_dst = smem_base + s * T::kStageBytes;
-                    const uint32_t b_dst = a_dst + kATileBytes;
+                    const uint32_t b_dst = a_dst + T::kATileBytes;
                     const int k0 = kb * kBk;
-                    if constexpr (CG == 1) {
-                        const uint32_t bar = full_bar(s);
-                        if (!p.a_mn_major) {
-                            ptx::tma_load_2d(a_dst, &tmap_a, bar, k0, m0_cta);
-                        } else {
-                            ptx::tma_load_2d(a_dst, &tmap_a, bar, m0_cta, k0);
-                            ptx::tma_load_2d(a_dst + 8192, &tmap_a, bar, m0_cta + 64, k0);
-                        }
-                        if (!p.b_mn_major) {
-                            ptx::tma_load_2d(b_dst, &tmap_b, bar, k0, n0_cta);
-                        } else {
+                    // The pair's barrier lives in CTA 0; a single CTA uses its own.
+                    const uint32_t bar = (CG == 2) ? ptx::mapa(full_bar(s), 0) : full_bar(s);
+                    auto load = [&](uint32_t dst, const CUtensorMap* m, int c0, int c1) {
+                        if constexpr (CG == 1) ptx::tma_load_2d(dst, m, bar, c0, c1);
+                        else ptx::tma_load_2d_pair(dst, m, bar, c0, c1);
+                    };
 #pragma unroll
-                            for (int j = 0; j < T::kBnCta / 64; ++j)
-                                ptx::tma_load_2d(b_dst + j * 8192, &tmap_b, bar, n0_cta + j * 64, k0);
+                    for (int mt = 0; mt < MT; ++mt) {
+                        const int m_sub = m0_cta + mt * kMmaM;
+                        const uint32_t dst = a_dst + mt * kASubTileBytes;
+                        if (!p.a_mn_major) {
+                            load(dst, &tmap_a, k0, m_sub);
+                        } else {
+                            load(dst, &tmap_a, m_sub, k0);
+                            load(dst + 8192, &tmap_a, m_sub + 64, k0);
                         }
+                    }
+                    if (p.diag == 4) {
+                    } else if (!p.b_mn_major) {
+                        load(b_dst, &tmap_b, k0, n0_cta);
                     } else {
-                        const uint32_t bar = ptx::mapa(full_bar(s), 0);   // the pair's barrier lives in CTA 0
-                        if (!p.a_mn_major) {
-                            ptx::tma_load_2d_pair(a_dst, &tmap_a, bar, k0, m0_cta);
-                        } else {
-                            ptx::tma_load_2d_pair(a_dst, &tmap_a, bar, m0_cta, k0);
-                            ptx::tma_load_2d_pair(a_dst + 8192, &tmap_a, bar, m0_cta + 64, k0);
-                        }
-                        if (!p.b_mn_major) {
-                            ptx::tma_load_2d_pair(b_dst, &tmap_b, bar, k0, n0_cta);
-                        } else {
 #pragma unroll
-                            for (int j = 0; j < T::kBnCta / 64; ++j)
-                                ptx::tma_load_2d_pair(b_dst + j * 8192, &tmap_b, bar, n0_cta + j * 64, k0);
-                        }
+                        for (int j = 0; j < T::kBnCta / 64; ++j) load(b_dst + j * 8192, &tmap_b, n0_cta + j * 64, k0);
                     }
                     if (++s == S) { s = 0; ph ^= 1u; }
                 }
@@ -328,49 +334,73 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
         if (lane == 0 && is_leader) {
             const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(p.a_mn_major) << 15) |
                                    (static_cast<uint32_t>(p.b_mn_major) << 16) | (static_cast<uint32_t>(BN >> 3) << 17) |
-                                   (static_cast<uint32_t>(BM >> 4) << 24);
+                                   (static_cast<uint32_t>(kMmaM >> 4) << 24);
             const uint32_t a_lbo = p.a_mn_major ? p.mn_lbo : 16u, a_sbo = p.a_mn_major ? p.mn_sbo : 1024u;
             const uint32_t b_lbo = p.b_mn_major ? p.mn_lbo : 16u, b_sbo = p.b_mn_major ? p.mn_sbo : 1024u;
             const uint32_t a_kstep = p.a_mn_major ? p.mn_kstep : 32u;
             const uint32_t b_kstep = p.b_mn_major ? p.mn_kstep : 32u;
             int s = 0;
             uint32_t ph = 0;
-            int acc = 0;
-            uint32_t acc_ph = 0;
+            int acc = 0;                       // MT == 1: the slot of this tile
+            uint32_t slot_ph[2] = {0u, 0u};    // phase of each accumulator slot
             bool ok = true;
             for (int w = cluster_id; w < num_work && ok; w += num_clusters) {
                 const WorkItem wi = decode_work(p, w, BM, BN);
-                if (!bounded_wait(tempty_bar(acc), acc_ph ^ 1u, ctl, DEV_TIMEOUT_TMEM_EMPTY)) { ok = false; break; }
-                ptx::tc_fence_after();
-                const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
+                if constexpr (MT == 1) {
+                    if (!bounded_wait(tempty_bar(acc), slot_ph[acc] ^ 1u, ctl, DEV_TIMEOUT_TMEM_EMPTY)) { ok = false; break; }
+                    ptx::tc_fence_after();
+                }
                 for (int kb = wi.kb_begin; kb < wi.kb_end; ++kb) {
-                    if (!bounded_wait(full_bar(s), ph, ctl, DEV_TIMEOUT_FULL)) { ok = false; break; }
+                    if (p.diag != 2 && !bounded_wait(full_bar(s), ph, ctl, DEV_TIMEOUT_FULL)) { ok = false; break; }
                     ptx::tc_fence_after();
                     const uint32_t a_addr = smem_base + s * T::kStageBytes;
-                    const uint32_t b_addr = a_addr + kATileBytes;
+                    const uint32_t b_addr = a_addr + T::kATileBytes;
 #pragma unroll
                     for (int k = 0; k < kBk / kUmmaK; ++k) {
-                        const uint64_t adesc = make_smem_desc(a_addr + k * a_kstep, a_lbo, a_sbo);
                         const uint64_t bdesc = make_smem_desc(b_addr + k * b_kstep, b_lbo, b_sbo);
-                        ptx::mma_f16<CG>(d_tmem, adesc, bdesc, idesc, (kb > wi.kb_begin || k > 0) ? 1u : 0u);
+#pragma unroll
+                        for (int mt = 0; mt < MT; ++mt) {
+                            const int slot = (MT == 1) ? acc : mt;
+                            if (MT == 2 && kb == wi.kb_begin && k == 0) {
+                                // First write into this slot for the tile: its previous contents must be drained.
+                                if (!bounded_wait(tempty_bar(slot), slot_ph[slot] ^ 1u, ctl, DEV_TIMEOUT_TMEM_EMPTY)) { ok = false; break; }
+                                ptx::tc_fence_after();
+                            }
+                            const uint64_t adesc = make_smem_desc(a_addr + mt * kASubTileBytes + k * a_kstep, a_lbo, a_sbo);
+                            if (p.diag != 1)
+                                ptx::mma_f16<CG>(tmem_base + static_cast<uint32_t>(slot * BN), adesc, bdesc, idesc,
+                                                 (kb > wi.kb_begin || k > 0) ? 1u : 0u);
+                        }
+                        if (!ok) break;
                     }
+                    if (!ok) break;
                     if constexpr (CG == 1) ptx::mma_commit(empty_bar(s));
                     else ptx::mma_commit_pair(empty_bar(s), 0x3);
                     if (++s == S) { s = 0; ph ^= 1u; }
                 }
                 if (!ok) break;
-                if constexpr (CG == 1) ptx::mma_commit(tfull_bar(acc));
-                else ptx::mma_commit_pair(tfull_bar(acc), 0x3);
-                acc ^= 1;
-                if (acc == 0) acc_ph ^= 1u;
+                if constexpr (MT == 1) {
+                    if constexpr (CG == 1) ptx::mma_commit(tfull_bar(acc));
+                    else ptx::mma_commit_pair(tfull_bar(acc), 0x3);
+                    slot_ph[acc] ^= 1u;
+                    acc ^= 1;
+                } else {
+#pragma unroll
+                    for (int slot = 0; slot < 2; ++slot) {
+                        if constexpr (CG == 1) ptx::mma_commit(tfull_bar(slot));
+                        else ptx::mma_commit_pair(tfull_bar(slot), 0x3);
+                        slot_ph[slot] ^= 1u;
+                    }
+                }
             }
         }
         __syncwarp();
     } else {
-        // ------------------------------------------------------------------ epilogue (4 warps, 32 TMEM lanes each)
-        const int q = warp & 3;   // TMEM lane quarter this warp may read
-        int acc = 0;
-        uint32_t acc_ph = 0;
+        // ------------------------------------------------------------------ epilogue: one group of 4 warps per slot owner
+        const int q = warp & 3;              // TMEM lane quarter this warp may read
+        const int group = (warp - 2) >> 2;   // MT == 2: group g drains slot g of every tile
+        int slot = (MT == 2) ? group : 0;
+        uint32_t slot_phase = 0;
         const bool to_slab = p.split_k > 1;
         const long long ld_out = to_slab ? p.ld_partial : p.ldc;
         bool vec_ok;
@@ -386,10 +416,10 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
         const bool need_bias = (epi == EPI_BIAS || epi == EPI_BIAS_RELU) && p.bias != nullptr;
         for (int w = cluster_id; w < num_work; w += num_clusters) {
             const WorkItem wi = decode_work(p, w, BM, BN);
-            if (!bounded_wait(tfull_bar(acc), acc_ph, ctl, DEV_TIMEOUT_TMEM_FULL)) break;
+            if (!bounded_wait(tfull_bar(slot), slot_phase, ctl, DEV_TIMEOUT_TMEM_FULL)) break;
             ptx::tc_fence_after();
-            const int row = wi.m0 + static_cast<int>(cta_rank) * kBmCta + q * 32 + lane;
-            const uint32_t t_row = tmem_base + static_cast<uint32_t>(acc * BN) + (static_cast<uint32_t>(q * 32) << 16);
+            const int row = wi.m0 + (MT == 2 ? group * kMmaM : 0) + static_cast<int>(cta_rank) * kBmCta + q * 32 + lane;
+            const uint32_t t_row = tmem_base + static_cast<uint32_t>(slot * BN) + (static_cast<uint32_t>(q * 32) << 16);
 #pragma unroll 1
             for (int c = 0; c < BN / 32; ++c) {
                 uint32_t raw[32];
@@ -400,8 +430,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                     ptx::tc_fence_before();
                     __syncwarp();
                     if (lane == 0) {
-                        if constexpr (CG == 1) ptx::mbar_arrive(tempty_bar(acc));
-                        else ptx::mbar_arrive_cluster(ptx::mapa(tempty_bar(acc), 0));
+                        if constexpr (CG == 1) ptx::mbar_arrive(tempty_bar(slot));
+                        else ptx::mbar_arrive_cluster(ptx::mapa(tempty_bar(slot), 0));
                     }
                 }
                 const int col0 = wi.n0 + c * 32;
@@ -430,8 +460,12 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                     }
                 }
             }
-            acc ^= 1;
-            if (acc == 0) acc_ph ^= 1u;
+            if constexpr (MT == 1) {
+                slot ^= 1;
+                if (slot == 0) slot_phase ^= 1u;
+            } else {
+                slot_phase ^= 1u;
+            }
         }
     }
 

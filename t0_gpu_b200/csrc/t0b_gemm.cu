@@ -3,6 +3,8 @@
 // (GpuRuntime::ensure_kernel_t0 / dispatch, src/ignis/gpu_context.rs:171-288) and the Ignis GEMM entry
 // points (src/ignis/ops/bf16_matmul.rs:162-308).
 #include <algorithm>
+#include <cmath>
+#include <cstdlib>
 #include <cstring>
 
 #include "gemm_sm100.cuh"
@@ -59,10 +61,10 @@ int32_t get_tmap(t0b_ctx* ctx, uint64_t ptr, uint64_t d0, uint64_t d1, uint64_t 
     return T0B_OK;
 }
 
-template <int BN, int CG>
+template <int BN, int CG, int MT>
 int32_t launch_variant(t0b_ctx* ctx, const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int num_work) {
-    using T = GemmTraits<BN, CG>;
-    auto kfn = gemm_bf16_tcgen05_kernel<BN, CG>;
+    using T = GemmTraits<BN, CG, MT>;
+    auto kfn = gemm_bf16_tcgen05_kernel<BN, CG, MT>;
     static bool configured[64] = {};
     static int max_clusters[64] = {};
     const int dev = ctx->device & 63;
@@ -76,7 +78,7 @@ int32_t launch_variant(t0b_ctx* ctx, const CUtensorMap& ta, const CUtensorMap& t
             if (rc != T0B_OK) return rc;
             cudaLaunchConfig_t qc{};
             qc.gridDim = dim3(ctx->num_sms - (ctx->num_sms % 2), 1, 1);
-            qc.blockDim = dim3(kGemmThreads, 1, 1);
+            qc.blockDim = dim3(T::kThreads, 1, 1);
             qc.dynamicSmemBytes = T::kSmemBytes;
             cudaLaunchAttribute qa[1];
             qa[0].id = cudaLaunchAttributeClusterDimension;
@@ -100,7 +102,7 @@ int32_t launch_variant(t0b_ctx* ctx, const CUtensorMap& ta, const CUtensorMap& t
     const int clusters = std::max(1, std::min(num_work, max_clusters[dev]));
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(clusters * CG, 1, 1);
-    cfg.blockDim = dim3(kGemmThreads, 1, 1);
+    cfg.blockDim = dim3(T::kThreads, 1, 1);
     cfg.dynamicSmemBytes = T::kSmemBytes;
     cfg.stream = ctx->stream;
     cudaLaunchAttribute attrs[1];
@@ -281,22 +283,34 @@ int32_t run_gemm(t0b_ctx* ctx, const GemmCall& g) {
         p.out_bf16 = g.out_bf16;
         p.epilogue = g.epilogue;
         p.raster_along_n = cfg.swap_grid ? 0 : 1;
-        p.group = 8;
+        {
+            // Concurrently running tiles should cover a square-ish patch of C, so that A and B panels are shared
+            // through L2: group * bm ~= (clusters / group) * bn.
+            const double clusters = static_cast<double>(ctx->num_sms) / plan.cta_group;
+            int grp = static_cast<int>(std::lround(std::sqrt(clusters * (cfg.swap_grid ? plan.bn : plan.bm) /
+                                                             static_cast<double>(cfg.swap_grid ? plan.bm : plan.bn))));
+            p.group = std::max(1, std::min(grp, 16));
+        }
         p.mn_lbo = 8192; p.mn_sbo = 1024; p.mn_kstep = 2048;
         p.status = ctx->status_dev;
         p.wait_limit_ns = ctx->wait_limit_ns;
+        {
+            static const int diag = [] { const char* e = getenv("T0B_GEMM_DIAG"); return e ? atoi(e) : 0; }();
+            p.diag = diag;
+        }
         if (g.slabs_only && sk == 1) {
             // One slab: store straight into it as f32.
             p.out_bf16 = 0; p.epilogue = EPI_STORE; p.n_dst = 1; p.ldc = static_cast<long long>(ld_partial);
         }
         const int num_work = p.tiles_m * p.tiles_n * p.split_k;
         if (plan.cta_group == 2) {
-            if (plan.bn == 256) rc = launch_variant<256, 2>(ctx, ta, tb, p, num_work);
-            else rc = launch_variant<128, 2>(ctx, ta, tb, p, num_work);
+            if (plan.m_tiles == 2) rc = launch_variant<256, 2, 2>(ctx, ta, tb, p, num_work);
+            else if (plan.bn == 256) rc = launch_variant<256, 2, 1>(ctx, ta, tb, p, num_work);
+            else rc = launch_variant<128, 2, 1>(ctx, ta, tb, p, num_work);
         } else {
-            if (plan.bn == 256) rc = launch_variant<256, 1>(ctx, ta, tb, p, num_work);
-            else if (plan.bn == 128) rc = launch_variant<128, 1>(ctx, ta, tb, p, num_work);
-            else rc = launch_variant<64, 1>(ctx, ta, tb, p, num_work);
+            if (plan.bn == 256) rc = launch_variant<256, 1, 1>(ctx, ta, tb, p, num_work);
+            else if (plan.bn == 128) rc = launch_variant<128, 1, 1>(ctx, ta, tb, p, num_work);
+            else rc = launch_variant<64, 1, 1>(ctx, ta, tb, p, num_work);
         }
         if (rc != T0B_OK) return rc;
         ++ctx->launches;
@@ -497,7 +511,7 @@ int32_t t0b_tune(t0b_ctx* ctx, uint32_t m, uint32_t n, uint32_t k, int32_t trans
     if (rc == T0B_OK) rc = t0b_alloc(ctx, static_cast<size_t>(m) * n * elem, &c);
     if (rc != T0B_OK) return rc;
     const uint64_t lda = trans_a ? m : k, ldb = trans_b ? k : n;
-    static const char* tiles[] = {"b200_256x256", "b200_256x128", "b200_128x256", "b200_128x128", "b200_128x64"};
+    static const char* tiles[] = {"b200_512x256", "b200_256x256", "b200_256x128", "b200_128x256", "b200_128x128", "b200_128x64"};
     const uint32_t kb_total = (k + 63) / 64;
     float best_ms = 1e30f;
     for (const char* t : tiles) {
@@ -505,7 +519,6 @@ int32_t t0b_tune(t0b_ctx* ctx, uint32_t m, uint32_t n, uint32_t k, int32_t trans
             if (sk > 1 && kb_total / sk < 2) break;
             t0b_gemm_config cfg;
             t0b_config_preset(t, &cfg);
-            cfg.wgp_mode = cfg.tile_m >= 256;
             cfg.split_k = sk > 1 ? sk : 0;
             t0b_gemm_plan plan;
             PlanInput pin{m, n, k, trans_a, trans_b, lda, ldb, a, b, ctx->num_sms};

@@ -55,6 +55,7 @@ const Preset* presets(int* count) {
         {"b200_128x256", make_cfg(128, 256, 64, 192, true, true)},
         {"b200_256x128", make_cfg(256, 128, 64, 192, true, true)},
         {"b200_256x256", make_cfg(256, 256, 64, 192, true, true)},
+        {"b200_512x256", make_cfg(512, 256, 64, 320, true, true)},
     };
     *count = static_cast<int>(sizeof(table) / sizeof(table[0]));
     return table;
@@ -77,9 +78,12 @@ void put_u32(uint8_t* p, uint32_t v) {
     for (int i = 0; i < 4; ++i) p[i] = static_cast<uint8_t>(v >> (8 * i));
 }
 
-int stages_for(uint32_t bn, uint32_t cg) {
-    const int bn_cta = static_cast<int>(bn / cg);
-    const int stage = 128 * 64 * 2 + bn_cta * 64 * 2;
+int stage_bytes(uint32_t bn, uint32_t cg, uint32_t mt) {
+    return static_cast<int>(mt) * 128 * 64 * 2 + static_cast<int>(bn / cg) * 64 * 2;
+}
+
+int stages_for(uint32_t bn, uint32_t cg, uint32_t mt) {
+    const int stage = stage_bytes(bn, cg, mt);
     const int budget = 227 * 1024 - 1024 - 512;
     return std::min(8, budget / stage);
 }
@@ -92,16 +96,17 @@ namespace t0b {
 // factor (larger tiles re-use more of each shared-memory byte); small grids get a power-of-two split-K.
 void default_b200_config(uint32_t m, uint32_t k, uint32_t n, int num_sms, t0b_gemm_config* out) {
     struct Cand {
-        uint32_t cg, bn;
-        double factor;
+        uint32_t bm, cg, bn;
+        double factor;   // measured relative throughput of the tile at large sizes (MMAs narrower than 256 run at reduced rate)
     };
-    static const Cand cands[] = {{2, 256, 1.00}, {2, 128, 0.90}, {1, 256, 0.93}, {1, 128, 0.82}, {1, 64, 0.62}};
+    static const Cand cands[] = {{512, 2, 256, 1.10}, {256, 2, 256, 1.00}, {128, 1, 256, 0.90},
+                                 {256, 2, 128, 0.50}, {128, 1, 128, 0.50}, {128, 1, 64, 0.30}};
     if (num_sms <= 0) num_sms = 148;
     double best = -1.0;
-    Cand pick = cands[3];
+    Cand pick = cands[4];
     uint64_t pick_tiles = 1;
     for (const Cand& c : cands) {
-        const uint64_t bm = 128ull * c.cg;
+        const uint64_t bm = c.bm;
         const uint64_t tiles = ((m + bm - 1) / bm) * ((n + c.bn - 1) / c.bn);
         const uint64_t clusters = static_cast<uint64_t>(num_sms) / c.cg;
         const uint64_t waves = (tiles + clusters - 1) / clusters;
@@ -114,7 +119,7 @@ void default_b200_config(uint32_t m, uint32_t k, uint32_t n, int num_sms, t0b_ge
             pick_tiles = tiles;
         }
     }
-    t0b_gemm_config cfg = make_cfg(128 * pick.cg, pick.bn, 64, 192, true, true);
+    t0b_gemm_config cfg = make_cfg(pick.bm, pick.bn, 64, pick.bm >= 512 ? 320 : 192, true, true);
     cfg.wgp_mode = pick.cg == 2;
     cfg.swap_grid = (m >= n) ? 1 : 0;
     const uint64_t clusters = static_cast<uint64_t>(num_sms) / pick.cg;
@@ -137,9 +142,10 @@ void resolve_plan(const t0b_gemm_config* cfg_in, const PlanInput& in, t0b_gemm_p
     const uint32_t want_n = cfg.tile_n * std::max(1u, cfg.n_col_passes);
     p.bn = want_n <= 64 ? 64 : (want_n <= 128 ? 128 : 256);
     if (p.cta_group == 2 && p.bn < 128) p.bn = 128;
-    p.bm = 128 * p.cta_group;
+    p.m_tiles = (cfg.tile_m >= 512 && p.bn == 256) ? 2 : 1;
+    p.bm = 128 * p.cta_group * p.m_tiles;
     p.bk = 64;
-    p.stages = static_cast<uint32_t>(stages_for(p.bn, p.cta_group));
+    p.stages = static_cast<uint32_t>(stages_for(p.bn, p.cta_group, p.m_tiles));
     const uint32_t kb_total = (in.k + 63) / 64;
     uint32_t sk = std::max(1u, sk_of(&cfg));
     sk = std::min(sk, std::max(1u, kb_total));
@@ -151,7 +157,7 @@ void resolve_plan(const t0b_gemm_config* cfg_in, const PlanInput& in, t0b_gemm_p
     const uint64_t tiles = static_cast<uint64_t>((in.m + p.bm - 1) / p.bm) * ((in.n + p.bn - 1) / p.bn) * p.split_k;
     const uint64_t clusters = static_cast<uint64_t>(num_sms) / p.cta_group;
     p.grid = static_cast<uint32_t>(std::min<uint64_t>(tiles, clusters) * p.cta_group);
-    p.smem_bytes = p.stages * (128 * 64 * 2 + (p.bn / p.cta_group) * 64 * 2) + 1024 + 512;
+    p.smem_bytes = p.stages * stage_bytes(p.bn, p.cta_group, p.m_tiles) + 1024 + 512;
     *out = p;
 }
 
