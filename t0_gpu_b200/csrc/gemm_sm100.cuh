@@ -66,6 +66,7 @@ struct GemmParams {
     unsigned mn_lbo, mn_sbo, mn_kstep;  // descriptor byte offsets for M/N-contiguous operands
     int* status;
     unsigned long long wait_limit_ns;
+    int l2_prefetch;        // > 0: prefetch the K block this many blocks ahead into L2
     int diag;               // 0 normal; diagnostics only (results are garbage): 1 = loads without MMA, 2 = MMA without loads
 };
 
@@ -91,12 +92,13 @@ struct GemmTraits {
     static constexpr int kBTileBytes = kBnCta * kBk * 2;
     static constexpr int kStageBytes = kATileBytes + kBTileBytes;
     static constexpr int kCtrlBytes = 512;
-    static constexpr int kBudget = 227 * 1024 - 1024 - kCtrlBytes;
+    static constexpr int kEpiWarps = 4 * MT;
+    static constexpr int kEpiStagingBytes = kEpiWarps * 4096;   // one 32x32 f32 transpose tile per epilogue warp
+    static constexpr int kBudget = 227 * 1024 - 1024 - kCtrlBytes - kEpiStagingBytes;
     static constexpr int kStagesRaw = kBudget / kStageBytes;
     static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
     static constexpr int kTmemCols = 2 * BN;             // two accumulator slots
-    static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + kCtrlBytes;
-    static constexpr int kEpiWarps = 4 * MT;
+    static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + kCtrlBytes + kEpiStagingBytes;
     static constexpr int kThreads = 64 + 32 * kEpiWarps;
     static constexpr int kBm = kBmCta * CG * MT;         // rows of the cluster tile
 };
@@ -215,6 +217,60 @@ __device__ __forceinline__ void store_chunk_bf16(__nv_bfloat16* base, long long 
     }
 }
 
+
+// Coalesced stores of one warp's 32x32 chunk (lane i holds row i) through a 4 KiB shared-memory transpose tile.
+// 16-byte pieces are XOR-swizzled by row so both the row-wise writes and the line-wise reads are conflict-free.
+// Each global store instruction then writes whole 128-byte (f32) or 64-byte (bf16) row segments.
+__device__ __forceinline__ void stage_chunk_f32(uint32_t stage, int lane, const float (&v)[32]) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const uint32_t addr = stage + lane * 128 + ((j ^ (lane & 7)) << 4);
+        asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(v[4 * j]), "f"(v[4 * j + 1]),
+                     "f"(v[4 * j + 2]), "f"(v[4 * j + 3])
+                     : "memory");
+    }
+}
+__device__ __forceinline__ void flush_chunk_f32(uint32_t stage, int lane, float* base, long long ld, int row0, int col0,
+                                                int M, int N) {
+    const int c = lane & 7;
+#pragma unroll
+    for (int t = 0; t < 8; ++t) {
+        const int r = t * 4 + (lane >> 3);
+        const uint32_t addr = stage + r * 128 + ((c ^ (r & 7)) << 4);
+        float4 q;
+        asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(q.x), "=f"(q.y), "=f"(q.z), "=f"(q.w) : "r"(addr));
+        if (row0 + r < M && col0 + c * 4 < N)   // N % 4 == 0 on this path, so a piece is all in or all out
+            *reinterpret_cast<float4*>(base + static_cast<long long>(row0 + r) * ld + col0 + c * 4) = q;
+    }
+}
+__device__ __forceinline__ void stage_chunk_bf16(uint32_t stage, int lane, const float (&v)[32]) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        __nv_bfloat162 h0 = __floats2bfloat162_rn(v[8 * j + 0], v[8 * j + 1]);
+        __nv_bfloat162 h1 = __floats2bfloat162_rn(v[8 * j + 2], v[8 * j + 3]);
+        __nv_bfloat162 h2 = __floats2bfloat162_rn(v[8 * j + 4], v[8 * j + 5]);
+        __nv_bfloat162 h3 = __floats2bfloat162_rn(v[8 * j + 6], v[8 * j + 7]);
+        const uint32_t addr = stage + lane * 64 + ((j ^ ((lane >> 1) & 3)) << 4);
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(*reinterpret_cast<uint32_t*>(&h0)),
+                     "r"(*reinterpret_cast<uint32_t*>(&h1)), "r"(*reinterpret_cast<uint32_t*>(&h2)),
+                     "r"(*reinterpret_cast<uint32_t*>(&h3))
+                     : "memory");
+    }
+}
+__device__ __forceinline__ void flush_chunk_bf16(uint32_t stage, int lane, __nv_bfloat16* base, long long ld, int row0,
+                                                 int col0, int M, int N) {
+    const int c = lane & 3;
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+        const int r = t * 8 + (lane >> 2);
+        const uint32_t addr = stage + r * 64 + ((c ^ ((r >> 1) & 3)) << 4);
+        uint4 q;
+        asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(q.x), "=r"(q.y), "=r"(q.z), "=r"(q.w) : "r"(addr));
+        if (row0 + r < M && col0 + c * 8 < N)   // N % 8 == 0 on this path
+            *reinterpret_cast<uint4*>(base + static_cast<long long>(row0 + r) * ld + col0 + c * 8) = q;
+    }
+}
+
 template <int BN, int CG, int MT>
 __global__ void __launch_bounds__(GemmTraits<BN, CG, MT>::kThreads, 1)
 gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
@@ -283,13 +339,17 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
             int s = 0;
             uint32_t ph = 0;
             bool ok = true;
+            long long t_empty = 0;
+            const long long tp_begin = clock64();
             for (int w = cluster_id; w < num_work && ok; w += num_clusters) {
                 const WorkItem wi = decode_work(p, w, BM, BN);
                 int m0_cta = wi.m0 + static_cast<int>(cta_rank) * kBmCta;
                 int n0_cta = wi.n0 + static_cast<int>(cta_rank) * T::kBnCta;
                 if (p.diag == 3) { m0_cta = static_cast<int>(cta_rank) * kBmCta; n0_cta = static_cast<int>(cta_rank) * T::kBnCta; }
                 for (int kb = wi.kb_begin; kb < wi.kb_end; ++kb) {
+                    const long long tq0 = clock64();
                     if (!bounded_wait(empty_bar(s), ph ^ 1u, ctl, DEV_TIMEOUT_EMPTY)) { ok = false; break; }
+                    t_empty += clock64() - tq0;
                     if (is_leader) ptx::mbar_arrive_expect_tx(full_bar(s), p.diag == 4 ? CG * T::kATileBytes : CG * T::kStageBytes);
                     const uint32_t a_dst = smem_base + s * T::kStageBytes;
                     const uint32_t b_dst = a_dst + T::kATileBytes;
@@ -318,8 +378,28 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
 #pragma unroll
                         for (int j = 0; j < T::kBnCta / 64; ++j) load(b_dst + j * 8192, &tmap_b, n0_cta + j * 64, k0);
                     }
+                    if (p.l2_prefetch > 0 && kb + p.l2_prefetch < wi.kb_end) {
+                        // Pull a K block further ahead into L2 so the later shared-memory fill finds it there.
+                        const int kp = (kb + p.l2_prefetch) * kBk;
+#pragma unroll
+                        for (int mt = 0; mt < MT; ++mt) {
+                            const int m_sub = m0_cta + mt * kMmaM;
+                            if (!p.a_mn_major) ptx::tma_prefetch_2d(&tmap_a, kp, m_sub);
+                            else { ptx::tma_prefetch_2d(&tmap_a, m_sub, kp); ptx::tma_prefetch_2d(&tmap_a, m_sub + 64, kp); }
+                        }
+                        if (!p.b_mn_major) ptx::tma_prefetch_2d(&tmap_b, kp, n0_cta);
+                        else {
+#pragma unroll
+                            for (int j = 0; j < T::kBnCta / 64; ++j) ptx::tma_prefetch_2d(&tmap_b, n0_cta + j * 64, kp);
+                        }
+                    }
                     if (++s == S) { s = 0; ph ^= 1u; }
                 }
+            }
+            if (p.diag == 5 && blockIdx.x == 0) {
+                volatile int* dbg = reinterpret_cast<volatile int*>(p.status);
+                dbg[5] = static_cast<int>(t_empty >> 4);
+                dbg[6] = static_cast<int>((clock64() - tp_begin) >> 4);
             }
             // Tail: every slot must have been released, so no MMA-completion arrival can target this
             // CTA's shared memory after it exits.
@@ -344,6 +424,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
             int acc = 0;                       // MT == 1: the slot of this tile
             uint32_t slot_ph[2] = {0u, 0u};    // phase of each accumulator slot
             bool ok = true;
+            long long t_full = 0, t_tempty = 0;
+            const long long t_begin = clock64();
             for (int w = cluster_id; w < num_work && ok; w += num_clusters) {
                 const WorkItem wi = decode_work(p, w, BM, BN);
                 if constexpr (MT == 1) {
@@ -351,7 +433,9 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                     ptx::tc_fence_after();
                 }
                 for (int kb = wi.kb_begin; kb < wi.kb_end; ++kb) {
+                    const long long tw0 = clock64();
                     if (p.diag != 2 && !bounded_wait(full_bar(s), ph, ctl, DEV_TIMEOUT_FULL)) { ok = false; break; }
+                    t_full += clock64() - tw0;
                     ptx::tc_fence_after();
                     const uint32_t a_addr = smem_base + s * T::kStageBytes;
                     const uint32_t b_addr = a_addr + T::kATileBytes;
@@ -363,7 +447,9 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                             const int slot = (MT == 1) ? acc : mt;
                             if (MT == 2 && kb == wi.kb_begin && k == 0) {
                                 // First write into this slot for the tile: its previous contents must be drained.
+                                const long long te0 = clock64();
                                 if (!bounded_wait(tempty_bar(slot), slot_ph[slot] ^ 1u, ctl, DEV_TIMEOUT_TMEM_EMPTY)) { ok = false; break; }
+                                t_tempty += clock64() - te0;
                                 ptx::tc_fence_after();
                             }
                             const uint64_t adesc = make_smem_desc(a_addr + mt * kASubTileBytes + k * a_kstep, a_lbo, a_sbo);
@@ -393,6 +479,12 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                     }
                 }
             }
+            if (p.diag == 5 && blockIdx.x == 0) {
+                volatile int* dbg = reinterpret_cast<volatile int*>(p.status);
+                dbg[2] = static_cast<int>(t_full >> 4);
+                dbg[3] = static_cast<int>(t_tempty >> 4);
+                dbg[4] = static_cast<int>((clock64() - t_begin) >> 4);
+            }
         }
         __syncwarp();
     } else {
@@ -414,11 +506,18 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
         }
         const int epi = to_slab ? EPI_STORE : p.epilogue;
         const bool need_bias = (epi == EPI_BIAS || epi == EPI_BIAS_RELU) && p.bias != nullptr;
+        // The transposing path needs whole 16-byte pieces inside [0, N): N % 4 (f32) or N % 8 (bf16).
+        const bool out16 = !to_slab && p.out_bf16;
+        const bool staged = vec_ok && (p.N % (out16 ? 8 : 4) == 0);
+        const uint32_t stage = ctrl + T::kCtrlBytes + static_cast<uint32_t>(warp - 2) * 4096u;
+        long long t_drain = 0, t_store = 0;
         for (int w = cluster_id; w < num_work; w += num_clusters) {
             const WorkItem wi = decode_work(p, w, BM, BN);
             if (!bounded_wait(tfull_bar(slot), slot_phase, ctl, DEV_TIMEOUT_TMEM_FULL)) break;
+            const long long td0 = clock64();
             ptx::tc_fence_after();
-            const int row = wi.m0 + (MT == 2 ? group * kMmaM : 0) + static_cast<int>(cta_rank) * kBmCta + q * 32 + lane;
+            const int row0 = wi.m0 + (MT == 2 ? group * kMmaM : 0) + static_cast<int>(cta_rank) * kBmCta + q * 32;
+            const int row = row0 + lane;
             const uint32_t t_row = tmem_base + static_cast<uint32_t>(slot * BN) + (static_cast<uint32_t>(q * 32) << 16);
 #pragma unroll 1
             for (int c = 0; c < BN / 32; ++c) {
@@ -433,10 +532,39 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                         if constexpr (CG == 1) ptx::mbar_arrive(tempty_bar(slot));
                         else ptx::mbar_arrive_cluster(ptx::mapa(tempty_bar(slot), 0));
                     }
+                    t_drain += clock64() - td0;
                 }
                 const int col0 = wi.n0 + c * 32;
                 const int ncols = p.N - col0;
-                if (row < p.M && ncols > 0) {
+                if (staged) {
+                    if (row0 < p.M && ncols > 0) {   // warp-uniform
+                        float v[32];
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(raw[j]);
+                        if (epi != EPI_STORE) {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) {
+                                float b = 0.0f;
+                                if (need_bias && j < ncols) b = __ldg(p.bias + col0 + j);
+                                v[j] = apply_epilogue(v[j], epi, b, p.alpha);
+                            }
+                        }
+                        __syncwarp();   // the previous chunk's reads of the staging tile are done
+                        if (out16) stage_chunk_bf16(stage, lane, v);
+                        else stage_chunk_f32(stage, lane, v);
+                        __syncwarp();
+                        if (to_slab) {
+                            flush_chunk_f32(stage, lane, p.partial + static_cast<long long>(wi.split) * p.slab_stride, ld_out,
+                                            row0, col0, p.M, p.N);
+                        } else if (out16) {
+                            for (int d = 0; d < p.n_dst; ++d)
+                                flush_chunk_bf16(stage, lane, static_cast<__nv_bfloat16*>(p.c_dst[d]), ld_out, row0, col0, p.M, p.N);
+                        } else {
+                            for (int d = 0; d < p.n_dst; ++d)
+                                flush_chunk_f32(stage, lane, static_cast<float*>(p.c_dst[d]), ld_out, row0, col0, p.M, p.N);
+                        }
+                    }
+                } else if (row < p.M && ncols > 0) {
                     float v[32];
 #pragma unroll
                     for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(raw[j]);
@@ -460,12 +588,18 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                     }
                 }
             }
+            t_store += clock64() - td0;
             if constexpr (MT == 1) {
                 slot ^= 1;
                 if (slot == 0) slot_phase ^= 1u;
             } else {
                 slot_phase ^= 1u;
             }
+        }
+        if (p.diag == 5 && blockIdx.x == 0 && threadIdx.x == 64) {
+            volatile int* dbg = reinterpret_cast<volatile int*>(p.status);
+            dbg[7] = static_cast<int>(t_drain >> 4);
+            dbg[8] = static_cast<int>(t_store >> 4);
         }
     }
 

@@ -297,6 +297,10 @@ int32_t run_gemm(t0b_ctx* ctx, const GemmCall& g) {
         {
             static const int diag = [] { const char* e = getenv("T0B_GEMM_DIAG"); return e ? atoi(e) : 0; }();
             p.diag = diag;
+            static const int pf = [] { const char* e = getenv("T0B_GEMM_L2PF"); return e ? atoi(e) : 0; }();
+            p.l2_prefetch = pf;
+            static const int grp = [] { const char* e = getenv("T0B_GEMM_GROUP"); return e ? atoi(e) : 0; }();
+            if (grp > 0) p.group = grp;
         }
         if (g.slabs_only && sk == 1) {
             // One slab: store straight into it as f32.

@@ -84,7 +84,7 @@ int stage_bytes(uint32_t bn, uint32_t cg, uint32_t mt) {
 
 int stages_for(uint32_t bn, uint32_t cg, uint32_t mt) {
     const int stage = stage_bytes(bn, cg, mt);
-    const int budget = 227 * 1024 - 1024 - 512;
+    const int budget = 227 * 1024 - 1024 - 512 - static_cast<int>(mt) * 4 * 4096;   // minus the epilogue transpose tiles
     return std::min(8, budget / stage);
 }
 
@@ -157,7 +157,7 @@ void resolve_plan(const t0b_gemm_config* cfg_in, const PlanInput& in, t0b_gemm_p
     const uint64_t tiles = static_cast<uint64_t>((in.m + p.bm - 1) / p.bm) * ((in.n + p.bn - 1) / p.bn) * p.split_k;
     const uint64_t clusters = static_cast<uint64_t>(num_sms) / p.cta_group;
     p.grid = static_cast<uint32_t>(std::min<uint64_t>(tiles, clusters) * p.cta_group);
-    p.smem_bytes = p.stages * stage_bytes(p.bn, p.cta_group, p.m_tiles) + 1024 + 512;
+    p.smem_bytes = p.stages * stage_bytes(p.bn, p.cta_group, p.m_tiles) + 1024 + 512 + p.m_tiles * 4 * 4096;
     *out = p;
 }
 
