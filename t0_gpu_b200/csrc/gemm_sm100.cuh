@@ -396,7 +396,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                     if (++s == S) { s = 0; ph ^= 1u; }
                 }
             }
-            if (p.diag == 5 && blockIdx.x == 0) {
+            if (p.diag >= 5 && blockIdx.x == 0) {
                 volatile int* dbg = reinterpret_cast<volatile int*>(p.status);
                 dbg[5] = static_cast<int>(t_empty >> 4);
                 dbg[6] = static_cast<int>((clock64() - tp_begin) >> 4);
@@ -479,7 +479,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                     }
                 }
             }
-            if (p.diag == 5 && blockIdx.x == 0) {
+            if (p.diag >= 5 && blockIdx.x == 0) {
                 volatile int* dbg = reinterpret_cast<volatile int*>(p.status);
                 dbg[2] = static_cast<int>(t_full >> 4);
                 dbg[3] = static_cast<int>(t_tempty >> 4);
@@ -519,11 +519,16 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
             const int row0 = wi.m0 + (MT == 2 ? group * kMmaM : 0) + static_cast<int>(cta_rank) * kBmCta + q * 32;
             const int row = row0 + lane;
             const uint32_t t_row = tmem_base + static_cast<uint32_t>(slot * BN) + (static_cast<uint32_t>(q * 32) << 16);
-#pragma unroll 1
+            // The TMEM read of chunk c+1 is in flight while chunk c is transposed and stored.
+            uint32_t nxt[32];
+            ptx::tmem_ld_32x32(t_row, nxt);
+#pragma unroll 2
             for (int c = 0; c < BN / 32; ++c) {
                 uint32_t raw[32];
-                ptx::tmem_ld_32x32(t_row + c * 32, raw);
-                ptx::tmem_ld_wait();
+                ptx::tmem_ld_wait_regs(nxt);
+#pragma unroll
+                for (int j = 0; j < 32; ++j) raw[j] = nxt[j];
+                if (c + 1 < BN / 32) ptx::tmem_ld_32x32(t_row + (c + 1) * 32, nxt);
                 if (c == BN / 32 - 1) {
                     // All of this warp's reads of the accumulator are done: hand it back to the MMA issuer.
                     ptx::tc_fence_before();
@@ -536,7 +541,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                 }
                 const int col0 = wi.n0 + c * 32;
                 const int ncols = p.N - col0;
-                if (staged) {
+                if (p.diag == 7) {
+                } else if (staged) {
                     if (row0 < p.M && ncols > 0) {   // warp-uniform
                         float v[32];
 #pragma unroll
@@ -553,7 +559,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                         if (out16) stage_chunk_bf16(stage, lane, v);
                         else stage_chunk_f32(stage, lane, v);
                         __syncwarp();
-                        if (to_slab) {
+                        if (p.diag == 6) {
+                        } else if (to_slab) {
                             flush_chunk_f32(stage, lane, p.partial + static_cast<long long>(wi.split) * p.slab_stride, ld_out,
                                             row0, col0, p.M, p.N);
                         } else if (out16) {
@@ -596,7 +603,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                 slot_phase ^= 1u;
             }
         }
-        if (p.diag == 5 && blockIdx.x == 0 && threadIdx.x == 64) {
+        if (p.diag >= 5 && blockIdx.x == 0 && threadIdx.x == 64) {
             volatile int* dbg = reinterpret_cast<volatile int*>(p.status);
             dbg[7] = static_cast<int>(t_drain >> 4);
             dbg[8] = static_cast<int>(t_store >> 4);
