@@ -243,27 +243,29 @@ __device__ __forceinline__ void flush_chunk_f32(uint32_t stage, int lane, float*
             *reinterpret_cast<float4*>(base + static_cast<long long>(row0 + r) * ld + col0 + c * 4) = q;
     }
 }
-__device__ __forceinline__ void stage_chunk_bf16(uint32_t stage, int lane, const float (&v)[32]) {
+// bf16 output: two 32-column chunks share one tile (32 rows x 64 bf16 = 128-byte rows), so the flush writes
+// whole 128-byte lines, local or remote.
+__device__ __forceinline__ void stage_half_bf16(uint32_t stage, int lane, int half, const float (&v)[32]) {
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
         __nv_bfloat162 h0 = __floats2bfloat162_rn(v[8 * j + 0], v[8 * j + 1]);
         __nv_bfloat162 h1 = __floats2bfloat162_rn(v[8 * j + 2], v[8 * j + 3]);
         __nv_bfloat162 h2 = __floats2bfloat162_rn(v[8 * j + 4], v[8 * j + 5]);
         __nv_bfloat162 h3 = __floats2bfloat162_rn(v[8 * j + 6], v[8 * j + 7]);
-        const uint32_t addr = stage + lane * 64 + ((j ^ ((lane >> 1) & 3)) << 4);
+        const uint32_t addr = stage + lane * 128 + (((half * 4 + j) ^ (lane & 7)) << 4);
         asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(*reinterpret_cast<uint32_t*>(&h0)),
                      "r"(*reinterpret_cast<uint32_t*>(&h1)), "r"(*reinterpret_cast<uint32_t*>(&h2)),
                      "r"(*reinterpret_cast<uint32_t*>(&h3))
                      : "memory");
     }
 }
-__device__ __forceinline__ void flush_chunk_bf16(uint32_t stage, int lane, __nv_bfloat16* base, long long ld, int row0,
-                                                 int col0, int M, int N) {
-    const int c = lane & 3;
+__device__ __forceinline__ void flush_pair_bf16(uint32_t stage, int lane, __nv_bfloat16* base, long long ld, int row0,
+                                                int col0, int M, int N) {
+    const int c = lane & 7;
 #pragma unroll
-    for (int t = 0; t < 4; ++t) {
-        const int r = t * 8 + (lane >> 2);
-        const uint32_t addr = stage + r * 64 + ((c ^ ((r >> 1) & 3)) << 4);
+    for (int t = 0; t < 8; ++t) {
+        const int r = t * 4 + (lane >> 3);
+        const uint32_t addr = stage + r * 128 + ((c ^ (r & 7)) << 4);
         uint4 q;
         asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(q.x), "=r"(q.y), "=r"(q.z), "=r"(q.w) : "r"(addr));
         if (row0 + r < M && col0 + c * 8 < N)   // N % 8 == 0 on this path
@@ -542,6 +544,31 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                 const int col0 = wi.n0 + c * 32;
                 const int ncols = p.N - col0;
                 if (p.diag == 7) {
+                } else if (staged && out16) {
+                    const int half = c & 1;
+                    if (half == 0) __syncwarp();   // the previous pair's reads of the staging tile are done
+                    if (row0 < p.M && ncols > 0) {   // warp-uniform
+                        float v[32];
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(raw[j]);
+                        if (epi != EPI_STORE) {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) {
+                                float b = 0.0f;
+                                if (need_bias && j < ncols) b = __ldg(p.bias + col0 + j);
+                                v[j] = apply_epilogue(v[j], epi, b, p.alpha);
+                            }
+                        }
+                        stage_half_bf16(stage, lane, half, v);
+                    }
+                    if (half == 1) {
+                        __syncwarp();
+                        const int cbase = col0 - 32;
+                        if (row0 < p.M && cbase < p.N && p.diag != 6) {
+                            for (int d = 0; d < p.n_dst; ++d)
+                                flush_pair_bf16(stage, lane, static_cast<__nv_bfloat16*>(p.c_dst[d]), ld_out, row0, cbase, p.M, p.N);
+                        }
+                    }
                 } else if (staged) {
                     if (row0 < p.M && ncols > 0) {   // warp-uniform
                         float v[32];
@@ -556,16 +583,12 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                             }
                         }
                         __syncwarp();   // the previous chunk's reads of the staging tile are done
-                        if (out16) stage_chunk_bf16(stage, lane, v);
-                        else stage_chunk_f32(stage, lane, v);
+                        stage_chunk_f32(stage, lane, v);
                         __syncwarp();
                         if (p.diag == 6) {
                         } else if (to_slab) {
                             flush_chunk_f32(stage, lane, p.partial + static_cast<long long>(wi.split) * p.slab_stride, ld_out,
                                             row0, col0, p.M, p.N);
-                        } else if (out16) {
-                            for (int d = 0; d < p.n_dst; ++d)
-                                flush_chunk_bf16(stage, lane, static_cast<__nv_bfloat16*>(p.c_dst[d]), ld_out, row0, col0, p.M, p.N);
                         } else {
                             for (int d = 0; d < p.n_dst; ++d)
                                 flush_chunk_f32(stage, lane, static_cast<float*>(p.c_dst[d]), ld_out, row0, col0, p.M, p.N);

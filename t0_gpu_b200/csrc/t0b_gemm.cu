@@ -372,6 +372,9 @@ int32_t t0b_gemm_multi_dst(t0b_ctx* ctx, const t0b_gemm_config* cfg, int32_t tra
         g.cfg = &local;
     } else {
         default_b200_config(m, k, n_local, ctx->num_sms, &local);
+        // Remote stores are slow to retire: with peers, prefer the tile whose two TMEM accumulators double-buffer,
+        // so the epilogue of one tile (which issues the peer stores) overlaps the main loop of the next.
+        if (n_dst > 1 && local.tile_m >= 512) { local.tile_m = 256; local.wg_size = 192; }
         local.split_k = 0;
         g.cfg = &local;
     }

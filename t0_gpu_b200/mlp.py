@@ -1,0 +1,221 @@
+"""The Ignis MLP training step on the B200 kernels, data-parallel over the GPUs of one node.
+
+Model (the benchmark's fifth config): input 4096 -> 3 x [Linear(4096) -> RMSNorm(eps 1e-6, weight 1) -> SiLU] ->
+Linear(32000) -> softmax cross-entropy.  bf16 compute copies of fp32 master weights (Kaiming-uniform), f32
+activations between kernels, bf16 operands into every GEMM, f32 accumulation, f32 gradients.
+
+The step follows the structure of the reference's training loop (examples/train_mlp.rs:121-233: forward, loss,
+backward, AdamW) with the ops of the hot path: `matmul` forward / backward-data / backward-weight
+(src/ignis/ops/bf16_matmul.rs:33-308) without its host-side conversions and transposes, `rmsnorm`
+(src/ignis/ops/rmsnorm.rs:26-305), SiLU (src/ignis/ops/silu.rs:32-152), `cross_entropy`
+(src/ignis/ops/cross_entropy.rs:34-115) with loss and gradient computed on the device, AdamW
+(src/t0/adamw_kernels.rs:35-119).  Data parallelism (rows split over ranks, fp32 gradient all-reduce) has no
+counterpart in the reference; `torch.distributed` carries the all-reduce, started per layer as soon as that
+layer's weight gradient is ready so it overlaps the rest of the backward pass.
+
+Device memory comes from torch tensors (the all-reduce needs them); every kernel is a C-ABI call.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import List, Optional
+
+from ._lib import lib
+from .gpu_context import OUT_BF16, OUT_F32, GpuRuntime
+
+
+@dataclass
+class MlpConfig:
+    d_in: int = 4096
+    hidden: List[int] = field(default_factory=lambda: [4096, 4096, 4096])
+    n_classes: int = 32000
+    eps: float = 1e-6
+    lr: float = 1e-3
+    beta1: float = 0.9
+    beta2: float = 0.999
+    adam_eps: float = 1e-8
+    weight_decay: float = 0.01
+
+    def dims(self):
+        d = [self.d_in] + list(self.hidden) + [self.n_classes]
+        return list(zip(d[:-1], d[1:]))          # (fan_in, fan_out) per Linear
+
+    def flops_per_row(self) -> float:
+        """Forward + backward GEMM FLOPs per batch row (2 MNK each; dX is not needed for the first layer)."""
+        f = 0.0
+        for i, (k, n) in enumerate(self.dims()):
+            f += 2.0 * k * n * (2 if i == 0 else 3)
+        return f
+
+
+def kaiming_uniform_(torch, w, fan_in: int, seed: int):
+    """U(-sqrt(6 / fan_in), +sqrt(6 / fan_in)), seeded per tensor."""
+    g = torch.Generator(device=w.device)
+    g.manual_seed(seed)
+    bound = (6.0 / fan_in) ** 0.5
+    w.uniform_(-bound, bound, generator=g)
+    return w
+
+
+class MlpTrainer:
+    """One data-parallel replica.  `rows` is this rank's share of the batch, `rows_total` the global batch."""
+
+    def __init__(self, rt: GpuRuntime, cfg: MlpConfig, rows: int, rows_total: Optional[int] = None, group=None,
+                 seed: int = 100):
+        import torch
+        import torch.distributed as dist
+
+        self.torch, self.rt, self.cfg, self.rows, self.group = torch, rt, cfg, rows, group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rows_total = rows_total if rows_total is not None else rows * self.world
+        self.dev = torch.device("cuda", torch.cuda.current_device())
+        self.L = lib()
+        # The library's launches and torch's own work (fills, all-reduce hand-off) share one non-default stream.
+        if torch.cuda.current_stream().cuda_stream == 0:
+            self.stream = torch.cuda.Stream(device=self.dev)
+            torch.cuda.set_stream(self.stream)
+        else:
+            self.stream = torch.cuda.current_stream()
+        rt.set_stream(self.stream.cuda_stream)
+        dims = cfg.dims()
+        f32, bf16 = torch.float32, torch.bfloat16
+        # Parameters: W_l stored [fan_in, fan_out] (row-major [K, N], the layout `Linear` uses), gamma_l = 1.
+        sizes = [k * n for k, n in dims] + list(cfg.hidden)
+        self.n_params = sum(sizes)
+        self.master = torch.empty(self.n_params, dtype=f32, device=self.dev)
+        self.grads = torch.zeros(self.n_params, dtype=f32, device=self.dev)
+        self.compute = torch.empty(self.n_params, dtype=bf16, device=self.dev)   # bf16 copies (gammas unused)
+        self.adam_m = torch.zeros(self.n_params, dtype=f32, device=self.dev)
+        self.adam_v = torch.zeros(self.n_params, dtype=f32, device=self.dev)
+        offs, o = [], 0
+        for s in sizes:
+            offs.append(o)
+            o += s
+        nl = len(dims)
+        self.w = [self.master[offs[i]:offs[i] + sizes[i]].view(dims[i]) for i in range(nl)]
+        self.w16 = [self.compute[offs[i]:offs[i] + sizes[i]].view(dims[i]) for i in range(nl)]
+        self.dw = [self.grads[offs[i]:offs[i] + sizes[i]].view(dims[i]) for i in range(nl)]
+        self.gamma = [self.master[offs[nl + i]:offs[nl + i] + sizes[nl + i]] for i in range(len(cfg.hidden))]
+        self.dgamma = [self.grads[offs[nl + i]:offs[nl + i] + sizes[nl + i]] for i in range(len(cfg.hidden))]
+        for i, (k, n) in enumerate(dims):
+            kaiming_uniform_(torch, self.w[i], k, seed + i)
+        for g in self.gamma:
+            g.fill_(1.0)
+        self._refresh_compute_copies()
+        # Activations.
+        B = rows
+        self.x16 = torch.empty((B, cfg.d_in), dtype=bf16, device=self.dev)
+        self.z = [torch.empty((B, h), dtype=f32, device=self.dev) for h in cfg.hidden]        # Linear outputs
+        self.r = [torch.empty((B, h), dtype=f32, device=self.dev) for h in cfg.hidden]        # RMSNorm outputs
+        self.a = torch.empty((B, max(cfg.hidden)), dtype=f32, device=self.dev)                # SiLU output (scratch)
+        self.h16 = [torch.empty((B, h), dtype=bf16, device=self.dev) for h in cfg.hidden]     # bf16 layer outputs
+        self.logits = torch.empty((B, cfg.n_classes), dtype=f32, device=self.dev)
+        self.dlogits = torch.empty((B, cfg.n_classes), dtype=f32, device=self.dev)
+        self.dlogits16 = torch.empty((B, cfg.n_classes), dtype=bf16, device=self.dev)
+        self.losses = torch.empty(B, dtype=f32, device=self.dev)
+        self.dh = torch.empty((B, max(cfg.hidden)), dtype=f32, device=self.dev)
+        self.dr = torch.empty((B, max(cfg.hidden)), dtype=f32, device=self.dev)
+        self.dz = torch.empty((B, max(cfg.hidden)), dtype=f32, device=self.dev)
+        self.dz16 = torch.empty((B, max(cfg.hidden)), dtype=bf16, device=self.dev)
+        self.scratch_bytes = self.L.t0b_rmsnorm_bwd_scratch_bytes(B, max(cfg.hidden))
+        self.scratch = torch.empty(self.scratch_bytes, dtype=torch.uint8, device=self.dev)
+        self.step_count = 0
+        self._pending = []
+
+    # ------------------------------------------------------------------ helpers (each one C-ABI call)
+    def _ck(self, rc):
+        self.rt._check(rc)
+
+    def _gemm(self, a, b, c, m, n, k, trans_a, trans_b, lda, ldb, out_dtype=OUT_F32):
+        self._ck(self.L.t0b_gemm(self.rt.handle, None, int(trans_a), int(trans_b), a.data_ptr(), b.data_ptr(),
+                                 c.data_ptr(), m, n, k, lda, ldb, n, out_dtype, 0, 0, 1.0, 0, 0, 1))
+
+    def _cast(self, src, dst, n):
+        self._ck(self.L.t0b_cast_f32_to_bf16(self.rt.handle, src.data_ptr(), dst.data_ptr(), n, 1))
+
+    def _refresh_compute_copies(self):
+        self._ck(self.L.t0b_cast_f32_to_bf16(self.rt.handle, self.master.data_ptr(), self.compute.data_ptr(),
+                                             self.n_params, 1))
+
+    # ------------------------------------------------------------------ one step
+    def forward_backward(self, x, targets):
+        """x: f32 [rows, d_in]; targets: int32/uint32 [rows].  Leaves the mean loss contribution of this rank in
+        `self.losses` (per-row losses) and the summed-over-ranks gradients in `self.grads`."""
+        cfg, B, L, h = self.cfg, self.rows, self.L, self.rt.handle
+        nh = len(cfg.hidden)
+        scale = 1.0 / float(self.rows_total)
+        # forward
+        self._cast(x, self.x16, B * cfg.d_in)
+        inp, k = self.x16, cfg.d_in
+        for l in range(nh):
+            n = cfg.hidden[l]
+            self._gemm(inp, self.w16[l], self.z[l], B, n, k, False, False, k, n)
+            self._ck(L.t0b_rmsnorm_fwd(h, self.z[l].data_ptr(), self.gamma[l].data_ptr(), self.r[l].data_ptr(), 0, B, n,
+                                       cfg.eps, 1))
+            self._ck(L.t0b_silu_gate_fwd(h, self.r[l].data_ptr(), 0, self.a.data_ptr(), B * n, 1))
+            self._cast(self.a, self.h16[l], B * n)
+            inp, k = self.h16[l], n
+        V = cfg.n_classes
+        self._gemm(inp, self.w16[nh], self.logits, B, V, k, False, False, k, V)
+        self._ck(L.t0b_softmax_ce(h, self.logits.data_ptr(), targets.data_ptr(), self.losses.data_ptr(),
+                                  self.dlogits.data_ptr(), B, V, V, scale, 1))
+        # backward
+        self._cast(self.dlogits, self.dlogits16, B * V)
+        # dW_out[k, V] = h_last^T [k, B] * dlogits [B, V]: A stored [B, k] read transposed
+        self._gemm(inp, self.dlogits16, self.dw[nh], k, V, B, True, False, k, V)
+        self._start_allreduce(self.dw[nh])
+        # dh_last[B, k] = dlogits [B, V] * W_out^T: B operand stored [k, V] = [N_gemm, K_gemm]
+        self._gemm(self.dlogits16, self.w16[nh], self.dh, B, k, V, False, True, V, V)
+        for l in range(nh - 1, -1, -1):
+            n = cfg.hidden[l]
+            k = cfg.hidden[l - 1] if l > 0 else cfg.d_in
+            prev = self.h16[l - 1] if l > 0 else self.x16
+            self._ck(L.t0b_silu_gate_bwd(h, self.dh.data_ptr(), self.r[l].data_ptr(), 0, self.dr.data_ptr(), 0, B * n, 1))
+            self._ck(L.t0b_rmsnorm_bwd(h, self.dr.data_ptr(), self.z[l].data_ptr(), self.gamma[l].data_ptr(),
+                                       self.dz.data_ptr(), self.dgamma[l].data_ptr(), self.scratch.data_ptr(),
+                                       self.scratch_bytes, B, n, cfg.eps, 1))
+            self._cast(self.dz, self.dz16, B * n)
+            self._gemm(prev, self.dz16, self.dw[l], k, n, B, True, False, k, n)
+            self._start_allreduce(self.dw[l])
+            if l > 0:
+                self._gemm(self.dz16, self.w16[l], self.dh, B, k, n, False, True, n, n)
+        if self.world > 1:
+            # the small gamma gradients go last, in one piece
+            g0 = self.dgamma[0]
+            flat = self.grads[g0.storage_offset():g0.storage_offset() + sum(cfg.hidden)]
+            self._start_allreduce(flat)
+        self._finish_allreduce()
+
+    def _start_allreduce(self, tensor):
+        if self.world == 1:
+            return
+        import torch.distributed as dist
+
+        self._pending.append(dist.all_reduce(tensor, op=dist.ReduceOp.SUM, group=self.group, async_op=True))
+
+    def _finish_allreduce(self):
+        for w in self._pending:
+            w.wait()
+        self._pending = []
+
+    def optimizer_step(self):
+        cfg = self.cfg
+        self.step_count += 1
+        self._ck(self.L.t0b_adamw_step(self.rt.handle, self.master.data_ptr(), self.grads.data_ptr(),
+                                       self.adam_m.data_ptr(), self.adam_v.data_ptr(), self.compute.data_ptr(),
+                                       self.n_params, cfg.lr, cfg.beta1, cfg.beta2, cfg.adam_eps, cfg.weight_decay,
+                                       self.step_count, 1.0, 1))
+
+    def step(self, x, targets):
+        self.forward_backward(x, targets)
+        self.optimizer_step()
+
+    def mean_loss(self) -> float:
+        """Global mean loss: sum of this rank's per-row losses / rows_total, summed over ranks."""
+        torch = self.torch
+        s = self.losses.sum() / float(self.rows_total)
+        if self.world > 1:
+            import torch.distributed as dist
+
+            dist.all_reduce(s, group=self.group)
+        return float(s.item())

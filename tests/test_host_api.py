@@ -148,7 +148,7 @@ def test_plan_resolution():
     p = t.resolve_plan(None, 8192, 8192, 8192)
     assert (p.bm, p.bn, p.bk, p.cta_group, p.m_tiles) == (512, 256, 64, 2, 2) and p.use_tma and p.smem_bytes <= 227 * 1024
     p = t.resolve_plan(GemmConfig.preset("b200_256x256"), 8192, 8192, 8192)
-    assert (p.bm, p.bn, p.cta_group, p.m_tiles, p.stages) == (256, 256, 2, 1, 7)
+    assert (p.bm, p.bn, p.cta_group, p.m_tiles, p.stages) == (256, 256, 2, 1, 6)
     # reference presets run as single-CTA 128-row tiles
     p = t.resolve_plan(GemmConfig.tile_64x64_k16().with_(split_k=4), 256, 256, 256)
     assert (p.bm, p.bn, p.cta_group, p.split_k, p.kb_per_split) == (128, 64, 1, 4, 1)
