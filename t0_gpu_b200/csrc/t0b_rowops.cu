@@ -8,6 +8,7 @@
 
 #include <algorithm>
 #include <cfloat>
+#include <cstdlib>
 
 #include "t0b_internal.hpp"
 
@@ -42,15 +43,16 @@ __device__ __forceinline__ void block_sum2(float& a, float& b, float* red) {
     b = warp_sum(y);
 }
 
-// Online softmax statistics (running max m, running sum s of exp(x - m)).
+// Online softmax statistics (running max m, running sum s of exp(x - m)).  __expf (ex2.approx based, relative
+// error ~1e-6) keeps these kernels memory-bound; the accurate expf made them instruction-bound.
 __device__ __forceinline__ void online_add(float& m, float& s, float x) {
-    if (x > m) { s = s * expf(m - x) + 1.0f; m = x; }
-    else s += expf(x - m);
+    if (x > m) { s = s * __expf(m - x) + 1.0f; m = x; }
+    else s += __expf(x - m);
 }
 __device__ __forceinline__ void online_merge(float& m, float& s, float m2, float s2) {
     const float mm = fmaxf(m, m2);
-    const float a = (m == -INFINITY) ? 0.0f : s * expf(m - mm);
-    const float b = (m2 == -INFINITY) ? 0.0f : s2 * expf(m2 - mm);
+    const float a = (m == -INFINITY) ? 0.0f : s * __expf(m - mm);
+    const float b = (m2 == -INFINITY) ? 0.0f : s2 * __expf(m2 - mm);
     m = mm;
     s = a + b;
 }
@@ -236,8 +238,8 @@ __device__ __forceinline__ void row_stats(const float* __restrict__ xr, uint32_t
             const float4 v = reinterpret_cast<const float4*>(xr)[i];
             if (CACHE) reinterpret_cast<float4*>(cache)[i] = v;
             const float lm = fmaxf(fmaxf(v.x, v.y), fmaxf(v.z, v.w));
-            if (lm > m) { s *= expf(m - lm); m = lm; }
-            s += expf(v.x - m) + expf(v.y - m) + expf(v.z - m) + expf(v.w - m);
+            if (lm > m) { s *= __expf(m - lm); m = lm; }
+            s += __expf(v.x - m) + __expf(v.y - m) + __expf(v.z - m) + __expf(v.w - m);
         }
     } else {
         for (uint32_t i = threadIdx.x; i < cols; i += blockDim.x) {
@@ -265,10 +267,10 @@ __global__ void __launch_bounds__(kRowThreads) softmax_fwd_kernel(const float* _
     if (vec) {
         for (uint32_t i = threadIdx.x; i < cols / 4; i += blockDim.x) {
             const float4 v = reinterpret_cast<const float4*>(src)[i];
-            reinterpret_cast<float4*>(yr)[i] = make_float4(expf(v.x - m) * inv, expf(v.y - m) * inv, expf(v.z - m) * inv, expf(v.w - m) * inv);
+            reinterpret_cast<float4*>(yr)[i] = make_float4(__expf(v.x - m) * inv, __expf(v.y - m) * inv, __expf(v.z - m) * inv, __expf(v.w - m) * inv);
         }
     } else {
-        for (uint32_t i = threadIdx.x; i < cols; i += blockDim.x) yr[i] = expf(src[i] - m) * inv;
+        for (uint32_t i = threadIdx.x; i < cols; i += blockDim.x) yr[i] = __expf(src[i] - m) * inv;
     }
 }
 
@@ -308,7 +310,7 @@ __global__ void __launch_bounds__(kRowThreads) softmax_ce_kernel(const float* __
     if (vec) {
         for (uint32_t i = threadIdx.x; i < cols / 4; i += blockDim.x) {
             const float4 v = reinterpret_cast<const float4*>(src)[i];
-            float4 o = make_float4(expf(v.x - m) * inv, expf(v.y - m) * inv, expf(v.z - m) * inv, expf(v.w - m) * inv);
+            float4 o = make_float4(__expf(v.x - m) * inv, __expf(v.y - m) * inv, __expf(v.z - m) * inv, __expf(v.w - m) * inv);
             const uint32_t c = i * 4;
             if (t - c < 4u) {
                 if (t == c) o.x -= 1.0f;
@@ -320,31 +322,75 @@ __global__ void __launch_bounds__(kRowThreads) softmax_ce_kernel(const float* __
         }
     } else {
         for (uint32_t i = threadIdx.x; i < cols; i += blockDim.x)
-            dr[i] = (expf(src[i] - m) * inv - (i == t ? 1.0f : 0.0f)) * scale;
+            dr[i] = (__expf(src[i] - m) * inv - (i == t ? 1.0f : 0.0f)) * scale;
     }
 }
 
 // ------------------------------------------------------------------------------------------------ element-wise
 
+__device__ __forceinline__ float sigmoidf_(float g) { return 1.0f / (1.0f + expf(-g)); }
+
 __global__ void __launch_bounds__(256) silu_gate_fwd_kernel(const float* __restrict__ gate, const float* __restrict__ up,
                                                             float* __restrict__ out, size_t n) {
     const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
-    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < n; i += stride) {
-        const float g = gate[i];
-        const float sig = 1.0f / (1.0f + expf(-g));
-        out[i] = g * sig * (up ? up[i] : 1.0f);
+    const size_t i0 = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x;
+    const bool vec = ((reinterpret_cast<uintptr_t>(gate) & 15) == 0) && ((reinterpret_cast<uintptr_t>(out) & 15) == 0) &&
+                     (!up || (reinterpret_cast<uintptr_t>(up) & 15) == 0);
+    size_t done = 0;
+    if (vec) {
+        const size_t n4 = n / 4;
+        for (size_t i = i0; i < n4; i += stride) {
+            const float4 g = reinterpret_cast<const float4*>(gate)[i];
+            float4 u = make_float4(1.0f, 1.0f, 1.0f, 1.0f);
+            if (up) u = reinterpret_cast<const float4*>(up)[i];
+            reinterpret_cast<float4*>(out)[i] = make_float4(g.x * sigmoidf_(g.x) * u.x, g.y * sigmoidf_(g.y) * u.y,
+                                                            g.z * sigmoidf_(g.z) * u.z, g.w * sigmoidf_(g.w) * u.w);
+        }
+        done = n4 * 4;
     }
+    for (size_t i = done + i0; i < n; i += stride) {
+        const float g = gate[i];
+        out[i] = g * sigmoidf_(g) * (up ? up[i] : 1.0f);
+    }
+}
+
+__device__ __forceinline__ void silu_bwd_one(float gr, float g, float u, float& dgate, float& dup) {
+    const float sig = sigmoidf_(g);
+    dup = gr * g * sig;
+    dgate = gr * u * sig * (1.0f + g * (1.0f - sig));
 }
 
 __global__ void __launch_bounds__(256) silu_gate_bwd_kernel(const float* __restrict__ grad, const float* __restrict__ gate,
                                                             const float* __restrict__ up, float* __restrict__ dgate,
                                                             float* __restrict__ dup, size_t n) {
     const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
-    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < n; i += stride) {
-        const float g = gate[i], gr = grad[i], u = up ? up[i] : 1.0f;
-        const float sig = 1.0f / (1.0f + expf(-g));
-        if (dup) dup[i] = gr * g * sig;
-        dgate[i] = gr * u * sig * (1.0f + g * (1.0f - sig));
+    const size_t i0 = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x;
+    const bool vec = ((reinterpret_cast<uintptr_t>(grad) & 15) == 0) && ((reinterpret_cast<uintptr_t>(gate) & 15) == 0) &&
+                     ((reinterpret_cast<uintptr_t>(dgate) & 15) == 0) && (!up || (reinterpret_cast<uintptr_t>(up) & 15) == 0) &&
+                     (!dup || (reinterpret_cast<uintptr_t>(dup) & 15) == 0);
+    size_t done = 0;
+    if (vec) {
+        const size_t n4 = n / 4;
+        for (size_t i = i0; i < n4; i += stride) {
+            const float4 gr = reinterpret_cast<const float4*>(grad)[i];
+            const float4 g = reinterpret_cast<const float4*>(gate)[i];
+            float4 u = make_float4(1.0f, 1.0f, 1.0f, 1.0f);
+            if (up) u = reinterpret_cast<const float4*>(up)[i];
+            float4 dg, du;
+            silu_bwd_one(gr.x, g.x, u.x, dg.x, du.x);
+            silu_bwd_one(gr.y, g.y, u.y, dg.y, du.y);
+            silu_bwd_one(gr.z, g.z, u.z, dg.z, du.z);
+            silu_bwd_one(gr.w, g.w, u.w, dg.w, du.w);
+            reinterpret_cast<float4*>(dgate)[i] = dg;
+            if (dup) reinterpret_cast<float4*>(dup)[i] = du;
+        }
+        done = n4 * 4;
+    }
+    for (size_t i = done + i0; i < n; i += stride) {
+        float dg, du;
+        silu_bwd_one(grad[i], gate[i], up ? up[i] : 1.0f, dg, du);
+        dgate[i] = dg;
+        if (dup) dup[i] = du;
     }
 }
 
@@ -366,18 +412,51 @@ __global__ void __launch_bounds__(256) residual_add_kernel(float* __restrict__ y
     }
 }
 
+__device__ __forceinline__ float adamw_one(float p, float gi, float& m, float& v, float lr, float beta1, float beta2,
+                                           float eps, float wd, float bc1, float bc2) {
+    m = beta1 * m + (1.0f - beta1) * gi;
+    v = beta2 * v + (1.0f - beta2) * gi * gi;
+    return p * (1.0f - lr * wd) - lr * (m * bc1) / (sqrtf(v * bc2) + eps);
+}
+
 __global__ void __launch_bounds__(256) adamw_kernel(float* __restrict__ p, const float* __restrict__ g, float* __restrict__ m,
                                                     float* __restrict__ v, __nv_bfloat16* __restrict__ p_bf16, size_t n,
                                                     float lr, float beta1, float beta2, float eps, float wd, float bc1,
                                                     float bc2, float grad_scale) {
     const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
-    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < n; i += stride) {
-        const float gi = g[i] * grad_scale;
-        const float mi = beta1 * m[i] + (1.0f - beta1) * gi;
-        const float vi = beta2 * v[i] + (1.0f - beta2) * gi * gi;
+    const size_t i0 = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x;
+    const bool vec = (((reinterpret_cast<uintptr_t>(p) | reinterpret_cast<uintptr_t>(g) | reinterpret_cast<uintptr_t>(m) |
+                        reinterpret_cast<uintptr_t>(v)) & 15) == 0) && ((reinterpret_cast<uintptr_t>(p_bf16) & 7) == 0);
+    size_t done = 0;
+    if (vec) {
+        const size_t n4 = n / 4;
+        for (size_t i = i0; i < n4; i += stride) {
+            float4 pp = reinterpret_cast<float4*>(p)[i];
+            const float4 gg = reinterpret_cast<const float4*>(g)[i];
+            float4 mm = reinterpret_cast<float4*>(m)[i];
+            float4 vv = reinterpret_cast<float4*>(v)[i];
+            pp.x = adamw_one(pp.x, gg.x * grad_scale, mm.x, vv.x, lr, beta1, beta2, eps, wd, bc1, bc2);
+            pp.y = adamw_one(pp.y, gg.y * grad_scale, mm.y, vv.y, lr, beta1, beta2, eps, wd, bc1, bc2);
+            pp.z = adamw_one(pp.z, gg.z * grad_scale, mm.z, vv.z, lr, beta1, beta2, eps, wd, bc1, bc2);
+            pp.w = adamw_one(pp.w, gg.w * grad_scale, mm.w, vv.w, lr, beta1, beta2, eps, wd, bc1, bc2);
+            reinterpret_cast<float4*>(p)[i] = pp;
+            reinterpret_cast<float4*>(m)[i] = mm;
+            reinterpret_cast<float4*>(v)[i] = vv;
+            if (p_bf16) {
+                __nv_bfloat162 lo = __floats2bfloat162_rn(pp.x, pp.y), hi = __floats2bfloat162_rn(pp.z, pp.w);
+                uint2 o;
+                o.x = *reinterpret_cast<uint32_t*>(&lo);
+                o.y = *reinterpret_cast<uint32_t*>(&hi);
+                reinterpret_cast<uint2*>(p_bf16)[i] = o;
+            }
+        }
+        done = n4 * 4;
+    }
+    for (size_t i = done + i0; i < n; i += stride) {
+        float mi = m[i], vi = v[i];
+        const float pn = adamw_one(p[i], g[i] * grad_scale, mi, vi, lr, beta1, beta2, eps, wd, bc1, bc2);
         m[i] = mi;
         v[i] = vi;
-        const float pn = p[i] * (1.0f - lr * wd) - lr * (mi * bc1) / (sqrtf(vi * bc2) + eps);
         p[i] = pn;
         if (p_bf16) p_bf16[i] = __float2bfloat16_rn(pn);
     }
@@ -388,7 +467,10 @@ int grid_for(t0b_ctx* ctx, size_t n, int per_block) {
     return static_cast<int>(std::max<size_t>(1, std::min<size_t>(blocks, static_cast<size_t>(ctx->num_sms) * 16)));
 }
 
-constexpr size_t kRowCacheMax = 200 * 1024;
+// Rows up to 64 KiB are cached in shared memory (several CTAs still fit per SM, one HBM read); wider rows are
+// re-read through L2 instead, which measured faster than one 128 KiB-row CTA per SM.
+constexpr size_t kRowCacheLimit = 200 * 1024;
+static const size_t kRowCacheMax = [] { const char* e = getenv("T0B_ROW_CACHE_MAX"); return e ? static_cast<size_t>(atol(e)) : static_cast<size_t>(64 * 1024); }();
 
 }  // namespace
 
@@ -550,7 +632,7 @@ int32_t t0b_softmax_fwd(t0b_ctx* ctx, uint64_t x, uint64_t y, uint32_t rows, uin
         static bool set[64] = {};
         if (!set[ctx->device & 63]) {
             rc = check_cuda(ctx, cudaFuncSetAttribute(softmax_fwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                      static_cast<int>(kRowCacheMax)), "cudaFuncSetAttribute(softmax)");
+                                                      static_cast<int>(kRowCacheLimit)), "cudaFuncSetAttribute(softmax)");
             if (rc != T0B_OK) return rc;
             set[ctx->device & 63] = true;
         }
@@ -585,7 +667,7 @@ int32_t t0b_softmax_ce(t0b_ctx* ctx, uint64_t logits, uint64_t targets, uint64_t
         static bool set[64] = {};
         if (!set[ctx->device & 63]) {
             rc = check_cuda(ctx, cudaFuncSetAttribute(softmax_ce_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                      static_cast<int>(kRowCacheMax)), "cudaFuncSetAttribute(softmax_ce)");
+                                                      static_cast<int>(kRowCacheLimit)), "cudaFuncSetAttribute(softmax_ce)");
             if (rc != T0B_OK) return rc;
             set[ctx->device & 63] = true;
         }
