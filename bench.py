@@ -189,6 +189,77 @@ def time_steps(torch, fn, steps, stream):
     return e0.elapsed_time(e1) / steps
 
 
+def context_measurements(torch, rt, L, stream, dev):
+    """The memory-bound kernels (achieved HBM GB/s on working sets larger than L2) and the MLP training step of the
+    fifth benchmark config at its per-GPU size (1024 rows), next to the headline GEMM number."""
+    from t0_gpu_b200.mlp import MlpConfig, MlpTrainer
+
+    out = {}
+    hbm_peak = None
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            hbm_peak = float(json.load(f)["hbm_gbs"])
+    except Exception:
+        pass
+
+    def gbs(fn, nbytes, steps=20):
+        for _ in range(3):
+            fn()
+        ms = time_steps(torch, fn, steps, stream)
+        g = nbytes / ms / 1e6
+        return {"ms": ms, "gbs": g, "frac_of_measured_hbm": (g / hbm_peak) if hbm_peak else None}
+
+    rows, cols = 8192, 4096
+    nbuf = 4                                   # 4 x (128 MiB in + 128 MiB out): rotating so nothing is served from L2
+    xs = [torch.randn(rows, cols, device=dev) for _ in range(nbuf)]
+    ys = [torch.empty(rows, cols, device=dev) for _ in range(nbuf)]
+    w = torch.ones(cols, device=dev)
+    i = [0]
+
+    def rms():
+        j = i[0] % nbuf
+        i[0] += 1
+        rt._check(L.t0b_rmsnorm_fwd(rt.handle, xs[j].data_ptr(), w.data_ptr(), ys[j].data_ptr(), 0, rows, cols, 1e-6, 1))
+
+    out["rmsnorm_fwd_8192x4096"] = gbs(rms, 2 * rows * cols * 4)
+    dy = torch.randn(rows, cols, device=dev)
+
+    def rms_bwd():
+        j = i[0] % nbuf
+        i[0] += 1
+        rt._check(L.t0b_rmsnorm_bwd(rt.handle, dy.data_ptr(), xs[j].data_ptr(), w.data_ptr(), ys[j].data_ptr(), 0, 0, 0,
+                                    rows, cols, 1e-6, 1))
+
+    out["rmsnorm_bwd_dx_8192x4096"] = gbs(rms_bwd, 3 * rows * cols * 4)
+    del xs, ys, dy
+    rows, cols = 1024, 32000
+    nbuf = 4
+    xs = [torch.randn(rows, cols, device=dev) * 3 for _ in range(nbuf)]
+    ds = [torch.empty(rows, cols, device=dev) for _ in range(nbuf)]
+    tg = torch.randint(0, cols, (rows,), device=dev, dtype=torch.int32)
+    loss = torch.empty(rows, device=dev)
+
+    def ce():
+        j = i[0] % nbuf
+        i[0] += 1
+        rt._check(L.t0b_softmax_ce(rt.handle, xs[j].data_ptr(), tg.data_ptr(), loss.data_ptr(), ds[j].data_ptr(), rows, cols,
+                                   cols, 1.0 / rows, 1))
+
+    out["softmax_ce_1024x32000"] = gbs(ce, 2 * rows * cols * 4)
+    del xs, ds
+    cfg = MlpConfig()
+    tr = MlpTrainer(rt, cfg, 1024)
+    x = torch.randn((1024, cfg.d_in), device=dev)
+    t_ = torch.randint(0, cfg.n_classes, (1024,), device=dev, dtype=torch.int32)
+    for _ in range(3):
+        tr.step(x, t_)
+    ms_fb = time_steps(torch, lambda: tr.forward_backward(x, t_), 10, stream)
+    ms_step = time_steps(torch, lambda: tr.step(x, t_), 10, stream)
+    out["mlp_step_1024rows_4096x3_32000"] = {"fwd_bwd_ms": ms_fb, "step_with_adamw_ms": ms_step,
+                                             "gemm_tflops_fwd_bwd": cfg.flops_per_row() * 1024 / ms_fb / 1e9}
+    return out
+
+
 def run_single(args, local_rank):
     import torch
 
@@ -254,6 +325,9 @@ def run_single(args, local_rank):
         t_ms = time_steps(torch, f, 5, stream)
         also["colshard_32768x32768x8192_bf16out_g1"] = {"ms": t_ms, "tflops": 2.0 * bm * bn * bk / (t_ms * 1e-3) / 1e12}
         del a4, b4, c4
+
+    if not args.quick:
+        also.update(context_measurements(torch, rt, L, stream, dev))
 
     # End to end through the C ABI with host buffers.
     a_h = a.cpu().pin_memory()
@@ -429,7 +503,8 @@ def run_multi(args, rank, local_rank, world):
                          "peak_kind": f"of {kind} (sustained cuBLAS bf16), per GPU",
                          "nvlink_egress_bytes_per_gpu": egress,
                          "nvlink_bound_ms": egress / 770e9 * 1e3,
-                         "compute_bound_ms": flops / world / (sustained * 1e12) * 1e3},
+                         "compute_bound_ms": flops / world / (sustained * 1e12) * 1e3,
+                         "frac_of_fused_bound": max(egress / 770e9 * 1e3, flops / world / (sustained * 1e12) * 1e3) / ms},
             "gemm_only": {"ms_per_step": ms_local, "tflops": flops / (ms_local * 1e-3) / 1e12},
             "cpu_baseline": None,
         }
