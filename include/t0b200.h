@@ -234,6 +234,19 @@ T0B_API int32_t t0b_dispatch_kernargs(t0b_ctx* ctx, const t0b_gemm_config* cfg, 
 T0B_API int32_t t0b_tune(t0b_ctx* ctx, uint32_t m, uint32_t n, uint32_t k, int32_t trans_a, int32_t trans_b,
                          int32_t out_dtype, t0b_gemm_config* best, float* best_tflops);
 
+/* Autotune cache on disk, the reference's wire format (src/t0/auto_gemm.rs:325-391): one file
+ * <dir>/gemm_<M>x<N>x<K>.json holding {"tile_m":..,"tile_n":..,"tile_k":..,"wg_size":..,"split_k":..,"lds_pad":..,
+ * "n_col_passes":..,"wgp":bool,"swap":bool,"tflops":..,"all":[..]}.  dir NULL = $T0_AUTOTUNE_DIR, else
+ * $HOME/.t0_autotune.  load returns T0B_ERR_INVALID when there is no (parsable) entry.  t0b_tune consults and
+ * updates this cache when the context has a directory set with t0b_set_autotune_dir. */
+T0B_API int32_t t0b_tune_cache_save(const char* dir, uint32_t m, uint32_t n, uint32_t k, const t0b_gemm_config* cfg,
+                                    float tflops);
+T0B_API int32_t t0b_tune_cache_load(const char* dir, uint32_t m, uint32_t n, uint32_t k, t0b_gemm_config* cfg,
+                                    float* tflops);
+/* GemmTuner::invalidate / clear (auto_gemm.rs:394-404). */
+T0B_API int32_t t0b_tune_cache_invalidate(const char* dir, uint32_t m, uint32_t n, uint32_t k);
+T0B_API int32_t t0b_set_autotune_dir(t0b_ctx* ctx, const char* dir);
+
 /* ------------------------------------------------------------------------------------------------
  * Element-wise and row kernels around the GEMMs (f32 activations)
  * ---------------------------------------------------------------------------------------------- */

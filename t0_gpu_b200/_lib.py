@@ -81,6 +81,10 @@ SIGNATURES = {
     "t0b_splitk_reduce": (_i32, [_ctx, _u64, _u32, _u32, _u32, _u64, _u64, _u64, _u64, _i32, _i32, _u64, _f, _i32]),
     "t0b_dispatch_kernargs": (_i32, [_ctx, _cfgp, _u32, _u32, _u8p, _sz, _i32]),
     "t0b_tune": (_i32, [_ctx, _u32, _u32, _u32, _i32, _i32, _i32, _cfgp, C.POINTER(_f)]),
+    "t0b_tune_cache_save": (_i32, [C.c_char_p, _u32, _u32, _u32, _cfgp, _f]),
+    "t0b_tune_cache_load": (_i32, [C.c_char_p, _u32, _u32, _u32, _cfgp, C.POINTER(_f)]),
+    "t0b_tune_cache_invalidate": (_i32, [C.c_char_p, _u32, _u32, _u32]),
+    "t0b_set_autotune_dir": (_i32, [_ctx, C.c_char_p]),
     "t0b_cast_f32_to_bf16": (_i32, [_ctx, _u64, _u64, _sz, _i32]),
     "t0b_cast_f32_to_bf16_transpose": (_i32, [_ctx, _u64, _u64, _u32, _u32, _i32]),
     "t0b_rmsnorm_fwd": (_i32, [_ctx, _u64, _u64, _u64, _u64, _u32, _u32, _f, _i32]),

@@ -66,6 +66,7 @@ struct GemmParams {
     unsigned mn_lbo, mn_sbo, mn_kstep;  // descriptor byte offsets for M/N-contiguous operands
     int* status;
     unsigned long long wait_limit_ns;
+    int tma_store;          // 1: the epilogue writes C with TMA stores through the third tensor map
     int l2_prefetch;        // > 0: prefetch the K block this many blocks ahead into L2
     int diag;               // 0 normal; diagnostics only (results are garbage): 1 = loads without MMA, 2 = MMA without loads
 };
@@ -91,7 +92,7 @@ struct GemmTraits {
     static constexpr int kATileBytes = MT * kASubTileBytes;
     static constexpr int kBTileBytes = kBnCta * kBk * 2;
     static constexpr int kStageBytes = kATileBytes + kBTileBytes;
-    static constexpr int kCtrlBytes = 512;
+    static constexpr int kCtrlBytes = 1024;   // keeps the transpose tiles behind it 1024-byte aligned (TMA swizzle)
     static constexpr int kEpiWarps = 4 * MT;
     static constexpr int kEpiStagingBytes = kEpiWarps * 4096;   // one 32x32 f32 transpose tile per epilogue warp
     static constexpr int kBudget = 227 * 1024 - 1024 - kCtrlBytes - kEpiStagingBytes;
@@ -276,7 +277,7 @@ __device__ __forceinline__ void flush_pair_bf16(uint32_t stage, int lane, __nv_b
 template <int BN, int CG, int MT>
 __global__ void __launch_bounds__(GemmTraits<BN, CG, MT>::kThreads, 1)
 gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                         const GemmParams p) {
+                         const __grid_constant__ CUtensorMap tmap_c, const GemmParams p) {
     using T = GemmTraits<BN, CG, MT>;
     constexpr int S = T::kStages;
     constexpr int BM = T::kBm;
@@ -510,7 +511,9 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
         const bool need_bias = (epi == EPI_BIAS || epi == EPI_BIAS_RELU) && p.bias != nullptr;
         // The transposing path needs whole 16-byte pieces inside [0, N): N % 4 (f32) or N % 8 (bf16).
         const bool out16 = !to_slab && p.out_bf16;
-        const bool staged = vec_ok && (p.N % (out16 ? 8 : 4) == 0);
+        const bool tma_out = p.tma_store != 0;   // implies one destination, no slabs, TMA-addressable C
+        const bool staged = tma_out || (vec_ok && (p.N % (out16 ? 8 : 4) == 0));
+        if (tma_out && lane == 0) ptx::prefetch_tmap(&tmap_c);
         const uint32_t stage = ctrl + T::kCtrlBytes + static_cast<uint32_t>(warp - 2) * 4096u;
         long long t_drain = 0, t_store = 0;
         for (int w = cluster_id; w < num_work; w += num_clusters) {
@@ -546,7 +549,10 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                 if (p.diag == 7) {
                 } else if (staged && out16) {
                     const int half = c & 1;
-                    if (half == 0) __syncwarp();   // the previous pair's reads of the staging tile are done
+                    if (half == 0) {
+                        if (tma_out && lane == 0) ptx::bulk_wait_group_read<0>();   // the TMA store has read the tile
+                        __syncwarp();   // the previous pair's reads of the staging tile are done
+                    }
                     if (row0 < p.M && ncols > 0) {   // warp-uniform
                         float v[32];
 #pragma unroll
@@ -561,7 +567,15 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                         }
                         stage_half_bf16(stage, lane, half, v);
                     }
-                    if (half == 1) {
+                    if (half == 1 && tma_out) {
+                        ptx::fence_proxy_async_smem();
+                        __syncwarp();
+                        const int cbase = col0 - 32;
+                        if (row0 < p.M && cbase < p.N && lane == 0 && p.diag != 6) {
+                            ptx::tma_store_2d(&tmap_c, stage, cbase, row0);
+                            ptx::bulk_commit_group();
+                        }
+                    } else if (half == 1) {
                         __syncwarp();
                         const int cbase = col0 - 32;
                         if (row0 < p.M && cbase < p.N && p.diag != 6) {
@@ -582,10 +596,17 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                                 v[j] = apply_epilogue(v[j], epi, b, p.alpha);
                             }
                         }
+                        if (tma_out && lane == 0) ptx::bulk_wait_group_read<0>();   // the TMA store has read the tile
                         __syncwarp();   // the previous chunk's reads of the staging tile are done
                         stage_chunk_f32(stage, lane, v);
+                        if (tma_out) ptx::fence_proxy_async_smem();
                         __syncwarp();
                         if (p.diag == 6) {
+                        } else if (tma_out) {
+                            if (lane == 0) {
+                                ptx::tma_store_2d(&tmap_c, stage, col0, row0);
+                                ptx::bulk_commit_group();
+                            }
                         } else if (to_slab) {
                             flush_chunk_f32(stage, lane, p.partial + static_cast<long long>(wi.split) * p.slab_stride, ld_out,
                                             row0, col0, p.M, p.N);
@@ -626,6 +647,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                 slot_phase ^= 1u;
             }
         }
+        if (tma_out && lane == 0) ptx::bulk_wait_group<0>();   // every TMA store of this warp has completed
         if (p.diag >= 5 && blockIdx.x == 0 && threadIdx.x == 64) {
             volatile int* dbg = reinterpret_cast<volatile int*>(p.status);
             dbg[7] = static_cast<int>(t_drain >> 4);

@@ -32,11 +32,11 @@ EncodeTiledFn encode_tiled_fn() {
     return fn;
 }
 
-// 2-D bf16 tensor map: inner (contiguous) extent d0, outer extent d1, outer pitch ld elements, box b0 x b1,
-// 128-byte swizzle, out-of-bounds elements read as zero.
+// 2-D tensor map (bf16, or f32 when elem == 4): inner (contiguous) extent d0, outer extent d1, outer pitch ld
+// elements, box b0 x b1, 128-byte swizzle; out-of-bounds elements read as zero and are not written.
 int32_t get_tmap(t0b_ctx* ctx, uint64_t ptr, uint64_t d0, uint64_t d1, uint64_t ld, uint32_t b0, uint32_t b1,
-                 CUtensorMap* out) {
-    t0b_ctx::TmapKey key{ptr, d0, d1, ld, b0, b1};
+                 CUtensorMap* out, uint32_t elem = 2) {
+    t0b_ctx::TmapKey key{ptr, d0, d1, ld, b0, b1, elem};
     auto it = ctx->tmaps.find(key);
     if (it != ctx->tmaps.end()) {
         *out = it->second;
@@ -45,10 +45,10 @@ int32_t get_tmap(t0b_ctx* ctx, uint64_t ptr, uint64_t d0, uint64_t d1, uint64_t 
     EncodeTiledFn fn = encode_tiled_fn();
     if (!fn) return set_error(ctx, T0B_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
     cuuint64_t dims[2] = {d0, d1};
-    cuuint64_t strides[1] = {ld * 2};
+    cuuint64_t strides[1] = {ld * elem};
     cuuint32_t box[2] = {b0, b1};
     cuuint32_t estr[2] = {1, 1};
-    CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, reinterpret_cast<void*>(ptr), dims, strides, box, estr,
+    CUresult r = fn(out, elem == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, reinterpret_cast<void*>(ptr), dims, strides, box, estr,
                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS)
@@ -62,7 +62,8 @@ int32_t get_tmap(t0b_ctx* ctx, uint64_t ptr, uint64_t d0, uint64_t d1, uint64_t 
 }
 
 template <int BN, int CG, int MT>
-int32_t launch_variant(t0b_ctx* ctx, const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int num_work) {
+int32_t launch_variant(t0b_ctx* ctx, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc,
+                       const GemmParams& p, int num_work) {
     using T = GemmTraits<BN, CG, MT>;
     auto kfn = gemm_bf16_tcgen05_kernel<BN, CG, MT>;
     static bool configured[64] = {};
@@ -112,7 +113,7 @@ int32_t launch_variant(t0b_ctx* ctx, const CUtensorMap& ta, const CUtensorMap& t
     attrs[0].val.clusterDim.z = 1;
     cfg.attrs = attrs;
     cfg.numAttrs = 1;
-    return check_cuda(ctx, cudaLaunchKernelEx(&cfg, kfn, ta, tb, p), "cudaLaunchKernelEx(gemm)");
+    return check_cuda(ctx, cudaLaunchKernelEx(&cfg, kfn, ta, tb, tc, p), "cudaLaunchKernelEx(gemm)");
 }
 
 struct GemmCall {
@@ -306,15 +307,32 @@ int32_t run_gemm(t0b_ctx* ctx, const GemmCall& g) {
             // One slab: store straight into it as f32.
             p.out_bf16 = 0; p.epilogue = EPI_STORE; p.n_dst = 1; p.ldc = static_cast<long long>(ld_partial);
         }
+        // Epilogue through TMA stores when there is one plain destination the TMA unit can address; peers and
+        // split-K slabs keep the warp-issued stores.
+        CUtensorMap tc = ta;
+        {
+            const uint32_t oelem = p.out_bf16 ? 2u : 4u;
+            static const int no_tma_store = [] { const char* e = getenv("T0B_GEMM_NO_TMA_STORE"); return e ? atoi(e) : 0; }();
+            // TMA clips a store at the tensor edge in 16-byte units, so N must be a whole number of them for
+            // nothing beyond column N to be touched.
+            const bool ok = !to_slabs && p.n_dst == 1 && (g.c_dst[0] % 16 == 0) && ((static_cast<uint64_t>(p.ldc) * oelem) % 16 == 0) &&
+                            ((static_cast<uint64_t>(g.n) * oelem) % 16 == 0) && !no_tma_store;
+            p.tma_store = 0;
+            if (ok) {
+                rc = get_tmap(ctx, g.c_dst[0], g.n, g.m, static_cast<uint64_t>(p.ldc), p.out_bf16 ? 64 : 32, 32, &tc, oelem);
+                if (rc != T0B_OK) return rc;
+                p.tma_store = 1;
+            }
+        }
         const int num_work = p.tiles_m * p.tiles_n * p.split_k;
         if (plan.cta_group == 2) {
-            if (plan.m_tiles == 2) rc = launch_variant<256, 2, 2>(ctx, ta, tb, p, num_work);
-            else if (plan.bn == 256) rc = launch_variant<256, 2, 1>(ctx, ta, tb, p, num_work);
-            else rc = launch_variant<128, 2, 1>(ctx, ta, tb, p, num_work);
+            if (plan.m_tiles == 2) rc = launch_variant<256, 2, 2>(ctx, ta, tb, tc, p, num_work);
+            else if (plan.bn == 256) rc = launch_variant<256, 2, 1>(ctx, ta, tb, tc, p, num_work);
+            else rc = launch_variant<128, 2, 1>(ctx, ta, tb, tc, p, num_work);
         } else {
-            if (plan.bn == 256) rc = launch_variant<256, 1, 1>(ctx, ta, tb, p, num_work);
-            else if (plan.bn == 128) rc = launch_variant<128, 1, 1>(ctx, ta, tb, p, num_work);
-            else rc = launch_variant<64, 1, 1>(ctx, ta, tb, p, num_work);
+            if (plan.bn == 256) rc = launch_variant<256, 1, 1>(ctx, ta, tb, tc, p, num_work);
+            else if (plan.bn == 128) rc = launch_variant<128, 1, 1>(ctx, ta, tb, tc, p, num_work);
+            else rc = launch_variant<64, 1, 1>(ctx, ta, tb, tc, p, num_work);
         }
         if (rc != T0B_OK) return rc;
         ++ctx->launches;
@@ -511,6 +529,17 @@ int32_t t0b_tune(t0b_ctx* ctx, uint32_t m, uint32_t n, uint32_t k, int32_t trans
     int32_t rc = precheck(ctx);
     if (rc != T0B_OK) return rc;
     if (!best || m == 0 || n == 0 || k == 0) return set_error(ctx, T0B_ERR_INVALID, "tune: bad arguments");
+    const std::string tkey = std::to_string(m) + "x" + std::to_string(n) + "x" + std::to_string(k) + "/" +
+                             std::to_string(trans_a != 0) + std::to_string(trans_b != 0) + std::to_string(out_dtype == T0B_OUT_BF16);
+    if (!ctx->autotune_dir.empty() && !trans_a && trans_b && out_dtype == T0B_OUT_F32) {
+        // The disk cache is keyed by (M, N, K) only, like the reference's; it describes the NT / f32-out kernel.
+        float tf = 0.0f;
+        if (t0b_tune_cache_load(ctx->autotune_dir.c_str(), m, n, k, best, &tf) == T0B_OK) {
+            if (best_tflops) *best_tflops = tf;
+            ctx->tuned[tkey] = *best;
+            return T0B_OK;
+        }
+    }
     const size_t elem = out_dtype == T0B_OUT_BF16 ? 2 : 4;
     uint64_t a = 0, b = 0, c = 0;
     rc = t0b_alloc_zero(ctx, static_cast<size_t>(m) * k * 2, &a);
@@ -550,6 +579,8 @@ done:
     const std::string key = std::to_string(m) + "x" + std::to_string(n) + "x" + std::to_string(k) + "/" +
                             std::to_string(trans_a != 0) + std::to_string(trans_b != 0) + std::to_string(out_dtype == T0B_OUT_BF16);
     ctx->tuned[key] = *best;
+    if (!ctx->autotune_dir.empty() && !trans_a && trans_b && out_dtype == T0B_OUT_F32)
+        t0b_tune_cache_save(ctx->autotune_dir.c_str(), m, n, k, best, best_tflops ? *best_tflops : 0.0f);
     return T0B_OK;
 }
 

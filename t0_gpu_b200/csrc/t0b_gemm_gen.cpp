@@ -1,9 +1,15 @@
 // Host-side GEMM front-end: GemmConfig presets, names, grids, kernarg blobs, auto_select and the mapping of a
 // GemmConfig onto the sm_100a kernel family.  Mirrors the public functions of src/t0/gemm_gen.rs (reference
 // project paths); the RDNA3 code generator behind them is replaced by precompiled tcgen05 kernels.
+#include <sys/stat.h>
+
 #include <algorithm>
 #include <cmath>
+#include <cstdio>
+#include <cstdlib>
 #include <cstring>
+#include <fstream>
+#include <sstream>
 #include <string>
 
 #include "t0b_internal.hpp"
@@ -84,7 +90,7 @@ int stage_bytes(uint32_t bn, uint32_t cg, uint32_t mt) {
 
 int stages_for(uint32_t bn, uint32_t cg, uint32_t mt) {
     const int stage = stage_bytes(bn, cg, mt);
-    const int budget = 227 * 1024 - 1024 - 512 - static_cast<int>(mt) * 4 * 4096;   // minus the epilogue transpose tiles
+    const int budget = 227 * 1024 - 1024 - 1024 - static_cast<int>(mt) * 4 * 4096;   // minus the epilogue transpose tiles
     return std::min(8, budget / stage);
 }
 
@@ -157,7 +163,7 @@ void resolve_plan(const t0b_gemm_config* cfg_in, const PlanInput& in, t0b_gemm_p
     const uint64_t tiles = static_cast<uint64_t>((in.m + p.bm - 1) / p.bm) * ((in.n + p.bn - 1) / p.bn) * p.split_k;
     const uint64_t clusters = static_cast<uint64_t>(num_sms) / p.cta_group;
     p.grid = static_cast<uint32_t>(std::min<uint64_t>(tiles, clusters) * p.cta_group);
-    p.smem_bytes = p.stages * stage_bytes(p.bn, p.cta_group, p.m_tiles) + 1024 + 512 + p.m_tiles * 4 * 4096;
+    p.smem_bytes = p.stages * stage_bytes(p.bn, p.cta_group, p.m_tiles) + 1024 + 1024 + p.m_tiles * 4 * 4096;
     *out = p;
 }
 
@@ -380,6 +386,82 @@ size_t t0b_gemm_workspace_bytes(const t0b_gemm_config* cfg, uint32_t m, uint32_t
     t0b::PlanInput in{m, n, k, 0, 1, k, k, 0, 0, 148};
     t0b::resolve_plan(cfg, in, &p);
     return p.split_k > 1 ? static_cast<size_t>(p.split_k) * m * n * 4 : 0;
+}
+
+// ------------------------------------------------------------------------------------------------ autotune cache
+
+static std::string tune_dir(const char* dir) {
+    if (dir && *dir) return dir;
+    if (const char* e = std::getenv("T0_AUTOTUNE_DIR")) return e;
+    const char* home = std::getenv("HOME");
+    return std::string(home ? home : ".") + "/.t0_autotune";
+}
+static std::string tune_path(const char* dir, uint32_t m, uint32_t n, uint32_t k) {
+    return tune_dir(dir) + "/gemm_" + std::to_string(m) + "x" + std::to_string(n) + "x" + std::to_string(k) + ".json";
+}
+// Minimal key lookup in the flat JSON object the cache files hold.
+static bool json_number(const std::string& text, const char* key, double* out) {
+    const std::string pat = std::string("\"") + key + "\":";
+    const size_t at = text.find(pat);
+    if (at == std::string::npos) return false;
+    const char* p = text.c_str() + at + pat.size();
+    char* end = nullptr;
+    const double v = std::strtod(p, &end);
+    if (end == p) return false;
+    *out = v;
+    return true;
+}
+
+int32_t t0b_tune_cache_save(const char* dir, uint32_t m, uint32_t n, uint32_t k, const t0b_gemm_config* c, float tflops) {
+    if (!c) return T0B_ERR_INVALID;
+    const std::string d = tune_dir(dir);
+    ::mkdir(d.c_str(), 0755);
+    char name[160];
+    t0b_config_name(c, name, sizeof(name));
+    char buf[640];
+    std::snprintf(buf, sizeof(buf),
+                  "{\"tile_m\":%u,\"tile_n\":%u,\"tile_k\":%u,\"wg_size\":%u,\"split_k\":%u,\"lds_pad\":%u,\"n_col_passes\":%u,"
+                  "\"wgp\":%s,\"swap\":%s,\"tflops\":%.2f,\"all\":[[\"%s\",%.2f]]}",
+                  c->tile_m, c->tile_n, c->tile_k, c->wg_size, c->split_k > 1 ? c->split_k : 1u, c->lds_pad, c->n_col_passes,
+                  c->wgp_mode ? "true" : "false", c->swap_grid ? "true" : "false", tflops, name, tflops);
+    std::ofstream f(tune_path(dir, m, n, k));
+    if (!f) return T0B_ERR_INVALID;
+    f << buf;
+    return f.good() ? T0B_OK : T0B_ERR_INVALID;
+}
+
+int32_t t0b_tune_cache_load(const char* dir, uint32_t m, uint32_t n, uint32_t k, t0b_gemm_config* c, float* tflops) {
+    if (!c) return T0B_ERR_INVALID;
+    std::ifstream f(tune_path(dir, m, n, k));
+    if (!f) return T0B_ERR_INVALID;
+    std::stringstream ss;
+    ss << f.rdbuf();
+    const std::string text = ss.str();
+    double tm, tn, tk, wg, tf, v;
+    if (!json_number(text, "tile_m", &tm) || !json_number(text, "tile_n", &tn) || !json_number(text, "tile_k", &tk) ||
+        !json_number(text, "wg_size", &wg) || !json_number(text, "tflops", &tf))
+        return T0B_ERR_INVALID;
+    t0b_gemm_config cfg = make_cfg(static_cast<uint32_t>(tm), static_cast<uint32_t>(tn), static_cast<uint32_t>(tk),
+                                   static_cast<uint32_t>(wg), true, true);
+    cfg.split_k = (json_number(text, "split_k", &v) && v > 1) ? static_cast<uint32_t>(v) : 0;
+    cfg.lds_pad = json_number(text, "lds_pad", &v) ? static_cast<uint32_t>(v) : 0;
+    cfg.n_col_passes = json_number(text, "n_col_passes", &v) ? static_cast<uint32_t>(v) : 1;
+    cfg.wgp_mode = text.find("\"wgp\":true") != std::string::npos;
+    cfg.swap_grid = text.find("\"swap\":true") != std::string::npos;
+    *c = cfg;
+    if (tflops) *tflops = static_cast<float>(tf);
+    return T0B_OK;
+}
+
+int32_t t0b_tune_cache_invalidate(const char* dir, uint32_t m, uint32_t n, uint32_t k) {
+    std::remove(tune_path(dir, m, n, k).c_str());
+    return T0B_OK;
+}
+
+int32_t t0b_set_autotune_dir(t0b_ctx* ctx, const char* dir) {
+    if (!ctx) return T0B_ERR_INVALID;
+    ctx->autotune_dir = tune_dir(dir);
+    return T0B_OK;
 }
 
 const char* t0b_version(void) { return "t0b200 0.1 (sm_100a)"; }

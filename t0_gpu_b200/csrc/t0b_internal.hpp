@@ -37,9 +37,9 @@ struct t0b_ctx {
     // Tensor-map cache.
     struct TmapKey {
         uint64_t ptr, d0, d1, ld;
-        uint32_t b0, b1;
+        uint32_t b0, b1, elem;
         bool operator==(const TmapKey& o) const {
-            return ptr == o.ptr && d0 == o.d0 && d1 == o.d1 && ld == o.ld && b0 == o.b0 && b1 == o.b1;
+            return ptr == o.ptr && d0 == o.d0 && d1 == o.d1 && ld == o.ld && b0 == o.b0 && b1 == o.b1 && elem == o.elem;
         }
     };
     struct TmapHash {
@@ -49,6 +49,7 @@ struct t0b_ctx {
             h ^= (k.d1 + 0x9E3779B97F4A7C15ull + (h << 6) + (h >> 2));
             h ^= (k.ld + 0x9E3779B97F4A7C15ull + (h << 6) + (h >> 2));
             h ^= ((static_cast<uint64_t>(k.b0) << 32 | k.b1) + (h << 6) + (h >> 2));
+            h ^= (k.elem + 0x9E3779B97F4A7C15ull + (h << 6) + (h >> 2));
             return static_cast<size_t>(h);
         }
     };
@@ -60,6 +61,7 @@ struct t0b_ctx {
     uint64_t launches = 0;
     // In-memory autotune results keyed by "MxNxK/ta/tb/out".
     std::unordered_map<std::string, t0b_gemm_config> tuned;
+    std::string autotune_dir;   // empty: the disk cache is not consulted
 };
 
 namespace t0b {

@@ -171,3 +171,32 @@ def test_split_k_selected_for_small_grids():
     assert (c.split_k or 1) >= 4
     assert t.auto_select(8192, 8192, 8192).split_k is None
     assert _lib.lib().t0b_gemm_workspace_bytes(C.byref(c.to_c()), 512, 512, 16384) == (c.split_k) * 512 * 512 * 4
+
+
+def test_autotune_cache_roundtrip(tmp_path):
+    """src/t0/auto_gemm.rs:578-610: save + load of the per-shape JSON cache, and a file in the reference's own
+    format (as its `save_cache` writes it) parses to the same config."""
+    d = str(tmp_path / "t0_autotune_cache_test").encode()
+    L = _lib.lib()
+    cfg = GemmConfig.tile_128x64_k32()
+    assert L.t0b_tune_cache_save(d, 4096, 4096, 4096, C.byref(cfg.to_c()), 79.2) == 0
+    out = _lib.GemmConfigC()
+    tf = C.c_float()
+    assert L.t0b_tune_cache_load(d, 4096, 4096, 4096, C.byref(out), C.byref(tf)) == 0
+    got = GemmConfig.from_c(out)
+    assert (got.tile_m, got.tile_n, got.tile_k, got.wg_size) == (128, 64, 32, 128)
+    assert abs(tf.value - 79.2) < 0.1 and got.split_k is None and got.wgp_mode and got.swap_grid
+    text = open(os.path.join(d.decode(), "gemm_4096x4096x4096.json")).read()
+    assert text.startswith('{"tile_m":128,"tile_n":64,"tile_k":32,"wg_size":128,"split_k":1,"lds_pad":0,"n_col_passes":1,'
+                           '"wgp":true,"swap":true,"tflops":79.20,"all":[["t0_gemm_128x64_k32_ldsdb_wgp",79.20]')
+    # a file written by the reference (two entries in "all", split_k 4, swap false)
+    with open(os.path.join(d.decode(), "gemm_512x512x16384.json"), "w") as f:
+        f.write('{"tile_m":64,"tile_n":64,"tile_k":16,"wg_size":64,"split_k":4,"lds_pad":0,"n_col_passes":1,'
+                '"wgp":true,"swap":false,"tflops":14.25,"all":[["t0_gemm_64x64_k16_ldsdb_sk4_mg_wgp",14.25],["x",1.00]]}')
+    assert L.t0b_tune_cache_load(d, 512, 512, 16384, C.byref(out), C.byref(tf)) == 0
+    got = GemmConfig.from_c(out)
+    assert (got.tile_m, got.split_k, got.swap_grid, got.wgp_mode) == (64, 4, False, True) and abs(tf.value - 14.25) < 1e-3
+    assert got.name() == "t0_gemm_64x64_k16_ldsdb_sk4_mg_wgp"
+    # invalidate removes the entry; loading a missing entry fails
+    assert L.t0b_tune_cache_invalidate(d, 4096, 4096, 4096) == 0
+    assert L.t0b_tune_cache_load(d, 4096, 4096, 4096, C.byref(out), C.byref(tf)) != 0
