@@ -68,6 +68,7 @@ typedef struct t0b_gemm_plan {
     uint32_t bm, bn, bk;       /* cluster tile: bm = 128 * cta_group * m_tiles */
     uint32_t cta_group;        /* 1, or 2 = CTA pair sharing one tcgen05.mma (tile_m >= 256) */
     uint32_t m_tiles;          /* 128-row A tiles per CTA: 1, or 2 (tile_m >= 512: both TMEM accumulators serve one tile) */
+    uint32_t n_tiles;          /* N-adjacent accumulators per tile: 1, or 2 (tile_n >= 512: bn = 2 x 256, A shared) */
     uint32_t stages;
     uint32_t split_k;          /* effective split (>= 1); may be lower than asked when K has too few 64-blocks */
     uint32_t kb_per_split;     /* 64-wide K blocks per split */
@@ -79,7 +80,7 @@ typedef struct t0b_gemm_plan {
 /* GemmConfig presets by name ("16x64_k16", "32x64_direct", "32x64_k16", "32x64_k32", "32x128_k16", "64x64_k16",
  * "64x64_k32", "128x64_k16", "64x128_k16", "128x64_k32", "128x128_k16", "64x64_k64", "128x128_2pass",
  * "64x128_2pass"): gemm_gen.rs:86-145.  B200-native presets: "b200_128x64", "b200_128x128", "b200_128x256",
- * "b200_256x128", "b200_256x256", "b200_512x256". */
+ * "b200_256x128", "b200_256x256", "b200_512x256", "b200_256x512". */
 T0B_API int32_t t0b_config_preset(const char* name, t0b_gemm_config* out);
 /* GemmConfig::name(), gemm_gen.rs:207-227 (the kernel-cache / autotune key). Returns the length written. */
 T0B_API int32_t t0b_config_name(const t0b_gemm_config* cfg, char* buf, size_t cap);

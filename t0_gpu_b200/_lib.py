@@ -17,7 +17,7 @@ class GemmConfigC(C.Structure):
 
 class GemmPlanC(C.Structure):
     _fields_ = [(n, C.c_uint32) for n in (
-        "bm", "bn", "bk", "cta_group", "m_tiles", "stages", "split_k", "kb_per_split", "use_tma", "grid", "smem_bytes")]
+        "bm", "bn", "bk", "cta_group", "m_tiles", "n_tiles", "stages", "split_k", "kb_per_split", "use_tma", "grid", "smem_bytes")]
 
 
 _u32, _u64, _i32, _sz, _f = C.c_uint32, C.c_uint64, C.c_int32, C.c_size_t, C.c_float

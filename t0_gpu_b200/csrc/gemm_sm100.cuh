@@ -82,15 +82,22 @@ constexpr int kASubTileBytes = kBmCta * kBk * 2;   // one 128-row A tile of a st
 //   MT = 2: both slots belong to the same tile, which is (256*CG) x BN: every B tile is used by two MMAs, so the
 //           shared-memory fill traffic per FLOP drops by a quarter; each slot has its own epilogue warp group and
 //           the slots drain in parallel.
-template <int BN, int CG, int MT>
+template <int BN, int CG, int MT, int ND = 0>
 struct GemmTraits {
     static_assert(BN == 64 || BN == 128 || BN == 256, "BN");
     static_assert(CG == 1 || CG == 2, "CG");
     static_assert(MT == 1 || MT == 2, "MT");
+    static_assert(ND == 0 || (ND == 1 && MT == 2), "the N-direction double tile uses both accumulator slots");
+    // ND == 1: the two slots hold two N-adjacent tiles that share one A tile (tile = (128*CG) x (2*BN)); consecutive
+    // MMAs then take A from the tensor core's collector, which removes a quarter of the operand reads from shared
+    // memory compared with two M-adjacent tiles sharing B.
+    static constexpr int kATiles = ND ? 1 : MT;
+    static constexpr int kBTiles = ND ? 2 : 1;
     static constexpr int kBnCta = BN / CG;               // B rows this CTA loads
     static_assert(kBnCta % 64 == 0, "each CTA's B slice must be whole 64-column swizzle blocks");
-    static constexpr int kATileBytes = MT * kASubTileBytes;
-    static constexpr int kBTileBytes = kBnCta * kBk * 2;
+    static constexpr int kATileBytes = kATiles * kASubTileBytes;
+    static constexpr int kBSubTileBytes = kBnCta * kBk * 2;
+    static constexpr int kBTileBytes = kBTiles * kBSubTileBytes;
     static constexpr int kStageBytes = kATileBytes + kBTileBytes;
     static constexpr int kCtrlBytes = 1024;   // keeps the transpose tiles behind it 1024-byte aligned (TMA swizzle)
     static constexpr int kEpiWarps = 4 * MT;
@@ -101,7 +108,8 @@ struct GemmTraits {
     static constexpr int kTmemCols = 2 * BN;             // two accumulator slots
     static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + kCtrlBytes + kEpiStagingBytes;
     static constexpr int kThreads = 64 + 32 * kEpiWarps;
-    static constexpr int kBm = kBmCta * CG * MT;         // rows of the cluster tile
+    static constexpr int kBm = kBmCta * CG * kATiles;    // rows of the cluster tile
+    static constexpr int kTileN = BN * kBTiles;          // columns of the cluster tile
 };
 
 struct WorkItem {
@@ -274,13 +282,14 @@ __device__ __forceinline__ void flush_pair_bf16(uint32_t stage, int lane, __nv_b
     }
 }
 
-template <int BN, int CG, int MT>
-__global__ void __launch_bounds__(GemmTraits<BN, CG, MT>::kThreads, 1)
+template <int BN, int CG, int MT, int ND = 0>
+__global__ void __launch_bounds__(GemmTraits<BN, CG, MT, ND>::kThreads, 1)
 gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                          const __grid_constant__ CUtensorMap tmap_c, const GemmParams p) {
-    using T = GemmTraits<BN, CG, MT>;
+    using T = GemmTraits<BN, CG, MT, ND>;
     constexpr int S = T::kStages;
     constexpr int BM = T::kBm;
+    constexpr int BNT = T::kTileN;
     constexpr int kMmaM = kBmCta * CG;    // rows of one MMA (128 or 256)
 
     extern __shared__ uint8_t smem_raw[];
@@ -345,7 +354,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
             long long t_empty = 0;
             const long long tp_begin = clock64();
             for (int w = cluster_id; w < num_work && ok; w += num_clusters) {
-                const WorkItem wi = decode_work(p, w, BM, BN);
+                const WorkItem wi = decode_work(p, w, BM, BNT);
                 int m0_cta = wi.m0 + static_cast<int>(cta_rank) * kBmCta;
                 int n0_cta = wi.n0 + static_cast<int>(cta_rank) * T::kBnCta;
                 if (p.diag == 3) { m0_cta = static_cast<int>(cta_rank) * kBmCta; n0_cta = static_cast<int>(cta_rank) * T::kBnCta; }
@@ -364,7 +373,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                         else ptx::tma_load_2d_pair(dst, m, bar, c0, c1);
                     };
 #pragma unroll
-                    for (int mt = 0; mt < MT; ++mt) {
+                    for (int mt = 0; mt < T::kATiles; ++mt) {
                         const int m_sub = m0_cta + mt * kMmaM;
                         const uint32_t dst = a_dst + mt * kASubTileBytes;
                         if (!p.a_mn_major) {
@@ -374,18 +383,23 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                             load(dst + 8192, &tmap_a, m_sub + 64, k0);
                         }
                     }
-                    if (p.diag == 4) {
-                    } else if (!p.b_mn_major) {
-                        load(b_dst, &tmap_b, k0, n0_cta);
-                    } else {
 #pragma unroll
-                        for (int j = 0; j < T::kBnCta / 64; ++j) load(b_dst + j * 8192, &tmap_b, n0_cta + j * 64, k0);
+                    for (int nt = 0; nt < T::kBTiles; ++nt) {
+                        const int n_sub = n0_cta + nt * BN;
+                        const uint32_t dst = b_dst + nt * T::kBSubTileBytes;
+                        if (p.diag == 4) {
+                        } else if (!p.b_mn_major) {
+                            load(dst, &tmap_b, k0, n_sub);
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < T::kBnCta / 64; ++j) load(dst + j * 8192, &tmap_b, n_sub + j * 64, k0);
+                        }
                     }
                     if (p.l2_prefetch > 0 && kb + p.l2_prefetch < wi.kb_end) {
                         // Pull a K block further ahead into L2 so the later shared-memory fill finds it there.
                         const int kp = (kb + p.l2_prefetch) * kBk;
 #pragma unroll
-                        for (int mt = 0; mt < MT; ++mt) {
+                        for (int mt = 0; mt < T::kATiles; ++mt) {
                             const int m_sub = m0_cta + mt * kMmaM;
                             if (!p.a_mn_major) ptx::tma_prefetch_2d(&tmap_a, kp, m_sub);
                             else { ptx::tma_prefetch_2d(&tmap_a, m_sub, kp); ptx::tma_prefetch_2d(&tmap_a, m_sub + 64, kp); }
@@ -430,7 +444,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
             long long t_full = 0, t_tempty = 0;
             const long long t_begin = clock64();
             for (int w = cluster_id; w < num_work && ok; w += num_clusters) {
-                const WorkItem wi = decode_work(p, w, BM, BN);
+                const WorkItem wi = decode_work(p, w, BM, BNT);
                 if constexpr (MT == 1) {
                     if (!bounded_wait(tempty_bar(acc), slot_ph[acc] ^ 1u, ctl, DEV_TIMEOUT_TMEM_EMPTY)) { ok = false; break; }
                     ptx::tc_fence_after();
@@ -444,21 +458,40 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                     const uint32_t b_addr = a_addr + T::kATileBytes;
 #pragma unroll
                     for (int k = 0; k < kBk / kUmmaK; ++k) {
-                        const uint64_t bdesc = make_smem_desc(b_addr + k * b_kstep, b_lbo, b_sbo);
+                        const uint32_t acc_flag = (kb > wi.kb_begin || k > 0) ? 1u : 0u;
+                        if constexpr (ND == 1) {
+                            // One A slice, two B slices: the second MMA takes A from the collector.
+                            const uint64_t adesc = make_smem_desc(a_addr + k * a_kstep, a_lbo, a_sbo);
 #pragma unroll
-                        for (int mt = 0; mt < MT; ++mt) {
-                            const int slot = (MT == 1) ? acc : mt;
-                            if (MT == 2 && kb == wi.kb_begin && k == 0) {
-                                // First write into this slot for the tile: its previous contents must be drained.
-                                const long long te0 = clock64();
-                                if (!bounded_wait(tempty_bar(slot), slot_ph[slot] ^ 1u, ctl, DEV_TIMEOUT_TMEM_EMPTY)) { ok = false; break; }
-                                t_tempty += clock64() - te0;
-                                ptx::tc_fence_after();
+                            for (int nt = 0; nt < 2; ++nt) {
+                                if (kb == wi.kb_begin && k == 0) {
+                                    const long long te0 = clock64();
+                                    if (!bounded_wait(tempty_bar(nt), slot_ph[nt] ^ 1u, ctl, DEV_TIMEOUT_TMEM_EMPTY)) { ok = false; break; }
+                                    t_tempty += clock64() - te0;
+                                    ptx::tc_fence_after();
+                                }
+                                const uint64_t bdesc = make_smem_desc(b_addr + nt * T::kBSubTileBytes + k * b_kstep, b_lbo, b_sbo);
+                                if (p.diag != 1) {
+                                    if (nt == 0) ptx::mma_f16<CG, 1>(tmem_base + 0u, adesc, bdesc, idesc, acc_flag);
+                                    else ptx::mma_f16<CG, 2>(tmem_base + static_cast<uint32_t>(BN), adesc, bdesc, idesc, acc_flag);
+                                }
                             }
-                            const uint64_t adesc = make_smem_desc(a_addr + mt * kASubTileBytes + k * a_kstep, a_lbo, a_sbo);
-                            if (p.diag != 1)
-                                ptx::mma_f16<CG>(tmem_base + static_cast<uint32_t>(slot * BN), adesc, bdesc, idesc,
-                                                 (kb > wi.kb_begin || k > 0) ? 1u : 0u);
+                        } else {
+                            const uint64_t bdesc = make_smem_desc(b_addr + k * b_kstep, b_lbo, b_sbo);
+#pragma unroll
+                            for (int mt = 0; mt < MT; ++mt) {
+                                const int slot = (MT == 1) ? acc : mt;
+                                if (MT == 2 && kb == wi.kb_begin && k == 0) {
+                                    // First write into this slot for the tile: its previous contents must be drained.
+                                    const long long te0 = clock64();
+                                    if (!bounded_wait(tempty_bar(slot), slot_ph[slot] ^ 1u, ctl, DEV_TIMEOUT_TMEM_EMPTY)) { ok = false; break; }
+                                    t_tempty += clock64() - te0;
+                                    ptx::tc_fence_after();
+                                }
+                                const uint64_t adesc = make_smem_desc(a_addr + mt * kASubTileBytes + k * a_kstep, a_lbo, a_sbo);
+                                if (p.diag != 1)
+                                    ptx::mma_f16<CG>(tmem_base + static_cast<uint32_t>(slot * BN), adesc, bdesc, idesc, acc_flag);
+                            }
                         }
                         if (!ok) break;
                     }
@@ -517,11 +550,12 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
         const uint32_t stage = ctrl + T::kCtrlBytes + static_cast<uint32_t>(warp - 2) * 4096u;
         long long t_drain = 0, t_store = 0;
         for (int w = cluster_id; w < num_work; w += num_clusters) {
-            const WorkItem wi = decode_work(p, w, BM, BN);
+            const WorkItem wi = decode_work(p, w, BM, BNT);
             if (!bounded_wait(tfull_bar(slot), slot_phase, ctl, DEV_TIMEOUT_TMEM_FULL)) break;
             const long long td0 = clock64();
             ptx::tc_fence_after();
-            const int row0 = wi.m0 + (MT == 2 ? group * kMmaM : 0) + static_cast<int>(cta_rank) * kBmCta + q * 32;
+            const int row0 = wi.m0 + ((MT == 2 && ND == 0) ? group * kMmaM : 0) + static_cast<int>(cta_rank) * kBmCta + q * 32;
+            const int n_base = wi.n0 + (ND == 1 ? group * BN : 0);
             const int row = row0 + lane;
             const uint32_t t_row = tmem_base + static_cast<uint32_t>(slot * BN) + (static_cast<uint32_t>(q * 32) << 16);
             // The TMEM read of chunk c+1 is in flight while chunk c is transposed and stored.
@@ -544,7 +578,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                     }
                     t_drain += clock64() - td0;
                 }
-                const int col0 = wi.n0 + c * 32;
+                const int col0 = n_base + c * 32;
                 const int ncols = p.N - col0;
                 if (p.diag == 7) {
                 } else if (staged && out16) {

@@ -147,26 +147,30 @@ __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence:
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
 // D[tmem] (+)= A[smem desc] * B[smem desc], bf16/f16 inputs (kind::f16), issued by ONE thread.
-template <int CG>
+// COLL selects the A-operand collector usage: 0 = default (discard), 1 = fill (keep A in the tensor core's
+// collector after this MMA), 2 = lastuse (take A from the collector filled by the previous MMA, then free it).
+#define T0B_MMA_ASM(GROUP, COLLQ)                                                                                  \
+    asm volatile(                                                                                                  \
+        "{\n\t"                                                                                                    \
+        ".reg .pred p;\n\t"                                                                                        \
+        "setp.ne.b32 p, %4, 0;\n\t"                                                                                \
+        "tcgen05.mma.cta_group::" GROUP ".kind::f16" COLLQ " [%0], %1, %2, %3, p;\n\t"                             \
+        "}" ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)                                  \
+        : "memory")
+template <int CG, int COLL = 0>
 __device__ __forceinline__ void mma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
                                         uint32_t accumulate) {
-    if constexpr (CG == 1)
-        asm volatile(
-            "{\n\t"
-            ".reg .pred p;\n\t"
-            "setp.ne.b32 p, %4, 0;\n\t"
-            "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t"
-            "}" ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-            : "memory");
-    else
-        asm volatile(
-            "{\n\t"
-            ".reg .pred p;\n\t"
-            "setp.ne.b32 p, %4, 0;\n\t"
-            "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t"
-            "}" ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-            : "memory");
+    if constexpr (CG == 1) {
+        if constexpr (COLL == 1) T0B_MMA_ASM("1", ".collector::a::fill");
+        else if constexpr (COLL == 2) T0B_MMA_ASM("1", ".collector::a::lastuse");
+        else T0B_MMA_ASM("1", "");
+    } else {
+        if constexpr (COLL == 1) T0B_MMA_ASM("2", ".collector::a::fill");
+        else if constexpr (COLL == 2) T0B_MMA_ASM("2", ".collector::a::lastuse");
+        else T0B_MMA_ASM("2", "");
+    }
 }
+#undef T0B_MMA_ASM
 
 // Make `bar` (this CTA) receive one arrival when all MMAs issued so far by this thread have completed.
 __device__ __forceinline__ void mma_commit(uint32_t bar) {

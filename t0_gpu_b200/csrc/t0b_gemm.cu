@@ -61,11 +61,11 @@ int32_t get_tmap(t0b_ctx* ctx, uint64_t ptr, uint64_t d0, uint64_t d1, uint64_t 
     return T0B_OK;
 }
 
-template <int BN, int CG, int MT>
+template <int BN, int CG, int MT, int ND = 0>
 int32_t launch_variant(t0b_ctx* ctx, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc,
                        const GemmParams& p, int num_work) {
-    using T = GemmTraits<BN, CG, MT>;
-    auto kfn = gemm_bf16_tcgen05_kernel<BN, CG, MT>;
+    using T = GemmTraits<BN, CG, MT, ND>;
+    auto kfn = gemm_bf16_tcgen05_kernel<BN, CG, MT, ND>;
     static bool configured[64] = {};
     static int max_clusters[64] = {};
     const int dev = ctx->device & 63;
@@ -100,7 +100,8 @@ int32_t launch_variant(t0b_ctx* ctx, const CUtensorMap& ta, const CUtensorMap& t
         }
         configured[dev] = true;
     }
-    const int clusters = std::max(1, std::min(num_work, max_clusters[dev]));
+    static const int cap = [] { const char* e = getenv("T0B_GEMM_MAXCLUSTERS"); return e ? atoi(e) : 0; }();
+    const int clusters = std::max(1, std::min(num_work, cap > 0 ? std::min(cap, max_clusters[dev]) : max_clusters[dev]));
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(clusters * CG, 1, 1);
     cfg.blockDim = dim3(T::kThreads, 1, 1);
@@ -258,7 +259,7 @@ int32_t run_gemm(t0b_ctx* ctx, const GemmCall& g) {
         if (!g.trans_a) rc = get_tmap(ctx, g.a, g.k, g.m, g.lda, 64, 128, &ta);
         else rc = get_tmap(ctx, g.a, g.m, g.k, g.lda, 64, 64, &ta);
         if (rc != T0B_OK) return rc;
-        const uint32_t bn_cta = plan.bn / plan.cta_group;
+        const uint32_t bn_cta = (plan.n_tiles == 2 ? 256u : plan.bn) / plan.cta_group;
         if (g.trans_b) rc = get_tmap(ctx, g.b, g.k, g.n, g.ldb, 64, bn_cta, &tb);
         else rc = get_tmap(ctx, g.b, g.n, g.k, g.ldb, 64, 64, &tb);
         if (rc != T0B_OK) return rc;
@@ -326,7 +327,8 @@ int32_t run_gemm(t0b_ctx* ctx, const GemmCall& g) {
         }
         const int num_work = p.tiles_m * p.tiles_n * p.split_k;
         if (plan.cta_group == 2) {
-            if (plan.m_tiles == 2) rc = launch_variant<256, 2, 2>(ctx, ta, tb, tc, p, num_work);
+            if (plan.n_tiles == 2) rc = launch_variant<256, 2, 2, 1>(ctx, ta, tb, tc, p, num_work);
+            else if (plan.m_tiles == 2) rc = launch_variant<256, 2, 2>(ctx, ta, tb, tc, p, num_work);
             else if (plan.bn == 256) rc = launch_variant<256, 2, 1>(ctx, ta, tb, tc, p, num_work);
             else rc = launch_variant<128, 2, 1>(ctx, ta, tb, tc, p, num_work);
         } else {
@@ -547,7 +549,7 @@ int32_t t0b_tune(t0b_ctx* ctx, uint32_t m, uint32_t n, uint32_t k, int32_t trans
     if (rc == T0B_OK) rc = t0b_alloc(ctx, static_cast<size_t>(m) * n * elem, &c);
     if (rc != T0B_OK) return rc;
     const uint64_t lda = trans_a ? m : k, ldb = trans_b ? k : n;
-    static const char* tiles[] = {"b200_512x256", "b200_256x256", "b200_256x128", "b200_128x256", "b200_128x128", "b200_128x64"};
+    static const char* tiles[] = {"b200_256x512", "b200_512x256", "b200_256x256", "b200_256x128", "b200_128x256", "b200_128x128", "b200_128x64"};
     const uint32_t kb_total = (k + 63) / 64;
     float best_ms = 1e30f;
     for (const char* t : tiles) {

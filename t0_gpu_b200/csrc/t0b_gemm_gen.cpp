@@ -62,6 +62,7 @@ const Preset* presets(int* count) {
         {"b200_256x128", make_cfg(256, 128, 64, 192, true, true)},
         {"b200_256x256", make_cfg(256, 256, 64, 192, true, true)},
         {"b200_512x256", make_cfg(512, 256, 64, 320, true, true)},
+        {"b200_256x512", make_cfg(256, 512, 64, 320, true, true)},
     };
     *count = static_cast<int>(sizeof(table) / sizeof(table[0]));
     return table;
@@ -105,11 +106,11 @@ void default_b200_config(uint32_t m, uint32_t k, uint32_t n, int num_sms, t0b_ge
         uint32_t bm, cg, bn;
         double factor;   // measured relative throughput of the tile at large sizes (MMAs narrower than 256 run at reduced rate)
     };
-    static const Cand cands[] = {{512, 2, 256, 1.10}, {256, 2, 256, 1.00}, {128, 1, 256, 0.90},
+    static const Cand cands[] = {{256, 2, 512, 1.12}, {512, 2, 256, 1.10}, {256, 2, 256, 1.00}, {128, 1, 256, 0.90},
                                  {256, 2, 128, 0.50}, {128, 1, 128, 0.50}, {128, 1, 64, 0.30}};
     if (num_sms <= 0) num_sms = 148;
     double best = -1.0;
-    Cand pick = cands[4];
+    Cand pick = cands[5];
     uint64_t pick_tiles = 1;
     for (const Cand& c : cands) {
         const uint64_t bm = c.bm;
@@ -125,7 +126,7 @@ void default_b200_config(uint32_t m, uint32_t k, uint32_t n, int num_sms, t0b_ge
             pick_tiles = tiles;
         }
     }
-    t0b_gemm_config cfg = make_cfg(pick.bm, pick.bn, 64, pick.bm >= 512 ? 320 : 192, true, true);
+    t0b_gemm_config cfg = make_cfg(pick.bm, pick.bn, 64, (pick.bm >= 512 || pick.bn >= 512) ? 320 : 192, true, true);
     cfg.wgp_mode = pick.cg == 2;
     cfg.swap_grid = (m >= n) ? 1 : 0;
     const uint64_t clusters = static_cast<uint64_t>(num_sms) / pick.cg;
@@ -148,10 +149,14 @@ void resolve_plan(const t0b_gemm_config* cfg_in, const PlanInput& in, t0b_gemm_p
     const uint32_t want_n = cfg.tile_n * std::max(1u, cfg.n_col_passes);
     p.bn = want_n <= 64 ? 64 : (want_n <= 128 ? 128 : 256);
     if (p.cta_group == 2 && p.bn < 128) p.bn = 128;
-    p.m_tiles = (cfg.tile_m >= 512 && p.bn == 256) ? 2 : 1;
+    // Both TMEM accumulators in one tile: two N-adjacent 256-wide halves sharing A (tile_n >= 512, CTA pair), or two
+    // M-adjacent halves sharing B (tile_m >= 512).
+    p.n_tiles = (want_n >= 512 && p.cta_group == 2) ? 2 : 1;
+    p.m_tiles = (p.n_tiles == 1 && cfg.tile_m >= 512 && p.bn == 256) ? 2 : 1;
+    if (p.n_tiles == 2) p.bn = 512;
     p.bm = 128 * p.cta_group * p.m_tiles;
     p.bk = 64;
-    p.stages = static_cast<uint32_t>(stages_for(p.bn, p.cta_group, p.m_tiles));
+    p.stages = static_cast<uint32_t>(stages_for(p.n_tiles == 2 ? 256 : p.bn, p.cta_group, std::max(p.m_tiles, p.n_tiles)));
     const uint32_t kb_total = (in.k + 63) / 64;
     uint32_t sk = std::max(1u, sk_of(&cfg));
     sk = std::min(sk, std::max(1u, kb_total));
@@ -163,7 +168,8 @@ void resolve_plan(const t0b_gemm_config* cfg_in, const PlanInput& in, t0b_gemm_p
     const uint64_t tiles = static_cast<uint64_t>((in.m + p.bm - 1) / p.bm) * ((in.n + p.bn - 1) / p.bn) * p.split_k;
     const uint64_t clusters = static_cast<uint64_t>(num_sms) / p.cta_group;
     p.grid = static_cast<uint32_t>(std::min<uint64_t>(tiles, clusters) * p.cta_group);
-    p.smem_bytes = p.stages * stage_bytes(p.bn, p.cta_group, p.m_tiles) + 1024 + 1024 + p.m_tiles * 4 * 4096;
+    p.smem_bytes = p.stages * stage_bytes(p.n_tiles == 2 ? 256 : p.bn, p.cta_group, std::max(p.m_tiles, p.n_tiles)) + 1024 + 1024 +
+                   std::max(p.m_tiles, p.n_tiles) * 4 * 4096;
     *out = p;
 }
 

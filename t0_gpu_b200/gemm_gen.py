@@ -225,6 +225,7 @@ class GemmPlan:
     bk: int
     cta_group: int
     m_tiles: int
+    n_tiles: int
     stages: int
     split_k: int
     kb_per_split: int
@@ -243,5 +244,5 @@ def resolve_plan(cfg: Optional[GemmConfig], m: int, n: int, k: int, trans_a: boo
     p = GemmPlanC()
     cp = C.byref(cfg.to_c()) if cfg is not None else None
     lib().t0b_resolve_plan(cp, m, n, k, int(trans_a), int(trans_b), lda, ldb, num_sms, C.byref(p))
-    return GemmPlan(p.bm, p.bn, p.bk, p.cta_group, p.m_tiles, p.stages, p.split_k, p.kb_per_split, bool(p.use_tma), p.grid,
+    return GemmPlan(p.bm, p.bn, p.bk, p.cta_group, p.m_tiles, p.n_tiles, p.stages, p.split_k, p.kb_per_split, bool(p.use_tma), p.grid,
                     p.smem_bytes)

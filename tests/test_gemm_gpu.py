@@ -57,7 +57,8 @@ def test_256_cubed_all_layouts(rt, trans_a, trans_b):
     A = oracle.rand_bf16(m * k, m * 1000 + k).reshape(m, k)
     Bt = oracle.rand_bf16(n * k, n * 2000 + k).reshape(n, k)
     ref = oracle.gemm_bf16(A, Bt, m, n, k, threads=8)
-    for cfg in (None, GemmConfig.preset("b200_128x128"), GemmConfig.preset("b200_256x128"), GemmConfig.preset("b200_512x256")):
+    for cfg in (None, GemmConfig.preset("b200_128x128"), GemmConfig.preset("b200_256x128"), GemmConfig.preset("b200_512x256"),
+                GemmConfig.preset("b200_256x512")):
         got = gpu_gemm(rt, A, Bt, trans_a=trans_a, trans_b=trans_b, cfg=cfg)
         check(got, ref, k, A, Bt)
 
@@ -193,7 +194,7 @@ def test_tile_suite_shapes_with_padded_k(rt, m, k, n):
 @pytest.mark.parametrize("m,n,k", [(1, 1, 8), (1, 130, 64), (130, 1, 64), (127, 129, 72), (33, 50, 104), (65, 255, 200),
                                    (300, 200, 520), (257, 513, 1032)])
 @pytest.mark.parametrize("preset", ["b200_128x64", "b200_128x128", "b200_128x256", "b200_256x128", "b200_256x256",
-                                    "b200_512x256"])
+                                    "b200_512x256", "b200_256x512"])
 def test_ragged_edges_without_padding(rt, m, n, k, preset):
     """M, N not multiples of the tile and K not a multiple of 64: TMA zero-fill stands in for the caller's
     padding; nothing outside [M, N] is written (sentinels around the output survive)."""
@@ -298,7 +299,7 @@ def test_activation_epilogues(rt):
         assert np.abs(got - ref).max() <= 1e-3 * max(1.0, np.abs(ref).max()), epi
 
 
-@pytest.mark.parametrize("preset", ["b200_128x128", "b200_256x256", "b200_512x256"])
+@pytest.mark.parametrize("preset", ["b200_128x128", "b200_256x256", "b200_512x256", "b200_256x512"])
 def test_bf16_output_is_rne_of_f32_result(rt, preset):
     m, k, n = 256, 512, 384
     A = oracle.normal_bf16((m, k), 4321, 1 / np.sqrt(k))

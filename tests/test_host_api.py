@@ -146,7 +146,9 @@ def test_grids():
 
 def test_plan_resolution():
     p = t.resolve_plan(None, 8192, 8192, 8192)
-    assert (p.bm, p.bn, p.bk, p.cta_group, p.m_tiles) == (512, 256, 64, 2, 2) and p.use_tma and p.smem_bytes <= 227 * 1024
+    assert (p.bm, p.bn, p.bk, p.cta_group, p.m_tiles, p.n_tiles) == (256, 512, 64, 2, 1, 2) and p.use_tma and p.smem_bytes <= 227 * 1024
+    p = t.resolve_plan(GemmConfig.preset("b200_512x256"), 8192, 8192, 8192)
+    assert (p.bm, p.bn, p.cta_group, p.m_tiles, p.n_tiles, p.stages) == (512, 256, 2, 2, 1, 4)
     p = t.resolve_plan(GemmConfig.preset("b200_256x256"), 8192, 8192, 8192)
     assert (p.bm, p.bn, p.cta_group, p.m_tiles, p.stages) == (256, 256, 2, 1, 6)
     # reference presets run as single-CTA 128-row tiles
@@ -161,7 +163,7 @@ def test_plan_resolution():
     # B200-native presets
     p = t.resolve_plan(GemmConfig.preset("b200_128x256"), 4096, 4096, 4096)
     assert (p.bm, p.bn, p.cta_group, p.stages) == (128, 256, 1, 4)
-    for name in ("b200_128x64", "b200_128x128", "b200_128x256", "b200_256x128", "b200_256x256", "b200_512x256"):
+    for name in ("b200_128x64", "b200_128x128", "b200_128x256", "b200_256x128", "b200_256x256", "b200_512x256", "b200_256x512"):
         p = t.resolve_plan(GemmConfig.preset(name), 4096, 4096, 4096)
         assert p.smem_bytes <= 227 * 1024 and p.stages >= 4
 
