@@ -351,6 +351,18 @@ int32_t run_gemm(t0b_ctx* ctx, const GemmCall& g) {
     return T0B_OK;
 }
 
+// Pseudo-random bf16 fill for the tuner: operands of zeros would draw less power than real data and make the
+// measured clocks (and the ranking of configs) unrepresentative.
+__global__ void __launch_bounds__(256) fill_random_bf16_kernel(__nv_bfloat16* dst, size_t n, uint32_t seed, float scale) {
+    const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < n; i += stride) {
+        uint32_t x = static_cast<uint32_t>(i) * 2654435761u ^ seed;
+        x ^= x >> 16; x *= 0x7feb352du; x ^= x >> 15; x *= 0x846ca68bu; x ^= x >> 16;
+        const float u = static_cast<float>(x >> 8) * (1.0f / 8388608.0f) - 1.0f;   // [-1, 1)
+        dst[i] = __float2bfloat16_rn(u * scale);
+    }
+}
+
 uint32_t rd_u32(const uint8_t* p) { return p[0] | (p[1] << 8) | (p[2] << 16) | (static_cast<uint32_t>(p[3]) << 24); }
 uint64_t rd_u64(const uint8_t* p) { return rd_u32(p) | (static_cast<uint64_t>(rd_u32(p + 4)) << 32); }
 
@@ -544,10 +556,17 @@ int32_t t0b_tune(t0b_ctx* ctx, uint32_t m, uint32_t n, uint32_t k, int32_t trans
     }
     const size_t elem = out_dtype == T0B_OUT_BF16 ? 2 : 4;
     uint64_t a = 0, b = 0, c = 0;
-    rc = t0b_alloc_zero(ctx, static_cast<size_t>(m) * k * 2, &a);
-    if (rc == T0B_OK) rc = t0b_alloc_zero(ctx, static_cast<size_t>(n) * k * 2, &b);
+    rc = t0b_alloc(ctx, static_cast<size_t>(m) * k * 2, &a);
+    if (rc == T0B_OK) rc = t0b_alloc(ctx, static_cast<size_t>(n) * k * 2, &b);
     if (rc == T0B_OK) rc = t0b_alloc(ctx, static_cast<size_t>(m) * n * elem, &c);
     if (rc != T0B_OK) return rc;
+    {
+        const float scale = 1.7f / sqrtf(static_cast<float>(k));   // unit-variance-like products, as in the benchmark inputs
+        fill_random_bf16_kernel<<<ctx->num_sms * 8, 256, 0, ctx->stream>>>(reinterpret_cast<__nv_bfloat16*>(a), static_cast<size_t>(m) * k, 0x1234u, scale);
+        fill_random_bf16_kernel<<<ctx->num_sms * 8, 256, 0, ctx->stream>>>(reinterpret_cast<__nv_bfloat16*>(b), static_cast<size_t>(n) * k, 0x5678u, scale);
+        rc = check_cuda(ctx, cudaGetLastError(), "tuner fill");
+        if (rc != T0B_OK) return rc;
+    }
     const uint64_t lda = trans_a ? m : k, ldb = trans_b ? k : n;
     static const char* tiles[] = {"b200_256x512", "b200_512x256", "b200_256x256", "b200_256x128", "b200_128x256", "b200_128x128", "b200_128x64"};
     const uint32_t kb_total = (k + 63) / 64;

@@ -99,43 +99,51 @@ int stages_for(uint32_t bn, uint32_t cg, uint32_t mt) {
 
 namespace t0b {
 
-// Pick the B200 tile for a shape.  Score = wave efficiency x padding efficiency x a per-tile throughput
-// factor (larger tiles re-use more of each shared-memory byte); small grids get a power-of-two split-K.
+// Pick the B200 tile for a shape with a small cost model whose constants were measured on B200 (on-device tuner,
+// random operands, SM clock ~1.5 GHz under tensor load).  It stands where the reference has its RDNA3 cost model
+// (src/t0/cost_model.rs:168-471): estimate the time of every candidate, keep the cheapest.
+//   time = waves * (k_blocks * cycles_per_k_block + exposed_epilogue) + launch, plus the slab reduce for split-K.
+// cycles_per_k_block: a 256-wide MMA runs at full rate, narrower ones take the same time for fewer columns; the
+// two-accumulator tiles (256x512, 512x256) move a quarter less operand data per FLOP but cannot hide their epilogue.
 void default_b200_config(uint32_t m, uint32_t k, uint32_t n, int num_sms, t0b_gemm_config* out) {
     struct Cand {
-        uint32_t bm, cg, bn;
-        double factor;   // measured relative throughput of the tile at large sizes (MMAs narrower than 256 run at reduced rate)
+        uint32_t bm, bn, cg;
+        double kb_cycles;      // per 64-deep K block, per CTA
+        double epi_exposed;    // cycles per tile the MMA pipe idles for the epilogue
+        double epi_tail;       // cycles after the last tile
     };
-    static const Cand cands[] = {{256, 2, 512, 1.12}, {512, 2, 256, 1.10}, {256, 2, 256, 1.00}, {128, 1, 256, 0.90},
-                                 {256, 2, 128, 0.50}, {128, 1, 128, 0.50}, {128, 1, 64, 0.30}};
+    static const Cand cands[] = {
+        {256, 512, 2, 1165.0, 10000.0, 0.0}, {512, 256, 2, 1175.0, 10000.0, 0.0}, {256, 256, 2, 650.0, 0.0, 8000.0},
+        {128, 256, 1, 640.0, 0.0, 8000.0},   {128, 128, 1, 700.0, 0.0, 5000.0},   {128, 64, 1, 550.0, 0.0, 3500.0},
+    };
     if (num_sms <= 0) num_sms = 148;
-    double best = -1.0;
-    Cand pick = cands[5];
-    uint64_t pick_tiles = 1;
+    const uint32_t kb_total = std::max(1u, (k + 63) / 64);
+    double best = 1e300;
+    Cand pick = cands[4];
+    uint32_t pick_sk = 1;
     for (const Cand& c : cands) {
-        const uint64_t bm = c.bm;
-        const uint64_t tiles = ((m + bm - 1) / bm) * ((n + c.bn - 1) / c.bn);
+        const uint64_t tiles = static_cast<uint64_t>((m + c.bm - 1) / c.bm) * ((n + c.bn - 1) / c.bn);
         const uint64_t clusters = static_cast<uint64_t>(num_sms) / c.cg;
-        const uint64_t waves = (tiles + clusters - 1) / clusters;
-        const double eff_wave = static_cast<double>(tiles) / static_cast<double>(waves * clusters);
-        const double eff_tile = (static_cast<double>(m) * n) / (static_cast<double>(tiles) * bm * c.bn);
-        const double score = eff_wave * eff_tile * c.factor;
-        if (score > best) {
-            best = score;
-            pick = c;
-            pick_tiles = tiles;
+        for (uint32_t sk = 1; sk <= 16; sk *= 2) {
+            if (sk > 1 && (kb_total / sk < 4 || tiles * (sk / 2) >= clusters)) break;   // split only while the grid is not full
+            const uint32_t kbps = (kb_total + sk - 1) / sk;
+            const uint64_t work = tiles * sk;
+            const uint64_t waves = (work + clusters - 1) / clusters;
+            double cyc = static_cast<double>(waves) * (kbps * c.kb_cycles + c.epi_exposed) + c.epi_tail + 4500.0;
+            // The hidden epilogue of a double-buffered tile still bounds a tile whose main loop is shorter than it.
+            if (c.epi_exposed == 0.0 && kbps * c.kb_cycles < c.epi_tail) cyc += static_cast<double>(waves - 1) * (c.epi_tail - kbps * c.kb_cycles);
+            if (sk > 1) cyc += 3000.0 + static_cast<double>(m) * n * 4.0 * (sk + 1) / 3300.0;   // reduce kernel: launch + bytes at ~5 TB/s
+            if (cyc < best) {
+                best = cyc;
+                pick = c;
+                pick_sk = sk;
+            }
         }
     }
     t0b_gemm_config cfg = make_cfg(pick.bm, pick.bn, 64, (pick.bm >= 512 || pick.bn >= 512) ? 320 : 192, true, true);
     cfg.wgp_mode = pick.cg == 2;
     cfg.swap_grid = (m >= n) ? 1 : 0;
-    const uint64_t clusters = static_cast<uint64_t>(num_sms) / pick.cg;
-    const uint32_t kb_total = (k + 63) / 64;
-    if (pick_tiles * 2 <= clusters && kb_total >= 8) {
-        uint32_t sk = 1;
-        while (sk * 2 * pick_tiles <= clusters && kb_total / (sk * 2) >= 4 && sk < 16) sk *= 2;
-        if (sk > 1) cfg.split_k = sk;
-    }
+    cfg.split_k = pick_sk > 1 ? pick_sk : 0;
     *out = cfg;
 }
 
