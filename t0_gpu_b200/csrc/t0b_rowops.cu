@@ -150,6 +150,44 @@ __global__ void __launch_bounds__(kRowThreads) rmsnorm_fwd_kernel(const float* _
     }
 }
 
+// Register-resident forward for rows of up to 4 * VPT * blockDim.x columns: CTAs walk rows with a grid stride,
+// the weight stays in registers for all of them and each row's x is read exactly once.
+template <int VPT>
+__global__ void __launch_bounds__(kRowThreads) rmsnorm_fwd_reg_kernel(const float* __restrict__ x, const float* __restrict__ w,
+                                                                      float* __restrict__ y, float* __restrict__ inv_rms,
+                                                                      uint32_t rows, uint32_t cols, float eps) {
+    __shared__ float red[64];
+    const uint32_t n4 = cols / 4;
+    float4 wv[VPT];
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) {
+        const uint32_t i = threadIdx.x + j * blockDim.x;
+        wv[j] = i < n4 ? reinterpret_cast<const float4*>(w)[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    for (uint32_t row = blockIdx.x; row < rows; row += gridDim.x) {
+        const float4* xr = reinterpret_cast<const float4*>(x + static_cast<size_t>(row) * cols);
+        float4* yr = reinterpret_cast<float4*>(y + static_cast<size_t>(row) * cols);
+        float4 xv[VPT];
+        float ss = 0.0f, unused = 0.0f;
+#pragma unroll
+        for (int j = 0; j < VPT; ++j) {
+            const uint32_t i = threadIdx.x + j * blockDim.x;
+            xv[j] = i < n4 ? xr[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+            ss += xv[j].x * xv[j].x + xv[j].y * xv[j].y + xv[j].z * xv[j].z + xv[j].w * xv[j].w;
+        }
+        block_sum2(ss, unused, red);
+        const float rstd = 1.0f / sqrtf(ss / static_cast<float>(cols) + eps);
+        if (threadIdx.x == 0 && inv_rms) inv_rms[row] = rstd;
+#pragma unroll
+        for (int j = 0; j < VPT; ++j) {
+            const uint32_t i = threadIdx.x + j * blockDim.x;
+            if (i < n4)
+                yr[i] = make_float4(xv[j].x * rstd * wv[j].x, xv[j].y * rstd * wv[j].y, xv[j].z * rstd * wv[j].z,
+                                    xv[j].w * rstd * wv[j].w);
+        }
+    }
+}
+
 // dx = rstd * (dy*w - x * rstd^2 * mean(x * dy*w)); also stores rstd per row for the dgamma stage.
 __global__ void __launch_bounds__(kRowThreads) rmsnorm_bwd_dx_kernel(const float* __restrict__ dy, const float* __restrict__ x,
                                                                      const float* __restrict__ w, float* __restrict__ dx,
@@ -224,6 +262,75 @@ __global__ void __launch_bounds__(256) rmsnorm_dgamma_final_kernel(const float* 
 
 constexpr uint32_t kDgammaRowBlocks = 64;
 
+// Fused RMSNorm backward: each CTA walks rows r = blockIdx.x, blockIdx.x + gridDim.x, ... keeping the row's x and
+// dy in registers between the reduction sweep and the dx sweep (one HBM read of each), and accumulates its share of
+// dgamma[c] = sum_r dy*x*rstd in registers; per-CTA partials are then summed in CTA order by
+// rmsnorm_dgamma_final_kernel.  Every thread owns VPT float4 column groups: cols <= 4 * VPT * blockDim.x.
+template <int VPT>
+__global__ void __launch_bounds__(kRowThreads) rmsnorm_bwd_fused_kernel(const float* __restrict__ dy, const float* __restrict__ x,
+                                                                        const float* __restrict__ w, float* __restrict__ dx,
+                                                                        float* __restrict__ partial, uint32_t rows,
+                                                                        uint32_t cols, float eps) {
+    __shared__ float red[64];
+    const uint32_t n4 = cols / 4;
+    float4 wv[VPT], acc[VPT];
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) {
+        const uint32_t i = threadIdx.x + j * blockDim.x;
+        wv[j] = i < n4 ? reinterpret_cast<const float4*>(w)[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+        acc[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    for (uint32_t row = blockIdx.x; row < rows; row += gridDim.x) {
+        const float4* xr = reinterpret_cast<const float4*>(x + static_cast<size_t>(row) * cols);
+        const float4* dyr = reinterpret_cast<const float4*>(dy + static_cast<size_t>(row) * cols);
+        float4 xv[VPT], dv[VPT];
+        float ss = 0.0f, dot = 0.0f;
+#pragma unroll
+        for (int j = 0; j < VPT; ++j) {
+            const uint32_t i = threadIdx.x + j * blockDim.x;
+            if (i < n4) {
+                xv[j] = xr[i];
+                dv[j] = dyr[i];
+            } else {
+                xv[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+                dv[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+            ss += xv[j].x * xv[j].x + xv[j].y * xv[j].y + xv[j].z * xv[j].z + xv[j].w * xv[j].w;
+            dot += xv[j].x * dv[j].x * wv[j].x + xv[j].y * dv[j].y * wv[j].y + xv[j].z * dv[j].z * wv[j].z + xv[j].w * dv[j].w * wv[j].w;
+        }
+        block_sum2(ss, dot, red);
+        const float rstd = 1.0f / sqrtf(ss / static_cast<float>(cols) + eps);
+        const float coef = rstd * rstd * (dot / static_cast<float>(cols));
+        float4* dxr = dx ? reinterpret_cast<float4*>(dx + static_cast<size_t>(row) * cols) : nullptr;
+#pragma unroll
+        for (int j = 0; j < VPT; ++j) {
+            const uint32_t i = threadIdx.x + j * blockDim.x;
+            acc[j].x += dv[j].x * xv[j].x * rstd;
+            acc[j].y += dv[j].y * xv[j].y * rstd;
+            acc[j].z += dv[j].z * xv[j].z * rstd;
+            acc[j].w += dv[j].w * xv[j].w * rstd;
+            if (dxr && i < n4)
+                dxr[i] = make_float4(rstd * (dv[j].x * wv[j].x - xv[j].x * coef), rstd * (dv[j].y * wv[j].y - xv[j].y * coef),
+                                     rstd * (dv[j].z * wv[j].z - xv[j].z * coef), rstd * (dv[j].w * wv[j].w - xv[j].w * coef));
+        }
+    }
+    if (partial == nullptr) return;   // dx only
+    float4* pr = reinterpret_cast<float4*>(partial + static_cast<size_t>(blockIdx.x) * cols);
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) {
+        const uint32_t i = threadIdx.x + j * blockDim.x;
+        if (i < n4) pr[i] = acc[j];
+    }
+}
+
+__host__ __device__ inline uint32_t rmsnorm_fused_ctas(uint32_t rows) {
+    uint32_t g = rows / 4;
+    if (g < 1) g = 1;
+    if (g > 512) g = 512;
+    return g;
+}
+
+
 // ------------------------------------------------------------------------------------------------ softmax / CE
 
 // Row statistics with the row cached in shared memory when it fits (one HBM read), else re-read.
@@ -234,12 +341,25 @@ __device__ __forceinline__ void row_stats(const float* __restrict__ xr, uint32_t
     s = 0.0f;
     const bool vec = (cols % 4 == 0) && ((reinterpret_cast<uintptr_t>(xr) & 15) == 0);
     if (vec) {
-        for (uint32_t i = threadIdx.x; i < cols / 4; i += blockDim.x) {
-            const float4 v = reinterpret_cast<const float4*>(xr)[i];
-            if (CACHE) reinterpret_cast<float4*>(cache)[i] = v;
-            const float lm = fmaxf(fmaxf(v.x, v.y), fmaxf(v.z, v.w));
-            if (lm > m) { s *= __expf(m - lm); m = lm; }
-            s += __expf(v.x - m) + __expf(v.y - m) + __expf(v.z - m) + __expf(v.w - m);
+        // Four independent 16-byte loads in flight per thread before the dependent max/sum update.
+        const uint32_t n4 = cols / 4;
+        for (uint32_t i0 = threadIdx.x; i0 < n4; i0 += 4 * blockDim.x) {
+            float4 v[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const uint32_t i = i0 + u * blockDim.x;
+                v[u] = i < n4 ? reinterpret_cast<const float4*>(xr)[i] : make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const uint32_t i = i0 + u * blockDim.x;
+                if (i < n4) {
+                    if (CACHE) reinterpret_cast<float4*>(cache)[i] = v[u];
+                    const float lm = fmaxf(fmaxf(v[u].x, v[u].y), fmaxf(v[u].z, v[u].w));
+                    if (lm > m) { s *= __expf(m - lm); m = lm; }
+                    s += __expf(v[u].x - m) + __expf(v[u].y - m) + __expf(v[u].z - m) + __expf(v[u].w - m);
+                }
+            }
         }
     } else {
         for (uint32_t i = threadIdx.x; i < cols; i += blockDim.x) {
@@ -265,9 +385,21 @@ __global__ void __launch_bounds__(kRowThreads) softmax_fwd_kernel(const float* _
     const float* src = CACHE ? cache : xr;
     const bool vec = (cols % 4 == 0) && ((reinterpret_cast<uintptr_t>(xr) & 15) == 0) && ((reinterpret_cast<uintptr_t>(yr) & 15) == 0);
     if (vec) {
-        for (uint32_t i = threadIdx.x; i < cols / 4; i += blockDim.x) {
-            const float4 v = reinterpret_cast<const float4*>(src)[i];
-            reinterpret_cast<float4*>(yr)[i] = make_float4(__expf(v.x - m) * inv, __expf(v.y - m) * inv, __expf(v.z - m) * inv, __expf(v.w - m) * inv);
+        const uint32_t n4 = cols / 4;
+        for (uint32_t i0 = threadIdx.x; i0 < n4; i0 += 4 * blockDim.x) {
+            float4 v[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const uint32_t i = i0 + u * blockDim.x;
+                if (i < n4) v[u] = reinterpret_cast<const float4*>(src)[i];
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const uint32_t i = i0 + u * blockDim.x;
+                if (i < n4)
+                    reinterpret_cast<float4*>(yr)[i] = make_float4(__expf(v[u].x - m) * inv, __expf(v[u].y - m) * inv,
+                                                                   __expf(v[u].z - m) * inv, __expf(v[u].w - m) * inv);
+            }
         }
     } else {
         for (uint32_t i = threadIdx.x; i < cols; i += blockDim.x) yr[i] = __expf(src[i] - m) * inv;
@@ -308,17 +440,29 @@ __global__ void __launch_bounds__(kRowThreads) softmax_ce_kernel(const float* __
     const float* src = CACHE ? cache : xr;
     const bool vec = (cols % 4 == 0) && ((reinterpret_cast<uintptr_t>(xr) & 15) == 0) && ((reinterpret_cast<uintptr_t>(dr) & 15) == 0);
     if (vec) {
-        for (uint32_t i = threadIdx.x; i < cols / 4; i += blockDim.x) {
-            const float4 v = reinterpret_cast<const float4*>(src)[i];
-            float4 o = make_float4(__expf(v.x - m) * inv, __expf(v.y - m) * inv, __expf(v.z - m) * inv, __expf(v.w - m) * inv);
-            const uint32_t c = i * 4;
-            if (t - c < 4u) {
-                if (t == c) o.x -= 1.0f;
-                else if (t == c + 1) o.y -= 1.0f;
-                else if (t == c + 2) o.z -= 1.0f;
-                else o.w -= 1.0f;
+        const uint32_t n4 = cols / 4;
+        for (uint32_t i0 = threadIdx.x; i0 < n4; i0 += 4 * blockDim.x) {
+            float4 v[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const uint32_t i = i0 + u * blockDim.x;
+                if (i < n4) v[u] = reinterpret_cast<const float4*>(src)[i];
             }
-            reinterpret_cast<float4*>(dr)[i] = make_float4(o.x * scale, o.y * scale, o.z * scale, o.w * scale);
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const uint32_t i = i0 + u * blockDim.x;
+                if (i >= n4) continue;
+                float4 o = make_float4(__expf(v[u].x - m) * inv, __expf(v[u].y - m) * inv, __expf(v[u].z - m) * inv,
+                                       __expf(v[u].w - m) * inv);
+                const uint32_t c = i * 4;
+                if (t - c < 4u) {
+                    if (t == c) o.x -= 1.0f;
+                    else if (t == c + 1) o.y -= 1.0f;
+                    else if (t == c + 2) o.z -= 1.0f;
+                    else o.w -= 1.0f;
+                }
+                reinterpret_cast<float4*>(dr)[i] = make_float4(o.x * scale, o.y * scale, o.z * scale, o.w * scale);
+            }
         }
     } else {
         for (uint32_t i = threadIdx.x; i < cols; i += blockDim.x)
@@ -506,13 +650,26 @@ int32_t t0b_rmsnorm_fwd(t0b_ctx* ctx, uint64_t x, uint64_t weight, uint64_t y, u
     if (rows == 0) return T0B_OK;
     if (cols == 0 || !x || !weight || !y) return set_error(ctx, T0B_ERR_INVALID, "rmsnorm_fwd: null pointer or zero cols");
     const int threads = cols >= 2048 ? kRowThreads : (cols >= 512 ? 128 : 32);
+    if (((x | weight | y) & 15) == 0 && cols % 4 == 0 && cols >= 1024 && cols <= 4u * 4u * kRowThreads) {
+        const uint32_t g = std::min<uint32_t>(rows, static_cast<uint32_t>(ctx->num_sms) * 4u);
+        const uint32_t n4 = cols / 4;
+        const float* xp = reinterpret_cast<const float*>(x);
+        const float* wp = reinterpret_cast<const float*>(weight);
+        float* yp = reinterpret_cast<float*>(y);
+        float* ip = reinterpret_cast<float*>(inv_rms);
+        if (n4 <= 1u * kRowThreads) rmsnorm_fwd_reg_kernel<1><<<g, kRowThreads, 0, ctx->stream>>>(xp, wp, yp, ip, rows, cols, eps);
+        else if (n4 <= 2u * kRowThreads) rmsnorm_fwd_reg_kernel<2><<<g, kRowThreads, 0, ctx->stream>>>(xp, wp, yp, ip, rows, cols, eps);
+        else rmsnorm_fwd_reg_kernel<4><<<g, kRowThreads, 0, ctx->stream>>>(xp, wp, yp, ip, rows, cols, eps);
+        return finish(ctx, async, "rmsnorm_fwd");
+    }
     rmsnorm_fwd_kernel<<<rows, threads, 0, ctx->stream>>>(reinterpret_cast<const float*>(x), reinterpret_cast<const float*>(weight),
                                                           reinterpret_cast<float*>(y), reinterpret_cast<float*>(inv_rms), cols, eps);
     return finish(ctx, async, "rmsnorm_fwd");
 }
 
 size_t t0b_rmsnorm_bwd_scratch_bytes(uint32_t rows, uint32_t cols) {
-    return (static_cast<size_t>(rows) + static_cast<size_t>(kDgammaRowBlocks) * cols) * sizeof(float);
+    const size_t blocks = std::max<size_t>(kDgammaRowBlocks, rmsnorm_fused_ctas(rows));
+    return (((static_cast<size_t>(rows) + 3) & ~static_cast<size_t>(3)) + blocks * cols) * sizeof(float);
 }
 
 int32_t t0b_rmsnorm_bwd(t0b_ctx* ctx, uint64_t dy, uint64_t x, uint64_t weight, uint64_t dx, uint64_t dgamma,
@@ -534,6 +691,29 @@ int32_t t0b_rmsnorm_bwd(t0b_ctx* ctx, uint64_t dy, uint64_t x, uint64_t weight, 
         partial = inv + rows;
     }
     const int threads = cols >= 2048 ? kRowThreads : (cols >= 512 ? 128 : 32);
+    const bool aligned = ((dy | x | weight | dx | scratch) & 15) == 0 && cols % 4 == 0;
+    if (aligned && cols >= 1024 && cols <= 4u * 4u * kRowThreads) {
+        // One pass over dy and x: dx and the per-CTA dgamma partials come out of the same kernel.
+        const uint32_t g = dgamma ? rmsnorm_fused_ctas(rows) : std::min<uint32_t>(rows, static_cast<uint32_t>(ctx->num_sms) * 4u);
+        const uint32_t n4 = cols / 4;
+        if (dgamma) partial = reinterpret_cast<float*>(scratch) + ((static_cast<size_t>(rows) + 3) & ~static_cast<size_t>(3));   // 16-byte aligned
+        if (n4 <= 1u * kRowThreads)
+            rmsnorm_bwd_fused_kernel<1><<<g, kRowThreads, 0, ctx->stream>>>(reinterpret_cast<const float*>(dy), reinterpret_cast<const float*>(x),
+                reinterpret_cast<const float*>(weight), reinterpret_cast<float*>(dx), partial, rows, cols, eps);
+        else if (n4 <= 2u * kRowThreads)
+            rmsnorm_bwd_fused_kernel<2><<<g, kRowThreads, 0, ctx->stream>>>(reinterpret_cast<const float*>(dy), reinterpret_cast<const float*>(x),
+                reinterpret_cast<const float*>(weight), reinterpret_cast<float*>(dx), partial, rows, cols, eps);
+        else
+            rmsnorm_bwd_fused_kernel<4><<<g, kRowThreads, 0, ctx->stream>>>(reinterpret_cast<const float*>(dy), reinterpret_cast<const float*>(x),
+                reinterpret_cast<const float*>(weight), reinterpret_cast<float*>(dx), partial, rows, cols, eps);
+        rc = check_cuda(ctx, cudaGetLastError(), "rmsnorm_bwd_fused launch");
+        if (rc != T0B_OK) return rc;
+        if (dgamma) {
+            ++ctx->launches;
+            rmsnorm_dgamma_final_kernel<<<(cols + 255) / 256, 256, 0, ctx->stream>>>(partial, reinterpret_cast<float*>(dgamma), cols, g);
+        }
+        return finish(ctx, async, "rmsnorm_bwd");
+    }
     rmsnorm_bwd_dx_kernel<<<rows, threads, 0, ctx->stream>>>(reinterpret_cast<const float*>(dy), reinterpret_cast<const float*>(x),
                                                              reinterpret_cast<const float*>(weight), reinterpret_cast<float*>(dx),
                                                              inv, cols, eps);

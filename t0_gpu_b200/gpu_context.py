@@ -222,6 +222,69 @@ class GpuRuntime:
             pass
 
 
+# ------------------------------------------------------------------ the low-level handshake the examples drive
+# generate(&cfg).compile(Target) -> blob; GpuKernel::load(&device, &blob, &KernelLoadConfig);
+# queue.submit(&kernel, [gx, gy, 1], kernargs); queue.wait_idle()   (examples/test_gemm_correctness.rs:93-188)
+
+class Target:
+    SM100A = "sm_100a"
+    GFX1100 = "sm_100a"      # accepted alias: code written against the reference keeps compiling
+
+
+class T0Kernel:
+    """What `gemm_gen::generate(&cfg)` returns here: a handle naming a precompiled sm_100a kernel variant."""
+
+    def __init__(self, cfg: GemmConfig):
+        self.cfg = cfg
+
+    def compile(self, target=Target.SM100A) -> bytes:
+        """Nothing is compiled at run time; the "ELF" is an opaque descriptor of the config."""
+        import json
+        from dataclasses import asdict
+        d = asdict(self.cfg)
+        d["transpose"], d["epilogue"] = int(self.cfg.transpose), int(self.cfg.epilogue)
+        return b"T0B200\0" + json.dumps(d, sort_keys=True).encode()
+
+
+def generate(cfg: GemmConfig) -> T0Kernel:
+    if not cfg.is_feasible():
+        raise ValueError(f"[gemm_gen] config {cfg.name()} cannot be mapped onto the sm_100a kernel family")
+    return T0Kernel(cfg)
+
+
+class KernelLoadConfig:
+    def __init__(self, workgroup_size=(192, 1, 1), lds_size: int = 0):
+        self.workgroup_size, self.lds_size = workgroup_size, lds_size    # accepted, not needed on B200
+
+
+class GpuKernel:
+    def __init__(self, cfg: GemmConfig):
+        self.cfg = cfg
+
+    @staticmethod
+    def load(rt: "GpuRuntime", blob: bytes, load_cfg: Optional[KernelLoadConfig] = None) -> "GpuKernel":
+        import json
+        from .gemm_gen import EpilogueOp, GemmTranspose
+        if not blob.startswith(b"T0B200\0"):
+            raise T0Error(-1, "GpuKernel.load: not a t0b200 kernel descriptor")
+        d = json.loads(blob[7:].decode())
+        d["transpose"], d["epilogue"] = GemmTranspose(d["transpose"]), EpilogueOp(d["epilogue"])
+        return GpuKernel(GemmConfig(**d))
+
+
+class AqlQueue:
+    """`queue.submit` + `queue.wait_idle` over the runtime's stream."""
+
+    def __init__(self, rt: "GpuRuntime"):
+        self.rt = rt
+
+    def submit(self, kernel: GpuKernel, grid, kernargs: bytes) -> None:
+        self.rt.dispatch_async(kernel.cfg, (grid[0], grid[1]), kernargs)
+
+    def wait_idle(self) -> None:
+        self.rt.synchronize()
+
+
 def _addr(b) -> int:
     if b is None:
         return 0
