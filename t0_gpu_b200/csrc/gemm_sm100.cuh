@@ -67,8 +67,6 @@ struct GemmParams {
     int* status;
     unsigned long long wait_limit_ns;
     int tma_store;          // 1: the epilogue writes C with TMA stores through the third tensor map
-    int l2_prefetch;        // > 0: prefetch the K block this many blocks ahead into L2
-    int diag;               // 0 normal; diagnostics only (results are garbage): 1 = loads without MMA, 2 = MMA without loads
 };
 
 constexpr int kBmCta = 128;   // accumulator rows per MMA per CTA (TMEM lanes)
@@ -347,22 +345,17 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
 
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
-        if (lane == 0 && p.diag != 2) {
+        if (lane == 0) {
             int s = 0;
             uint32_t ph = 0;
             bool ok = true;
-            long long t_empty = 0;
-            const long long tp_begin = clock64();
             for (int w = cluster_id; w < num_work && ok; w += num_clusters) {
                 const WorkItem wi = decode_work(p, w, BM, BNT);
-                int m0_cta = wi.m0 + static_cast<int>(cta_rank) * kBmCta;
-                int n0_cta = wi.n0 + static_cast<int>(cta_rank) * T::kBnCta;
-                if (p.diag == 3) { m0_cta = static_cast<int>(cta_rank) * kBmCta; n0_cta = static_cast<int>(cta_rank) * T::kBnCta; }
+                const int m0_cta = wi.m0 + static_cast<int>(cta_rank) * kBmCta;
+                const int n0_cta = wi.n0 + static_cast<int>(cta_rank) * T::kBnCta;
                 for (int kb = wi.kb_begin; kb < wi.kb_end; ++kb) {
-                    const long long tq0 = clock64();
                     if (!bounded_wait(empty_bar(s), ph ^ 1u, ctl, DEV_TIMEOUT_EMPTY)) { ok = false; break; }
-                    t_empty += clock64() - tq0;
-                    if (is_leader) ptx::mbar_arrive_expect_tx(full_bar(s), p.diag == 4 ? CG * T::kATileBytes : CG * T::kStageBytes);
+                    if (is_leader) ptx::mbar_arrive_expect_tx(full_bar(s), CG * T::kStageBytes);
                     const uint32_t a_dst = smem_base + s * T::kStageBytes;
                     const uint32_t b_dst = a_dst + T::kATileBytes;
                     const int k0 = kb * kBk;
@@ -387,36 +380,15 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                     for (int nt = 0; nt < T::kBTiles; ++nt) {
                         const int n_sub = n0_cta + nt * BN;
                         const uint32_t dst = b_dst + nt * T::kBSubTileBytes;
-                        if (p.diag == 4) {
-                        } else if (!p.b_mn_major) {
+                        if (!p.b_mn_major) {
                             load(dst, &tmap_b, k0, n_sub);
                         } else {
 #pragma unroll
                             for (int j = 0; j < T::kBnCta / 64; ++j) load(dst + j * 8192, &tmap_b, n_sub + j * 64, k0);
                         }
                     }
-                    if (p.l2_prefetch > 0 && kb + p.l2_prefetch < wi.kb_end) {
-                        // Pull a K block further ahead into L2 so the later shared-memory fill finds it there.
-                        const int kp = (kb + p.l2_prefetch) * kBk;
-#pragma unroll
-                        for (int mt = 0; mt < T::kATiles; ++mt) {
-                            const int m_sub = m0_cta + mt * kMmaM;
-                            if (!p.a_mn_major) ptx::tma_prefetch_2d(&tmap_a, kp, m_sub);
-                            else { ptx::tma_prefetch_2d(&tmap_a, m_sub, kp); ptx::tma_prefetch_2d(&tmap_a, m_sub + 64, kp); }
-                        }
-                        if (!p.b_mn_major) ptx::tma_prefetch_2d(&tmap_b, kp, n0_cta);
-                        else {
-#pragma unroll
-                            for (int j = 0; j < T::kBnCta / 64; ++j) ptx::tma_prefetch_2d(&tmap_b, n0_cta + j * 64, kp);
-                        }
-                    }
                     if (++s == S) { s = 0; ph ^= 1u; }
                 }
-            }
-            if (p.diag >= 5 && blockIdx.x == 0) {
-                volatile int* dbg = reinterpret_cast<volatile int*>(p.status);
-                dbg[5] = static_cast<int>(t_empty >> 4);
-                dbg[6] = static_cast<int>((clock64() - tp_begin) >> 4);
             }
             // Tail: every slot must have been released, so no MMA-completion arrival can target this
             // CTA's shared memory after it exits.
@@ -441,8 +413,6 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
             int acc = 0;                       // MT == 1: the slot of this tile
             uint32_t slot_ph[2] = {0u, 0u};    // phase of each accumulator slot
             bool ok = true;
-            long long t_full = 0, t_tempty = 0;
-            const long long t_begin = clock64();
             for (int w = cluster_id; w < num_work && ok; w += num_clusters) {
                 const WorkItem wi = decode_work(p, w, BM, BNT);
                 if constexpr (MT == 1) {
@@ -450,9 +420,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                     ptx::tc_fence_after();
                 }
                 for (int kb = wi.kb_begin; kb < wi.kb_end; ++kb) {
-                    const long long tw0 = clock64();
-                    if (p.diag != 2 && !bounded_wait(full_bar(s), ph, ctl, DEV_TIMEOUT_FULL)) { ok = false; break; }
-                    t_full += clock64() - tw0;
+                    if (!bounded_wait(full_bar(s), ph, ctl, DEV_TIMEOUT_FULL)) { ok = false; break; }
                     ptx::tc_fence_after();
                     const uint32_t a_addr = smem_base + s * T::kStageBytes;
                     const uint32_t b_addr = a_addr + T::kATileBytes;
@@ -465,16 +433,12 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
 #pragma unroll
                             for (int nt = 0; nt < 2; ++nt) {
                                 if (kb == wi.kb_begin && k == 0) {
-                                    const long long te0 = clock64();
                                     if (!bounded_wait(tempty_bar(nt), slot_ph[nt] ^ 1u, ctl, DEV_TIMEOUT_TMEM_EMPTY)) { ok = false; break; }
-                                    t_tempty += clock64() - te0;
                                     ptx::tc_fence_after();
                                 }
                                 const uint64_t bdesc = make_smem_desc(b_addr + nt * T::kBSubTileBytes + k * b_kstep, b_lbo, b_sbo);
-                                if (p.diag != 1) {
-                                    if (nt == 0) ptx::mma_f16<CG, 1>(tmem_base + 0u, adesc, bdesc, idesc, acc_flag);
-                                    else ptx::mma_f16<CG, 2>(tmem_base + static_cast<uint32_t>(BN), adesc, bdesc, idesc, acc_flag);
-                                }
+                                if (nt == 0) ptx::mma_f16<CG, 1>(tmem_base + 0u, adesc, bdesc, idesc, acc_flag);
+                                else ptx::mma_f16<CG, 2>(tmem_base + static_cast<uint32_t>(BN), adesc, bdesc, idesc, acc_flag);
                             }
                         } else {
                             const uint64_t bdesc = make_smem_desc(b_addr + k * b_kstep, b_lbo, b_sbo);
@@ -483,14 +447,11 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                                 const int slot = (MT == 1) ? acc : mt;
                                 if (MT == 2 && kb == wi.kb_begin && k == 0) {
                                     // First write into this slot for the tile: its previous contents must be drained.
-                                    const long long te0 = clock64();
                                     if (!bounded_wait(tempty_bar(slot), slot_ph[slot] ^ 1u, ctl, DEV_TIMEOUT_TMEM_EMPTY)) { ok = false; break; }
-                                    t_tempty += clock64() - te0;
                                     ptx::tc_fence_after();
                                 }
                                 const uint64_t adesc = make_smem_desc(a_addr + mt * kASubTileBytes + k * a_kstep, a_lbo, a_sbo);
-                                if (p.diag != 1)
-                                    ptx::mma_f16<CG>(tmem_base + static_cast<uint32_t>(slot * BN), adesc, bdesc, idesc, acc_flag);
+                                ptx::mma_f16<CG>(tmem_base + static_cast<uint32_t>(slot * BN), adesc, bdesc, idesc, acc_flag);
                             }
                         }
                         if (!ok) break;
@@ -514,12 +475,6 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                         slot_ph[slot] ^= 1u;
                     }
                 }
-            }
-            if (p.diag >= 5 && blockIdx.x == 0) {
-                volatile int* dbg = reinterpret_cast<volatile int*>(p.status);
-                dbg[2] = static_cast<int>(t_full >> 4);
-                dbg[3] = static_cast<int>(t_tempty >> 4);
-                dbg[4] = static_cast<int>((clock64() - t_begin) >> 4);
             }
         }
         __syncwarp();
@@ -548,11 +503,9 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
         const bool staged = tma_out || (vec_ok && (p.N % (out16 ? 8 : 4) == 0));
         if (tma_out && lane == 0) ptx::prefetch_tmap(&tmap_c);
         const uint32_t stage = ctrl + T::kCtrlBytes + static_cast<uint32_t>(warp - 2) * 4096u;
-        long long t_drain = 0, t_store = 0;
         for (int w = cluster_id; w < num_work; w += num_clusters) {
             const WorkItem wi = decode_work(p, w, BM, BNT);
             if (!bounded_wait(tfull_bar(slot), slot_phase, ctl, DEV_TIMEOUT_TMEM_FULL)) break;
-            const long long td0 = clock64();
             ptx::tc_fence_after();
             const int row0 = wi.m0 + ((MT == 2 && ND == 0) ? group * kMmaM : 0) + static_cast<int>(cta_rank) * kBmCta + q * 32;
             const int n_base = wi.n0 + (ND == 1 ? group * BN : 0);
@@ -576,12 +529,10 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                         if constexpr (CG == 1) ptx::mbar_arrive(tempty_bar(slot));
                         else ptx::mbar_arrive_cluster(ptx::mapa(tempty_bar(slot), 0));
                     }
-                    t_drain += clock64() - td0;
                 }
                 const int col0 = n_base + c * 32;
                 const int ncols = p.N - col0;
-                if (p.diag == 7) {
-                } else if (staged && out16) {
+                if (staged && out16) {
                     const int half = c & 1;
                     if (half == 0) {
                         if (tma_out && lane == 0) ptx::bulk_wait_group_read<0>();   // the TMA store has read the tile
@@ -605,14 +556,14 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                         ptx::fence_proxy_async_smem();
                         __syncwarp();
                         const int cbase = col0 - 32;
-                        if (row0 < p.M && cbase < p.N && lane == 0 && p.diag != 6) {
+                        if (row0 < p.M && cbase < p.N && lane == 0) {
                             ptx::tma_store_2d(&tmap_c, stage, cbase, row0);
                             ptx::bulk_commit_group();
                         }
                     } else if (half == 1) {
                         __syncwarp();
                         const int cbase = col0 - 32;
-                        if (row0 < p.M && cbase < p.N && p.diag != 6) {
+                        if (row0 < p.M && cbase < p.N) {
                             for (int d = 0; d < p.n_dst; ++d)
                                 flush_pair_bf16(stage, lane, static_cast<__nv_bfloat16*>(p.c_dst[d]), ld_out, row0, cbase, p.M, p.N);
                         }
@@ -635,8 +586,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                         stage_chunk_f32(stage, lane, v);
                         if (tma_out) ptx::fence_proxy_async_smem();
                         __syncwarp();
-                        if (p.diag == 6) {
-                        } else if (tma_out) {
+                        if (tma_out) {
                             if (lane == 0) {
                                 ptx::tma_store_2d(&tmap_c, stage, col0, row0);
                                 ptx::bulk_commit_group();
@@ -673,7 +623,6 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                     }
                 }
             }
-            t_store += clock64() - td0;
             if constexpr (MT == 1) {
                 slot ^= 1;
                 if (slot == 0) slot_phase ^= 1u;
@@ -682,11 +631,6 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
             }
         }
         if (tma_out && lane == 0) ptx::bulk_wait_group<0>();   // every TMA store of this warp has completed
-        if (p.diag >= 5 && blockIdx.x == 0 && threadIdx.x == 64) {
-            volatile int* dbg = reinterpret_cast<volatile int*>(p.status);
-            dbg[7] = static_cast<int>(t_drain >> 4);
-            dbg[8] = static_cast<int>(t_store >> 4);
-        }
     }
 
     // ---------------------------------------------------------------------- teardown (normal and abort paths)

@@ -100,8 +100,7 @@ int32_t launch_variant(t0b_ctx* ctx, const CUtensorMap& ta, const CUtensorMap& t
         }
         configured[dev] = true;
     }
-    static const int cap = [] { const char* e = getenv("T0B_GEMM_MAXCLUSTERS"); return e ? atoi(e) : 0; }();
-    const int clusters = std::max(1, std::min(num_work, cap > 0 ? std::min(cap, max_clusters[dev]) : max_clusters[dev]));
+    const int clusters = std::max(1, std::min(num_work, max_clusters[dev]));
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(clusters * CG, 1, 1);
     cfg.blockDim = dim3(T::kThreads, 1, 1);
@@ -296,14 +295,6 @@ int32_t run_gemm(t0b_ctx* ctx, const GemmCall& g) {
         p.mn_lbo = 8192; p.mn_sbo = 1024; p.mn_kstep = 2048;
         p.status = ctx->status_dev;
         p.wait_limit_ns = ctx->wait_limit_ns;
-        {
-            static const int diag = [] { const char* e = getenv("T0B_GEMM_DIAG"); return e ? atoi(e) : 0; }();
-            p.diag = diag;
-            static const int pf = [] { const char* e = getenv("T0B_GEMM_L2PF"); return e ? atoi(e) : 0; }();
-            p.l2_prefetch = pf;
-            static const int grp = [] { const char* e = getenv("T0B_GEMM_GROUP"); return e ? atoi(e) : 0; }();
-            if (grp > 0) p.group = grp;
-        }
         if (g.slabs_only && sk == 1) {
             // One slab: store straight into it as f32.
             p.out_bf16 = 0; p.epilogue = EPI_STORE; p.n_dst = 1; p.ldc = static_cast<long long>(ld_partial);
@@ -313,11 +304,10 @@ int32_t run_gemm(t0b_ctx* ctx, const GemmCall& g) {
         CUtensorMap tc = ta;
         {
             const uint32_t oelem = p.out_bf16 ? 2u : 4u;
-            static const int no_tma_store = [] { const char* e = getenv("T0B_GEMM_NO_TMA_STORE"); return e ? atoi(e) : 0; }();
             // TMA clips a store at the tensor edge in 16-byte units, so N must be a whole number of them for
             // nothing beyond column N to be touched.
             const bool ok = !to_slabs && p.n_dst == 1 && (g.c_dst[0] % 16 == 0) && ((static_cast<uint64_t>(p.ldc) * oelem) % 16 == 0) &&
-                            ((static_cast<uint64_t>(g.n) * oelem) % 16 == 0) && !no_tma_store;
+                            ((static_cast<uint64_t>(g.n) * oelem) % 16 == 0);
             p.tma_store = 0;
             if (ok) {
                 rc = get_tmap(ctx, g.c_dst[0], g.n, g.m, static_cast<uint64_t>(p.ldc), p.out_bf16 ? 64 : 32, 32, &tc, oelem);

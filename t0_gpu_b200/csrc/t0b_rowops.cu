@@ -614,7 +614,7 @@ int grid_for(t0b_ctx* ctx, size_t n, int per_block) {
 // Rows up to 64 KiB are cached in shared memory (several CTAs still fit per SM, one HBM read); wider rows are
 // re-read through L2 instead, which measured faster than one 128 KiB-row CTA per SM.
 constexpr size_t kRowCacheLimit = 200 * 1024;
-static const size_t kRowCacheMax = [] { const char* e = getenv("T0B_ROW_CACHE_MAX"); return e ? static_cast<size_t>(atol(e)) : static_cast<size_t>(64 * 1024); }();
+constexpr size_t kRowCacheMax = 64 * 1024;
 
 }  // namespace
 

@@ -272,8 +272,6 @@ int32_t t0b_sync(t0b_ctx* ctx) {
 
 uint64_t t0b_launch_count(t0b_ctx* ctx) { return ctx ? ctx->launches : 0; }
 
-// Diagnostics: the host view of the status block (word 0 = status code, words 2.. = kernel counters in diag mode).
-__attribute__((visibility("default"))) int* t0b_debug_counters(t0b_ctx* ctx) { return ctx ? ctx->status_host : nullptr; }
 
 // ------------------------------------------------------------------------------------------------ IPC
 
