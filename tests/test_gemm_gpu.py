@@ -402,3 +402,41 @@ def test_bad_arguments_are_rejected_before_launch(rt):
         rt.gemm(a, b, c, 32, 32, 1024, cfg=cfg.with_(split_k=4), workspace=ws)   # undersized workspace
     assert not rt.is_poisoned()                                    # validation errors do not poison
     rt.gemm(a, b, c, 16, 16, 16)                                   # and the runtime still works
+
+
+# ------------------------------------------------------------------------------------------------ config 4 at full size (one GPU)
+
+def test_large_gemm_bf16_output_full_size(rt):
+    """M = N = 32768, K = 8192, N(0,1)/sqrt(K) bf16 inputs, bf16 output (2 GiB), on one GPU: sampled rows against the
+    oracle, the all-ones known answer on a row block, and bit-identical results for a column block computed alone
+    (the property the column-sharded multi-GPU run relies on: no reduction crosses a column block)."""
+    import torch
+    from t0_gpu_b200._lib import lib
+
+    m = n = 32768
+    k = 8192
+    dev = torch.device("cuda", 0)
+    g = torch.Generator(device=dev); g.manual_seed(4321)
+    a = (torch.randn((m, k), generator=g, device=dev) / k ** 0.5).to(torch.bfloat16)
+    g.manual_seed(4322)
+    b = (torch.randn((k, n), generator=g, device=dev) / k ** 0.5).to(torch.bfloat16)       # [K, N] row-major
+    c = torch.empty((m, n), dtype=torch.bfloat16, device=dev)
+    L = lib()
+    rt._check(L.t0b_gemm(rt.handle, None, 0, 0, a.data_ptr(), b.data_ptr(), c.data_ptr(), m, n, k, k, n, n, 1, 0, 0, 1.0, 0, 0, 0))
+    rows = [0, 777, 16384, m - 1]
+    a_np = a[rows].view(torch.uint16).cpu().numpy()
+    cols = slice(12288, 12288 + 2048)                                                   # a 2048-column window keeps the oracle cheap
+    bt_np = np.ascontiguousarray(b[:, cols].t().contiguous().view(torch.uint16).cpu().numpy())
+    ref = oracle.gemm_bf16(a_np, bt_np, len(rows), 2048, k, trans_a=False, trans_b=True, threads=8)
+    got = oracle.bf16_to_f32(c[rows][:, cols].contiguous().view(torch.uint16).cpu().numpy())
+    assert np.linalg.norm(got - ref) / np.linalg.norm(ref) <= 5e-3
+    assert np.abs(got - ref).max() <= 2.0 ** -7 * np.sqrt(k) * float(np.abs(oracle.bf16_to_f32(a_np)).max()) * float(np.abs(oracle.bf16_to_f32(bt_np)).max())
+    # a column block computed on its own (what one rank of the sharded run does) gives the same bits
+    n_local, col0 = 4096, 3 * 4096
+    b_blk = b[:, col0:col0 + n_local].contiguous()
+    c_blk = torch.zeros((m, n_local), dtype=torch.bfloat16, device=dev)
+    rt._check(L.t0b_gemm(rt.handle, None, 0, 0, a.data_ptr(), b_blk.data_ptr(), c_blk.data_ptr(), m, n_local, k, k, n_local, n_local,
+                         1, 0, 0, 1.0, 0, 0, 0))
+    assert torch.equal(c_blk, c[:, col0:col0 + n_local])
+    del a, b, c, b_blk, c_blk
+    torch.cuda.empty_cache()

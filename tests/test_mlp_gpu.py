@@ -14,20 +14,24 @@ pytestmark = pytest.mark.gpu
 
 
 def oracle_step(x, targets, w16, gammas, eps, scale):
-    """w16: list of bf16-bit arrays [k, n]; returns loss rows, dW list, dgamma list."""
+    """w16: list of bf16-bit arrays [k, n]; returns loss rows, dW list, dgamma list.
+
+    The oracle reads B either as [K, N] or as [N, K]; the element order of every sum is the same (k ascending), so the
+    forward products use a transposed copy of W, whose rows are contiguous for the oracle's inner loop."""
     B = x.shape[0]
     nh = len(gammas)
+    wt16 = [np.ascontiguousarray(w.T) for w in w16]
     inp = oracle.f32_to_bf16_rne(x)
     zs, rs, hs = [], [], [inp]
     for l in range(nh):
         k, n = w16[l].shape
-        z = oracle.gemm_bf16(inp, w16[l], B, n, k, trans_a=False, trans_b=False, threads=8)
+        z = oracle.gemm_bf16(inp, wt16[l], B, n, k, trans_a=False, trans_b=True, threads=8)
         r, _ = oracle.rmsnorm_forward(z, gammas[l], eps)
         a = oracle.silu_gate_forward(r, np.ones_like(r))
         inp = oracle.f32_to_bf16_rne(a)
         zs.append(z); rs.append(r); hs.append(inp)
     k, V = w16[nh].shape
-    logits = oracle.gemm_bf16(inp, w16[nh], B, V, k, trans_a=False, trans_b=False, threads=8)
+    logits = oracle.gemm_bf16(inp, wt16[nh], B, V, k, trans_a=False, trans_b=True, threads=8)
     loss = oracle.ce_loss_forward(logits, targets)
     dl16 = oracle.f32_to_bf16_rne(oracle.ce_loss_backward(logits, targets, scale))
     dws = [None] * (nh + 1)
@@ -50,8 +54,9 @@ def rel_fro(a, b):
     return float(np.linalg.norm(a - b) / max(np.linalg.norm(b), 1e-30))
 
 
-@pytest.mark.parametrize("rows,d,V", [(64, 256, 1000), (48, 512, 2048)])
+@pytest.mark.parametrize("rows,d,V", [(64, 256, 1000), (48, 512, 2048), (16, 4096, 32000)])
 def test_mlp_step_matches_oracle(rt, rows, d, V):
+    """The last case has the layer widths and class count of the benchmark's MLP config on a reduced-row replica."""
     import torch
     from t0_gpu_b200.mlp import MlpConfig, MlpTrainer
 
