@@ -49,7 +49,7 @@ enum {
 enum { T0B_TRANSPOSE_NT = 0, T0B_TRANSPOSE_NN = 1 };                       /* GemmTranspose, gemm_gen.rs:23-33 */
 enum { T0B_EPI_STORE_F32 = 0, T0B_EPI_BIAS_ADD = 1, T0B_EPI_BIAS_ADD_RELU = 2, /* EpilogueOp, gemm_gen.rs:40-49 */
        T0B_EPI_RELU = 3, T0B_EPI_SILU = 4, T0B_EPI_GELU_SIGMOID = 5,           /* tile_ir EpilogueOp members,   */
-       T0B_EPI_SCALE = 6, T0B_EPI_ABS = 7, T0B_EPI_NEG = 8 };                  /* src/t0/tile_ir.rs:41-62       */
+       T0B_EPI_SCALE = 6, T0B_EPI_ABS = 7, T0B_EPI_NEG = 8, T0B_EPI_CLAMP = 9 }; /* src/t0/tile_ir.rs:41-62     */
 enum { T0B_OUT_F32 = 0, T0B_OUT_BF16 = 1 };
 
 typedef struct t0b_gemm_config {
@@ -201,6 +201,14 @@ T0B_API int32_t t0b_gemm(t0b_ctx* ctx, const t0b_gemm_config* cfg, int32_t trans
                          uint64_t b, uint64_t c, uint32_t m, uint32_t n, uint32_t k, uint64_t lda, uint64_t ldb,
                          uint64_t ldc, int32_t out_dtype, int32_t epilogue, uint64_t bias, float alpha,
                          uint64_t workspace, size_t workspace_bytes, int32_t async);
+/* The same GEMM with a chain of up to four store-phase operations applied in order, the tile_ir epilogue chain
+ * (`TileGemm::add_epilogue`, src/t0/tile_ir.rs:41-62, lowered at :2213-2339): BiasAdd (bias f32[N]), Scale (scale),
+ * ReLU, SiLU, GELU (the reference's x*sigmoid(1.702x) form), Abs, Neg, Clamp (clamp_min, clamp_max). */
+T0B_API int32_t t0b_gemm_chain(t0b_ctx* ctx, const t0b_gemm_config* cfg, int32_t trans_a, int32_t trans_b, uint64_t a,
+                               uint64_t b, uint64_t c, uint32_t m, uint32_t n, uint32_t k, uint64_t lda, uint64_t ldb,
+                               uint64_t ldc, int32_t out_dtype, const int32_t* ops, int32_t n_ops, uint64_t bias,
+                               float scale, float clamp_min, float clamp_max, uint64_t workspace, size_t workspace_bytes,
+                               int32_t async);
 T0B_API size_t t0b_gemm_workspace_bytes(const t0b_gemm_config* cfg, uint32_t m, uint32_t n, uint32_t k);
 
 /* Column-sharded GEMM with the all-gather folded into the epilogue: this rank computes C[:, col0 : col0+n_local]

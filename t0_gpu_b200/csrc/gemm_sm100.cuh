@@ -31,6 +31,18 @@ enum EpilogueKind : int {
     EPI_SCALE = 6,
     EPI_ABS = 7,
     EPI_NEG = 8,
+    EPI_CLAMP = 9,
+};
+
+// A store-phase chain of up to four operations applied in order (the tile_ir epilogue chain,
+// src/t0/tile_ir.rs:2213-2339).  EPI_BIAS_RELU never appears here: the host expands it to {EPI_BIAS, EPI_RELU}.
+constexpr int kMaxEpiOps = 4;
+struct EpiChain {
+    int n;
+    int ops[kMaxEpiOps];
+    float alpha;              // EPI_SCALE factor
+    float clamp_lo, clamp_hi; // EPI_CLAMP bounds
+    const float* bias;        // f32[N] for EPI_BIAS
 };
 
 // Device status codes written to the context's status word.
@@ -49,8 +61,7 @@ struct GemmParams {
     void* c_dst[kMaxDst];   // destinations of the epilogue store: [0] local, [1..] peers of a column-sharded GEMM
     int n_dst;
     long long ldc;          // row pitch of C in elements
-    const float* bias;      // f32[N] or null
-    float alpha;            // EPI_SCALE factor
+    EpiChain epi;           // fused store-phase operations (none when epi.n == 0)
     float* partial;         // split-K slabs (f32, slab s at partial + s * slab_stride); null when split_k == 1
     long long slab_stride;  // elements
     long long ld_partial;   // row pitch of a slab in elements
@@ -60,7 +71,6 @@ struct GemmParams {
     int kb_total, kb_per_split;  // K blocks of 64
     int a_mn_major, b_mn_major;  // 0: operand stored K-contiguous; 1: stored M/N-contiguous
     int out_bf16;
-    int epilogue;
     int raster_along_n;     // 0: group tile rows (walk N inside a group of M tiles); 1: the transpose
     int group;              // rasterisation group width in tiles
     unsigned mn_lbo, mn_sbo, mn_kstep;  // descriptor byte offsets for M/N-contiguous operands
@@ -171,18 +181,27 @@ __device__ __forceinline__ bool bounded_wait(uint32_t bar, uint32_t parity, cons
     }
 }
 
-__device__ __forceinline__ float apply_epilogue(float v, int kind, float bias, float alpha) {
-    switch (kind) {
-        case EPI_BIAS: return v + bias;
-        case EPI_BIAS_RELU: return fmaxf(v + bias, 0.0f);
-        case EPI_RELU: return fmaxf(v, 0.0f);
-        case EPI_SILU: return v / (1.0f + __expf(-v));
-        case EPI_GELU_SIGMOID: return v / (1.0f + __expf(-1.702f * v));
-        case EPI_SCALE: return v * alpha;
-        case EPI_ABS: return fabsf(v);
-        case EPI_NEG: return -v;
-        default: return v;
+__device__ __forceinline__ bool chain_has_bias(const EpiChain& e) {
+    bool b = false;
+    for (int i = 0; i < e.n; ++i) b = b || (e.ops[i] == EPI_BIAS);
+    return b && e.bias != nullptr;
+}
+
+__device__ __forceinline__ float apply_chain(float v, const EpiChain& e, float bias) {
+    for (int i = 0; i < e.n; ++i) {
+        switch (e.ops[i]) {
+            case EPI_BIAS: v = v + bias; break;
+            case EPI_RELU: v = fmaxf(v, 0.0f); break;
+            case EPI_SILU: v = v / (1.0f + __expf(-v)); break;
+            case EPI_GELU_SIGMOID: v = v / (1.0f + __expf(-1.702f * v)); break;
+            case EPI_SCALE: v = v * e.alpha; break;
+            case EPI_ABS: v = fabsf(v); break;
+            case EPI_NEG: v = -v; break;
+            case EPI_CLAMP: v = fminf(fmaxf(v, e.clamp_lo), e.clamp_hi); break;
+            default: break;
+        }
     }
+    return v;
 }
 
 // Store one thread's 32 consecutive output columns of one row.
@@ -495,8 +514,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
             vec_ok = (ld_out % 8 == 0);
             for (int d = 0; d < p.n_dst; ++d) vec_ok = vec_ok && ((reinterpret_cast<uintptr_t>(p.c_dst[d]) & 15) == 0);
         }
-        const int epi = to_slab ? EPI_STORE : p.epilogue;
-        const bool need_bias = (epi == EPI_BIAS || epi == EPI_BIAS_RELU) && p.bias != nullptr;
+        const bool has_epi = !to_slab && p.epi.n > 0;
+        const bool need_bias = has_epi && chain_has_bias(p.epi);
         // The transposing path needs whole 16-byte pieces inside [0, N): N % 4 (f32) or N % 8 (bf16).
         const bool out16 = !to_slab && p.out_bf16;
         const bool tma_out = p.tma_store != 0;   // implies one destination, no slabs, TMA-addressable C
@@ -542,12 +561,12 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                         float v[32];
 #pragma unroll
                         for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(raw[j]);
-                        if (epi != EPI_STORE) {
+                        if (has_epi) {
 #pragma unroll
                             for (int j = 0; j < 32; ++j) {
                                 float b = 0.0f;
-                                if (need_bias && j < ncols) b = __ldg(p.bias + col0 + j);
-                                v[j] = apply_epilogue(v[j], epi, b, p.alpha);
+                                if (need_bias && j < ncols) b = __ldg(p.epi.bias + col0 + j);
+                                v[j] = apply_chain(v[j], p.epi, b);
                             }
                         }
                         stage_half_bf16(stage, lane, half, v);
@@ -573,12 +592,12 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                         float v[32];
 #pragma unroll
                         for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(raw[j]);
-                        if (epi != EPI_STORE) {
+                        if (has_epi) {
 #pragma unroll
                             for (int j = 0; j < 32; ++j) {
                                 float b = 0.0f;
-                                if (need_bias && j < ncols) b = __ldg(p.bias + col0 + j);
-                                v[j] = apply_epilogue(v[j], epi, b, p.alpha);
+                                if (need_bias && j < ncols) b = __ldg(p.epi.bias + col0 + j);
+                                v[j] = apply_chain(v[j], p.epi, b);
                             }
                         }
                         if (tma_out && lane == 0) ptx::bulk_wait_group_read<0>();   // the TMA store has read the tile
@@ -603,12 +622,12 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                     float v[32];
 #pragma unroll
                     for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(raw[j]);
-                    if (epi != EPI_STORE) {
+                    if (has_epi) {
 #pragma unroll
                         for (int j = 0; j < 32; ++j) {
                             float b = 0.0f;
-                            if (need_bias && j < ncols) b = __ldg(p.bias + col0 + j);
-                            v[j] = apply_epilogue(v[j], epi, b, p.alpha);
+                            if (need_bias && j < ncols) b = __ldg(p.epi.bias + col0 + j);
+                            v[j] = apply_chain(v[j], p.epi, b);
                         }
                     }
                     if (to_slab) {
@@ -662,9 +681,8 @@ struct ReduceParams {
     long long slab_stride, ld_partial;
     void* c;
     long long ldc;
-    const float* bias;
-    float alpha;
-    int M, N, sk, out_bf16, epilogue;
+    EpiChain epi;
+    int M, N, sk, out_bf16;
 };
 
 __global__ void __launch_bounds__(256) splitk_reduce_kernel(const ReduceParams p) {
@@ -690,9 +708,8 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(const ReduceParams p
                 for (int j = 0; j < nv; ++j) acc[j] = acc[j] + ps[j];
             }
         }
-        const bool need_bias = (p.epilogue == EPI_BIAS || p.epilogue == EPI_BIAS_RELU) && p.bias != nullptr;
-        for (int j = 0; j < nv; ++j)
-            acc[j] = apply_epilogue(acc[j], p.epilogue, need_bias ? p.bias[col + j] : 0.0f, p.alpha);
+        const bool need_bias = chain_has_bias(p.epi);
+        for (int j = 0; j < nv; ++j) acc[j] = apply_chain(acc[j], p.epi, need_bias ? p.epi.bias[col + j] : 0.0f);
         if (p.out_bf16) {
             __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.c) + static_cast<long long>(row) * p.ldc + col;
             for (int j = 0; j < nv; ++j) dst[j] = __float2bfloat16_rn(acc[j]);
@@ -711,10 +728,9 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(const ReduceParams p
 struct SimtParams {
     const __nv_bfloat16 *a, *b;
     void* c;
-    const float* bias;
-    float alpha;
+    EpiChain epi;
     long long lda, ldb, ldc;
-    int M, N, K, trans_a, trans_b, out_bf16, epilogue;
+    int M, N, K, trans_a, trans_b, out_bf16;
     int k_begin, k_end;
 };
 
@@ -751,12 +767,12 @@ __global__ void __launch_bounds__(256) gemm_bf16_simt_kernel(const SimtParams p)
         }
         __syncthreads();
     }
-    const bool need_bias = (p.epilogue == EPI_BIAS || p.epilogue == EPI_BIAS_RELU) && p.bias != nullptr;
+    const bool need_bias = chain_has_bias(p.epi);
     for (int i = 0; i < 4; ++i)
         for (int j = 0; j < 4; ++j) {
             const int gm = m0 + ty * 4 + i, gn = n0 + tx * 4 + j;
             if (gm < p.M && gn < p.N) {
-                const float v = apply_epilogue(acc[i][j], p.epilogue, need_bias ? p.bias[gn] : 0.0f, p.alpha);
+                const float v = apply_chain(acc[i][j], p.epi, need_bias ? p.epi.bias[gn] : 0.0f);
                 if (p.out_bf16) static_cast<__nv_bfloat16*>(p.c)[static_cast<long long>(gm) * p.ldc + gn] = __float2bfloat16_rn(v);
                 else static_cast<float*>(p.c)[static_cast<long long>(gm) * p.ldc + gn] = v;
             }

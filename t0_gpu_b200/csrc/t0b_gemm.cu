@@ -124,21 +124,40 @@ struct GemmCall {
     int n_dst;
     uint32_t m, n, k;
     uint64_t lda, ldb, ldc;
-    int out_bf16, epilogue;
-    uint64_t bias;
-    float alpha;
+    int out_bf16;
+    EpiChain epi;
     uint64_t workspace;
     size_t workspace_bytes;
     bool slabs_only;        // leave unreduced split-K slabs in c_dst[0] (reference contract)
     uint32_t force_split;   // for slabs_only: the exact number of slabs the caller expects
 };
 
+// Expand the public single-op epilogue code into a chain (EPI_BIAS_RELU = bias add, then ReLU).
+int32_t make_chain(t0b_ctx* ctx, const int32_t* ops, int n_ops, uint64_t bias, float alpha, float lo, float hi, EpiChain* out) {
+    EpiChain e{};
+    e.alpha = alpha; e.clamp_lo = lo; e.clamp_hi = hi; e.bias = reinterpret_cast<const float*>(bias);
+    for (int i = 0; i < n_ops; ++i) {
+        const int op = ops[i];
+        if (op == EPI_STORE) continue;
+        if (op < 0 || op > EPI_CLAMP) return set_error(ctx, T0B_ERR_INVALID, "gemm: unknown epilogue %d", op);
+        const int expanded[2] = {op == EPI_BIAS_RELU ? EPI_BIAS : op, EPI_RELU};
+        const int count = op == EPI_BIAS_RELU ? 2 : 1;
+        for (int j = 0; j < count; ++j) {
+            if (e.n >= kMaxEpiOps) return set_error(ctx, T0B_ERR_INVALID, "gemm: epilogue chain longer than %d operations", kMaxEpiOps);
+            e.ops[e.n++] = expanded[j];
+        }
+        if ((op == EPI_BIAS || op == EPI_BIAS_RELU) && !bias)
+            return set_error(ctx, T0B_ERR_INVALID, "gemm: bias epilogue without a bias pointer");
+    }
+    *out = e;
+    return T0B_OK;
+}
+
 int32_t launch_reduce(t0b_ctx* ctx, const float* partial, uint32_t sk, uint32_t m, uint32_t n, uint64_t slab_stride,
-                      uint64_t ld_partial, void* c, uint64_t ldc, int out_bf16, int epilogue, const float* bias,
-                      float alpha) {
+                      uint64_t ld_partial, void* c, uint64_t ldc, int out_bf16, const EpiChain& epi) {
     ReduceParams rp{partial, static_cast<long long>(slab_stride), static_cast<long long>(ld_partial), c,
-                    static_cast<long long>(ldc), bias, alpha, static_cast<int>(m), static_cast<int>(n),
-                    static_cast<int>(sk), out_bf16, epilogue};
+                    static_cast<long long>(ldc), epi, static_cast<int>(m), static_cast<int>(n),
+                    static_cast<int>(sk), out_bf16};
     const long long total = static_cast<long long>(m) * ((n + 3) / 4);
     const int blocks = static_cast<int>(std::min<long long>((total + 255) / 256, static_cast<long long>(ctx->num_sms) * 8));
     splitk_reduce_kernel<<<std::max(blocks, 1), 256, 0, ctx->stream>>>(rp);
@@ -156,9 +175,6 @@ int32_t run_gemm(t0b_ctx* ctx, const GemmCall& g) {
         return set_error(ctx, T0B_ERR_INVALID, "gemm: leading dimension smaller than the row length (lda=%llu ldb=%llu ldc=%llu)",
                          static_cast<unsigned long long>(g.lda), static_cast<unsigned long long>(g.ldb),
                          static_cast<unsigned long long>(g.ldc));
-    if (g.epilogue < 0 || g.epilogue > EPI_NEG) return set_error(ctx, T0B_ERR_INVALID, "gemm: unknown epilogue %d", g.epilogue);
-    if ((g.epilogue == EPI_BIAS || g.epilogue == EPI_BIAS_RELU) && !g.bias)
-        return set_error(ctx, T0B_ERR_INVALID, "gemm: bias epilogue without a bias pointer");
 
     t0b_gemm_config cfg;
     if (g.cfg) cfg = *g.cfg;
@@ -239,11 +255,9 @@ int32_t run_gemm(t0b_ctx* ctx, const GemmCall& g) {
             const int ndst = to_slabs ? 1 : g.n_dst;
             for (int d = 0; d < ndst; ++d) {
                 if (to_slabs) {
-                    sp.c = partial + slab_stride * s; sp.ldc = ld_partial; sp.out_bf16 = 0; sp.epilogue = EPI_STORE;
-                    sp.bias = nullptr; sp.alpha = 1.0f;
+                    sp.c = partial + slab_stride * s; sp.ldc = ld_partial; sp.out_bf16 = 0; sp.epi = EpiChain{};
                 } else {
-                    sp.c = reinterpret_cast<void*>(g.c_dst[d]); sp.ldc = g.ldc; sp.out_bf16 = g.out_bf16;
-                    sp.epilogue = g.epilogue; sp.bias = reinterpret_cast<const float*>(g.bias); sp.alpha = g.alpha;
+                    sp.c = reinterpret_cast<void*>(g.c_dst[d]); sp.ldc = g.ldc; sp.out_bf16 = g.out_bf16; sp.epi = g.epi;
                 }
                 dim3 grid((g.n + 63) / 64, (g.m + 63) / 64);
                 gemm_bf16_simt_kernel<<<grid, 256, 0, ctx->stream>>>(sp);
@@ -267,8 +281,7 @@ int32_t run_gemm(t0b_ctx* ctx, const GemmCall& g) {
         for (int d = 0; d < g.n_dst; ++d) p.c_dst[d] = reinterpret_cast<void*>(g.c_dst[d]);
         p.n_dst = g.n_dst;
         p.ldc = static_cast<long long>(g.ldc);
-        p.bias = reinterpret_cast<const float*>(g.bias);
-        p.alpha = g.alpha;
+        p.epi = g.epi;
         p.partial = to_slabs ? partial : nullptr;
         p.slab_stride = static_cast<long long>(slab_stride);
         p.ld_partial = static_cast<long long>(ld_partial);
@@ -282,7 +295,6 @@ int32_t run_gemm(t0b_ctx* ctx, const GemmCall& g) {
         p.a_mn_major = g.trans_a ? 1 : 0;     // A stored [K,M]: M contiguous
         p.b_mn_major = g.trans_b ? 0 : 1;     // B stored [K,N]: N contiguous
         p.out_bf16 = g.out_bf16;
-        p.epilogue = g.epilogue;
         p.raster_along_n = cfg.swap_grid ? 0 : 1;
         {
             // Concurrently running tiles should cover a square-ish patch of C, so that A and B panels are shared
@@ -297,7 +309,7 @@ int32_t run_gemm(t0b_ctx* ctx, const GemmCall& g) {
         p.wait_limit_ns = ctx->wait_limit_ns;
         if (g.slabs_only && sk == 1) {
             // One slab: store straight into it as f32.
-            p.out_bf16 = 0; p.epilogue = EPI_STORE; p.n_dst = 1; p.ldc = static_cast<long long>(ld_partial);
+            p.out_bf16 = 0; p.epi = EpiChain{}; p.n_dst = 1; p.ldc = static_cast<long long>(ld_partial);
         }
         // Epilogue through TMA stores when there is one plain destination the TMA unit can address; peers and
         // split-K slabs keep the warp-issued stores.
@@ -333,7 +345,7 @@ int32_t run_gemm(t0b_ctx* ctx, const GemmCall& g) {
     if (!g.slabs_only && sk > 1) {
         for (int d = 0; d < g.n_dst; ++d) {
             int32_t rc = launch_reduce(ctx, partial, sk, g.m, g.n, slab_stride, ld_partial, reinterpret_cast<void*>(g.c_dst[d]),
-                                       g.ldc, g.out_bf16, g.epilogue, reinterpret_cast<const float*>(g.bias), g.alpha);
+                                       g.ldc, g.out_bf16, g.epi);
             if (rc != T0B_OK) return rc;
             ++ctx->launches;
         }
@@ -370,12 +382,35 @@ int32_t t0b_gemm(t0b_ctx* ctx, const t0b_gemm_config* cfg, int32_t trans_a, int3
     GemmCall g{};
     g.cfg = cfg; g.trans_a = trans_a != 0; g.trans_b = trans_b != 0; g.a = a; g.b = b;
     g.c_dst[0] = c; g.n_dst = 1; g.m = m; g.n = n; g.k = k; g.lda = lda; g.ldb = ldb; g.ldc = ldc;
-    g.out_bf16 = out_dtype == T0B_OUT_BF16; g.epilogue = epilogue; g.bias = bias; g.alpha = alpha;
+    g.out_bf16 = out_dtype == T0B_OUT_BF16;
     g.workspace = workspace; g.workspace_bytes = workspace_bytes;
     if (out_dtype != T0B_OUT_F32 && out_dtype != T0B_OUT_BF16) return set_error(ctx, T0B_ERR_INVALID, "gemm: unknown out_dtype %d", out_dtype);
+    rc = make_chain(ctx, &epilogue, 1, bias, alpha, 0.0f, 0.0f, &g.epi);
+    if (rc != T0B_OK) return rc;
     rc = run_gemm(ctx, g);
     if (rc != T0B_OK) return rc;
     return finish(ctx, async, "t0b_gemm", 0);
+}
+
+int32_t t0b_gemm_chain(t0b_ctx* ctx, const t0b_gemm_config* cfg, int32_t trans_a, int32_t trans_b, uint64_t a, uint64_t b,
+                       uint64_t c, uint32_t m, uint32_t n, uint32_t k, uint64_t lda, uint64_t ldb, uint64_t ldc,
+                       int32_t out_dtype, const int32_t* ops, int32_t n_ops, uint64_t bias, float scale, float clamp_min,
+                       float clamp_max, uint64_t workspace, size_t workspace_bytes, int32_t async) {
+    int32_t rc = precheck(ctx);
+    if (rc != T0B_OK) return rc;
+    if (n_ops < 0 || (n_ops > 0 && !ops)) return set_error(ctx, T0B_ERR_INVALID, "gemm_chain: bad operation list");
+    if (out_dtype != T0B_OUT_F32 && out_dtype != T0B_OUT_BF16) return set_error(ctx, T0B_ERR_INVALID, "gemm: unknown out_dtype %d", out_dtype);
+    std::lock_guard<std::recursive_mutex> lk(ctx->mu);
+    GemmCall g{};
+    g.cfg = cfg; g.trans_a = trans_a != 0; g.trans_b = trans_b != 0; g.a = a; g.b = b;
+    g.c_dst[0] = c; g.n_dst = 1; g.m = m; g.n = n; g.k = k; g.lda = lda; g.ldb = ldb; g.ldc = ldc;
+    g.out_bf16 = out_dtype == T0B_OUT_BF16;
+    g.workspace = workspace; g.workspace_bytes = workspace_bytes;
+    rc = make_chain(ctx, ops, n_ops, bias, scale, clamp_min, clamp_max, &g.epi);
+    if (rc != T0B_OK) return rc;
+    rc = run_gemm(ctx, g);
+    if (rc != T0B_OK) return rc;
+    return finish(ctx, async, "t0b_gemm_chain", 0);
 }
 
 int32_t t0b_gemm_multi_dst(t0b_ctx* ctx, const t0b_gemm_config* cfg, int32_t trans_a, int32_t trans_b, uint64_t a,
@@ -404,7 +439,7 @@ int32_t t0b_gemm_multi_dst(t0b_ctx* ctx, const t0b_gemm_config* cfg, int32_t tra
     const size_t elem = out_dtype == T0B_OUT_BF16 ? 2 : 4;
     for (int d = 0; d < n_dst; ++d) g.c_dst[d] = c_dsts[d] ? c_dsts[d] + col0 * elem : 0;
     g.n_dst = n_dst; g.m = m; g.n = n_local; g.k = k; g.lda = lda; g.ldb = ldb; g.ldc = ldc;
-    g.out_bf16 = out_dtype == T0B_OUT_BF16; g.epilogue = EPI_STORE; g.alpha = 1.0f;
+    g.out_bf16 = out_dtype == T0B_OUT_BF16;
     rc = run_gemm(ctx, g);
     if (rc != T0B_OK) return rc;
     return finish(ctx, async, "t0b_gemm_multi_dst", 0);
@@ -422,7 +457,7 @@ int32_t t0b_gemm_slabs(t0b_ctx* ctx, const t0b_gemm_config* cfg, uint64_t x, uin
     else default_b200_config(m, k, n, ctx->num_sms, &local);
     GemmCall g{};
     g.cfg = &local; g.trans_a = 0; g.trans_b = 1; g.a = x; g.b = wt; g.c_dst[0] = y; g.n_dst = 1;
-    g.m = m; g.n = n; g.k = k; g.lda = k; g.ldb = k; g.ldc = n; g.out_bf16 = 0; g.epilogue = EPI_STORE; g.alpha = 1.0f;
+    g.m = m; g.n = n; g.k = k; g.lda = k; g.ldb = k; g.ldc = n; g.out_bf16 = 0;
     g.slabs_only = true; g.force_split = split_k;
     rc = run_gemm(ctx, g);
     if (rc != T0B_OK) return rc;
@@ -438,9 +473,11 @@ int32_t t0b_splitk_reduce(t0b_ctx* ctx, uint64_t partial, uint32_t split_k, uint
     if (m == 0 || n == 0) return T0B_OK;
     if (ld_partial < n || ldc < n) return set_error(ctx, T0B_ERR_INVALID, "splitk_reduce: pitch smaller than n");
     std::lock_guard<std::recursive_mutex> lk(ctx->mu);
+    EpiChain chain;
+    rc = make_chain(ctx, &epilogue, 1, bias, alpha, 0.0f, 0.0f, &chain);
+    if (rc != T0B_OK) return rc;
     rc = launch_reduce(ctx, reinterpret_cast<const float*>(partial), split_k, m, n, slab_stride_elems, ld_partial,
-                       reinterpret_cast<void*>(c), ldc, out_dtype == T0B_OUT_BF16, epilogue,
-                       reinterpret_cast<const float*>(bias), alpha);
+                       reinterpret_cast<void*>(c), ldc, out_dtype == T0B_OUT_BF16, chain);
     if (rc != T0B_OK) return rc;
     return finish(ctx, async, "t0b_splitk_reduce", 1);
 }
@@ -478,15 +515,20 @@ int32_t t0b_dispatch_kernargs(t0b_ctx* ctx, const t0b_gemm_config* cfg, uint32_t
     GemmCall g{};
     t0b_gemm_config local = *cfg;
     g.cfg = &local; g.trans_a = 0; g.trans_b = 1; g.a = x; g.b = wt; g.c_dst[0] = y; g.n_dst = 1;
-    g.m = m; g.n = n; g.k = k; g.lda = k; g.ldb = k; g.ldc = n_pitch; g.alpha = 1.0f;
+    g.m = m; g.n = n; g.k = k; g.lda = k; g.ldb = k; g.ldc = n_pitch;
     g.out_bf16 = 0;
-    g.epilogue = cfg->epilogue;
-    g.bias = len == 48 ? rd_u64(ka + 40) : 0;
-    if (g.epilogue != EPI_STORE && (len != 48 || !g.bias)) g.epilogue = EPI_STORE;   // gemm_gen.rs:437: bias 0 = plain store
+    {
+        int32_t epi = static_cast<int32_t>(cfg->epilogue);
+        const uint64_t bias = len == 48 ? rd_u64(ka + 40) : 0;
+        if (epi != EPI_STORE && (len != 48 || !bias)) epi = EPI_STORE;   // gemm_gen.rs:437: bias 0 = plain store
+        if (sk > 1) epi = EPI_STORE;
+        rc = make_chain(ctx, &epi, 1, bias, 1.0f, 0.0f, 0.0f, &g.epi);
+        if (rc != T0B_OK) return rc;
+    }
     if (sk > 1) {
         if (y_stride != m * n * 4u)
             return set_error(ctx, T0B_ERR_INVALID, "dispatch_kernargs: y_split_stride %u does not match M*N*4 = %u", y_stride, m * n * 4u);
-        g.slabs_only = true; g.force_split = sk; g.ldc = n; g.epilogue = EPI_STORE;
+        g.slabs_only = true; g.force_split = sk; g.ldc = n;
     } else {
         local.split_k = 0;
     }

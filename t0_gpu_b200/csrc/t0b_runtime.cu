@@ -24,6 +24,9 @@ int32_t set_error(t0b_ctx* ctx, int32_t code, const char* fmt, ...) {
 
 int32_t check_cuda(t0b_ctx* ctx, cudaError_t e, const char* what) {
     if (e == cudaSuccess) return T0B_OK;
+    // The runtime also remembers the error per host thread; clear that copy so it cannot surface later as the
+    // "last error" of an unrelated launch from another context.
+    cudaGetLastError();
     return set_error(ctx, T0B_ERR_CUDA, "%s: %s (%s)", what, cudaGetErrorString(e), cudaGetErrorName(e));
 }
 

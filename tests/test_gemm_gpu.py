@@ -440,3 +440,37 @@ def test_large_gemm_bf16_output_full_size(rt):
     assert torch.equal(c_blk, c[:, col0:col0 + n_local])
     del a, b, c, b_blk, c_blk
     torch.cuda.empty_cache()
+
+
+def test_epilogue_chain(rt):
+    """tile_ir's epilogue chain (src/t0/tile_ir.rs:41-62, 2213-2339): operations applied in list order."""
+    import ctypes as C
+    from t0_gpu_b200._lib import lib
+
+    m, k, n = 192, 256, 160
+    A = oracle.rand_bf16(m * k, 21).reshape(m, k)
+    Bt = oracle.rand_bf16(n * k, 22).reshape(n, k)
+    bias = np.linspace(-3, 3, n).astype(np.float32)
+    base = oracle.gemm_bf16(A, Bt, m, n, k).astype(np.float64)
+    da, db, dbias = rt.upload(A), rt.upload(Bt), rt.upload_f32(bias)
+    dc = rt.alloc(m * n * 4)
+    BIAS, RELU, SILU, GELU, SCALE, ABS, NEG, CLAMP = 1, 3, 4, 5, 6, 7, 8, 9
+    cases = [
+        ([BIAS, SCALE, RELU], lambda y: np.maximum((y + bias) * 0.5, 0)),
+        ([SCALE, BIAS, SILU], lambda y: (y * 0.5 + bias) / (1 + np.exp(-(y * 0.5 + bias)))),
+        ([ABS, NEG, CLAMP], lambda y: np.clip(-np.abs(y), -2.0, -0.25)),
+        ([BIAS, GELU, SCALE, CLAMP], lambda y: np.clip(((y + bias) / (1 + np.exp(-1.702 * (y + bias)))) * 0.5, -2.0, -0.25)),
+        ([], lambda y: y),
+    ]
+    for ops, fn in cases:
+        arr = (C.c_int32 * max(len(ops), 1))(*ops)
+        for cfg in (None, GemmConfig.tile_64x64_k16().with_(split_k=2)):      # fused in the GEMM and in the split-K reduce
+            cp = C.byref(cfg.to_c()) if cfg is not None else None
+            rt._check(lib().t0b_gemm_chain(rt.handle, cp, 0, 1, da.gpu_addr(), db.gpu_addr(), dc.gpu_addr(), m, n, k, k, k, n, 0,
+                                           arr, len(ops), dbias.gpu_addr(), 0.5, -2.0, -0.25, 0, 0, 0))
+            got = dc.read_as(np.float32, m * n).reshape(m, n)
+            ref = fn(base)
+            assert np.abs(got - ref).max() <= 2e-3 * max(1.0, np.abs(ref).max()), ops
+    too_long = (C.c_int32 * 5)(RELU, ABS, NEG, RELU, ABS)
+    assert lib().t0b_gemm_chain(rt.handle, None, 0, 1, da.gpu_addr(), db.gpu_addr(), dc.gpu_addr(), m, n, k, k, k, n, 0, too_long, 5,
+                                0, 1.0, 0.0, 0.0, 0, 0, 0) == -1

@@ -84,3 +84,26 @@ def test_launch_counter_counts_kernels(rt):
     assert rt.launch_count() == n0 + 1
     rt.gemm(a, a, c, 64, 64, 256, cfg=t.GemmConfig.preset("b200_128x64").with_(split_k=2))
     assert rt.launch_count() == n0 + 3      # GEMM + reduce
+
+
+def test_cuda_error_poisons_the_context_and_a_new_one_works():
+    """After a CUDA error the runtime refuses further work, like the reference's poisoned queue
+    (src/ignis/gpu_context.rs:149-157, 270-287).  The error is produced on the host side: a copy from an address
+    the driver knows is not device memory is rejected by the runtime before anything reaches the GPU."""
+    r = t.GpuRuntime()
+    host = np.zeros(16, np.uint8)
+    rc = lib().t0b_memcpy_d2h(r.handle, host.ctypes.data, 0x10, 16)
+    assert rc == -2 and r.is_poisoned()                       # T0B_ERR_CUDA
+    msg = lib().t0b_last_error(r.handle).decode()
+    assert "cudaMemcpyAsync" in msg
+    p = C.c_uint64()
+    assert lib().t0b_alloc(r.handle, 64, C.byref(p)) == -3    # T0B_ERR_POISONED
+    assert lib().t0b_gemm(r.handle, None, 0, 1, 16, 16, 16, 16, 16, 16, 16, 16, 16, 0, 0, 0, 1.0, 0, 0, 0) == -3
+    assert lib().t0b_last_error(r.handle).decode() == msg      # the first error's message is kept
+    r.close()
+    r2 = t.GpuRuntime()                                        # the device itself is fine
+    ones = r2.upload(np.full(64 * 64, 0x3F80, np.uint16))
+    c = r2.alloc(64 * 64 * 4)
+    r2.gemm(ones, ones, c, 64, 64, 64)
+    assert np.all(c.read_as(np.float32, 64 * 64) == 64.0)
+    r2.close()
