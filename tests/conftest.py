@@ -10,6 +10,12 @@ if ROOT not in sys.path:
 
 def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (B200, sm_100a)")
+    # The CUDA library is built in-tree and kept out of version control: build it when a fresh checkout lacks it
+    # (nvcc cross-compiles for sm_100a without a GPU).
+    from t0_gpu_b200 import _lib, build as lib_build
+
+    if not os.path.exists(_lib.LIB_PATH):
+        lib_build.build()
 
 
 def _has_gpu() -> bool:
