@@ -211,6 +211,19 @@ T0B_API int32_t t0b_gemm_chain(t0b_ctx* ctx, const t0b_gemm_config* cfg, int32_t
                                int32_t async);
 T0B_API size_t t0b_gemm_workspace_bytes(const t0b_gemm_config* cfg, uint32_t m, uint32_t n, uint32_t k);
 
+/* The same product with A, B and C in HOST memory (what a caller of the reference sees through its host-mapped
+ * buffers).  A is cut into blocks of `chunk_rows` output rows (0 = automatic, about eight blocks) and B into up to
+ * eight column panels; step s uploads A block s and B panel s, and every strip of C whose operands are then resident
+ * is multiplied at once and copied back while the next step uploads, on three streams.  With pinned host memory both
+ * copy directions and the math overlap; pageable memory works but serialises.  Every element is accumulated over the
+ * whole K in one pass (an automatically chosen config never splits K here), so the result has the same bits for every
+ * blocking and equals t0b_gemm without split-K.  Device staging buffers come from the context's pool.  Synchronous:
+ * returns when C is complete in host memory.  (The reference's counterpart is the write / dispatch / read sequence on
+ * mapped VRAM, examples/test_gemm_correctness.rs:136-211.) */
+T0B_API int32_t t0b_gemm_host(t0b_ctx* ctx, const t0b_gemm_config* cfg, int32_t trans_a, int32_t trans_b, const void* a,
+                              const void* b, void* c, uint32_t m, uint32_t n, uint32_t k, uint64_t lda, uint64_t ldb,
+                              uint64_t ldc, int32_t out_dtype, uint32_t chunk_rows);
+
 /* Column-sharded GEMM with the all-gather folded into the epilogue: this rank computes C[:, col0 : col0+n_local]
  * and stores every finished tile into each of the n_dst row-major [M, ldc] destinations (its own and its
  * peers', as peer-mapped device pointers).  No counterpart in the reference (single GPU). */

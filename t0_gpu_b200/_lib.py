@@ -77,6 +77,8 @@ SIGNATURES = {
     "t0b_gemm_chain": (_i32, [_ctx, _cfgp, _i32, _i32, _u64, _u64, _u64, _u32, _u32, _u32, _u64, _u64, _u64, _i32,
                               C.POINTER(_i32), _i32, _u64, _f, _f, _f, _u64, _sz, _i32]),
     "t0b_gemm_workspace_bytes": (_sz, [_cfgp, _u32, _u32, _u32]),
+    "t0b_gemm_host": (_i32, [_ctx, _cfgp, _i32, _i32, C.c_void_p, C.c_void_p, C.c_void_p, _u32, _u32, _u32, _u64, _u64, _u64,
+                             _i32, _u32]),
     "t0b_gemm_multi_dst": (_i32, [_ctx, _cfgp, _i32, _i32, _u64, _u64, C.POINTER(_u64), _i32, _u32, _u32, _u32, _u64,
                                   _u64, _u64, _u64, _i32, _i32]),
     "t0b_gemm_slabs": (_i32, [_ctx, _cfgp, _u64, _u64, _u64, _u32, _u32, _u32, _u32, _i32]),

@@ -6,6 +6,7 @@
 #include <cmath>
 #include <cstdlib>
 #include <cstring>
+#include <vector>
 
 #include "gemm_sm100.cuh"
 #include "t0b_internal.hpp"
@@ -130,6 +131,7 @@ struct GemmCall {
     size_t workspace_bytes;
     bool slabs_only;        // leave unreduced split-K slabs in c_dst[0] (reference contract)
     uint32_t force_split;   // for slabs_only: the exact number of slabs the caller expects
+    bool no_auto_split;     // an automatically chosen config keeps the whole contraction in one tile (fixed summation order)
 };
 
 // Expand the public single-op epilogue code into a chain (EPI_BIAS_RELU = bias add, then ReLU).
@@ -176,6 +178,30 @@ int32_t run_gemm(t0b_ctx* ctx, const GemmCall& g) {
                          static_cast<unsigned long long>(g.lda), static_cast<unsigned long long>(g.ldb),
                          static_cast<unsigned long long>(g.ldc));
 
+    {
+        // An operand that starts one of this runtime's own allocations must fit in it: an undersized buffer is reported
+        // here instead of faulting on the device.  (Pointers from elsewhere, or into the middle of a buffer, are not known.)
+        std::lock_guard<std::recursive_mutex> lk(ctx->mu);
+        auto too_small = [&](uint64_t ptr, uint64_t rows, uint64_t cols, uint64_t ld, size_t elem_bytes, uint64_t* have) {
+            auto it = ctx->live.find(reinterpret_cast<void*>(ptr));
+            if (it == ctx->live.end() || rows == 0 || cols == 0) return false;
+            *have = it->second;
+            return ((rows - 1) * ld + cols) * elem_bytes > it->second;
+        };
+        uint64_t have = 0;
+        if (too_small(g.a, g.trans_a ? g.k : g.m, g.trans_a ? g.m : g.k, g.lda, 2, &have))
+            return set_error(ctx, T0B_ERR_INVALID, "gemm: A (%u x %u bf16) does not fit its %llu-byte buffer", g.m, g.k,
+                             static_cast<unsigned long long>(have));
+        if (too_small(g.b, g.trans_b ? g.n : g.k, g.trans_b ? g.k : g.n, g.ldb, 2, &have))
+            return set_error(ctx, T0B_ERR_INVALID, "gemm: B (%u x %u bf16) does not fit its %llu-byte buffer", g.k, g.n,
+                             static_cast<unsigned long long>(have));
+        if (!g.slabs_only)
+            for (int d = 0; d < g.n_dst; ++d)
+                if (too_small(g.c_dst[d], g.m, g.n, g.ldc, g.out_bf16 ? 2 : 4, &have))
+                    return set_error(ctx, T0B_ERR_INVALID, "gemm: C (%u x %u) does not fit its %llu-byte buffer", g.m, g.n,
+                                     static_cast<unsigned long long>(have));
+    }
+
     t0b_gemm_config cfg;
     if (g.cfg) cfg = *g.cfg;
     else {
@@ -184,6 +210,7 @@ int32_t run_gemm(t0b_ctx* ctx, const GemmCall& g) {
         auto it = ctx->tuned.find(key);
         if (it != ctx->tuned.end()) cfg = it->second;
         else default_b200_config(g.m, g.k, g.n, ctx->num_sms, &cfg);
+        if (g.no_auto_split) cfg.split_k = 0;
     }
     if (g.slabs_only) cfg.split_k = g.force_split;
     if (cfg.split_k > 1 && (cfg.split_k & (cfg.split_k - 1)) != 0)
@@ -411,6 +438,131 @@ int32_t t0b_gemm_chain(t0b_ctx* ctx, const t0b_gemm_config* cfg, int32_t trans_a
     rc = run_gemm(ctx, g);
     if (rc != T0B_OK) return rc;
     return finish(ctx, async, "t0b_gemm_chain", 0);
+}
+
+int32_t t0b_gemm_host(t0b_ctx* ctx, const t0b_gemm_config* cfg, int32_t trans_a, int32_t trans_b, const void* a, const void* b,
+                      void* c, uint32_t m, uint32_t n, uint32_t k, uint64_t lda, uint64_t ldb, uint64_t ldc, int32_t out_dtype,
+                      uint32_t chunk_rows) {
+    int32_t rc = precheck(ctx);
+    if (rc != T0B_OK) return rc;
+    if (m == 0 || n == 0) return T0B_OK;
+    if (!a || !b || !c) return set_error(ctx, T0B_ERR_INVALID, "gemm_host: null host pointer");
+    if (out_dtype != T0B_OUT_F32 && out_dtype != T0B_OUT_BF16) return set_error(ctx, T0B_ERR_INVALID, "gemm_host: unknown out_dtype %d", out_dtype);
+    const uint64_t a_rows = trans_a ? k : m, a_cols = trans_a ? m : k;
+    const uint64_t b_rows = trans_b ? n : k, b_cols = trans_b ? k : n;
+    if (lda < a_cols || ldb < b_cols || ldc < n) return set_error(ctx, T0B_ERR_INVALID, "gemm_host: pitch smaller than the row");
+    if (ctx->capturing) return set_error(ctx, T0B_ERR_INVALID, "gemm_host: not available during graph capture");
+    std::lock_guard<std::recursive_mutex> lk(ctx->mu);
+    if (!ctx->h2d_stream) {
+        rc = check_cuda(ctx, cudaStreamCreateWithFlags(&ctx->h2d_stream, cudaStreamNonBlocking), "cudaStreamCreate(h2d)");
+        if (rc == T0B_OK) rc = check_cuda(ctx, cudaStreamCreateWithFlags(&ctx->d2h_stream, cudaStreamNonBlocking), "cudaStreamCreate(d2h)");
+        if (rc != T0B_OK) return rc;
+    }
+    const size_t oelem = out_dtype == T0B_OUT_BF16 ? 2 : 4;
+    // Device copies are dense, with pitches rounded up so that every row starts on a 16-byte boundary (TMA).
+    const uint64_t dlda = (a_cols + 7) & ~7ull, dldb = (b_cols + 7) & ~7ull, dldc = (static_cast<uint64_t>(n) + 7) & ~7ull;
+    uint64_t da = 0, db = 0, dc = 0;
+    rc = t0b_alloc(ctx, a_rows * dlda * 2, &da);
+    if (rc == T0B_OK) rc = t0b_alloc(ctx, b_rows * dldb * 2, &db);
+    if (rc == T0B_OK) rc = t0b_alloc(ctx, static_cast<uint64_t>(m) * dldc * oelem, &dc);
+    if (rc != T0B_OK) {
+        if (da) t0b_recycle(ctx, da);
+        if (db) t0b_recycle(ctx, db);
+        return rc;
+    }
+    // The product is cut into row blocks of A (and C) and column panels of B (and C).  Step s uploads A block s and
+    // B panel s; the blocks of C that became computable (row strip s up to panel s, column strip s above it) are
+    // multiplied and copied back while step s+1 uploads, so both PCIe directions stay busy from the second step on.
+    if (chunk_rows == 0) chunk_rows = std::max<uint32_t>(512u, ((m + 7) / 8 + 511u) & ~511u);   // about eight blocks
+    chunk_rows = (chunk_rows + 127u) & ~127u;
+    const uint32_t nchunks = (m + chunk_rows - 1) / chunk_rows;
+    const uint32_t want_panels = std::max(1u, std::min(8u, n / 512u));
+    const uint32_t panel_cols = (((n + want_panels - 1) / want_panels) + 63u) & ~63u;
+    const uint32_t npanels = (n + panel_cols - 1) / panel_cols;
+    const uint32_t nsteps = std::max(nchunks, npanels);
+    std::vector<cudaEvent_t> ev(3 * static_cast<size_t>(nsteps) + 1, nullptr);
+    for (auto& x : ev) cudaEventCreateWithFlags(&x, cudaEventDisableTiming);
+    cudaEvent_t* ev_up = ev.data();                  // step s uploaded
+    cudaEvent_t* ev_row = ev.data() + nsteps;        // row strip s multiplied
+    cudaEvent_t* ev_col = ev.data() + 2 * nsteps;    // column strip s multiplied
+    cudaEvent_t ev_start = ev.back();
+    // Work already queued on the compute stream (e.g. earlier users of the pooled buffers) goes first.
+    cudaEventRecord(ev_start, ctx->stream);
+    cudaStreamWaitEvent(ctx->h2d_stream, ev_start, 0);
+    cudaStreamWaitEvent(ctx->d2h_stream, ev_start, 0);
+    cudaError_t e = cudaSuccess;
+    GemmCall g{};
+    g.cfg = cfg; g.trans_a = trans_a != 0; g.trans_b = trans_b != 0; g.n_dst = 1;
+    g.k = k; g.lda = dlda; g.ldb = dldb; g.ldc = dldc; g.out_bf16 = out_dtype == T0B_OUT_BF16;
+    g.no_auto_split = true;   // blocks of one product must not differ in summation order; the call is PCIe-bound anyway
+    // Multiply C[r0:r0+rows, c0:c0+cols] on the compute stream, then copy it back behind `done`.
+    auto strip = [&](uint32_t r0, uint32_t rows, uint32_t c0, uint32_t cols, cudaEvent_t done) {
+        g.a = trans_a ? da + static_cast<uint64_t>(r0) * 2 : da + static_cast<uint64_t>(r0) * dlda * 2;
+        g.b = trans_b ? db + static_cast<uint64_t>(c0) * dldb * 2 : db + static_cast<uint64_t>(c0) * 2;
+        g.c_dst[0] = dc + (static_cast<uint64_t>(r0) * dldc + c0) * oelem;
+        g.m = rows;
+        g.n = cols;
+        rc = run_gemm(ctx, g);
+        if (rc != T0B_OK) return;
+        cudaEventRecord(done, ctx->stream);
+        cudaStreamWaitEvent(ctx->d2h_stream, done, 0);
+        e = cudaMemcpy2DAsync(static_cast<char*>(c) + (static_cast<uint64_t>(r0) * ldc + c0) * oelem, ldc * oelem,
+                              reinterpret_cast<char*>(dc) + (static_cast<uint64_t>(r0) * dldc + c0) * oelem, dldc * oelem,
+                              static_cast<size_t>(cols) * oelem, rows, cudaMemcpyDeviceToHost, ctx->d2h_stream);
+    };
+    for (uint32_t s = 0; s < nsteps && e == cudaSuccess && rc == T0B_OK; ++s) {
+        const uint32_t r0 = s * chunk_rows, c0 = s * panel_cols;
+        const uint32_t rows = s < nchunks ? std::min(chunk_rows, m - r0) : 0;
+        const uint32_t cols = s < npanels ? std::min(panel_cols, n - c0) : 0;
+        if (rows && e == cudaSuccess) {
+            if (!trans_a)   // A[M, K]: a row block
+                e = cudaMemcpy2DAsync(reinterpret_cast<char*>(da) + static_cast<uint64_t>(r0) * dlda * 2, dlda * 2,
+                                      static_cast<const char*>(a) + static_cast<uint64_t>(r0) * lda * 2, lda * 2,
+                                      static_cast<size_t>(k) * 2, rows, cudaMemcpyHostToDevice, ctx->h2d_stream);
+            else            // A[K, M]: a column block
+                e = cudaMemcpy2DAsync(reinterpret_cast<char*>(da) + static_cast<uint64_t>(r0) * 2, dlda * 2,
+                                      static_cast<const char*>(a) + static_cast<uint64_t>(r0) * 2, lda * 2,
+                                      static_cast<size_t>(rows) * 2, k, cudaMemcpyHostToDevice, ctx->h2d_stream);
+        }
+        if (cols && e == cudaSuccess) {
+            if (!trans_b)   // B[K, N]: a column block
+                e = cudaMemcpy2DAsync(reinterpret_cast<char*>(db) + static_cast<uint64_t>(c0) * 2, dldb * 2,
+                                      static_cast<const char*>(b) + static_cast<uint64_t>(c0) * 2, ldb * 2,
+                                      static_cast<size_t>(cols) * 2, k, cudaMemcpyHostToDevice, ctx->h2d_stream);
+            else            // B[N, K]: a row block
+                e = cudaMemcpy2DAsync(reinterpret_cast<char*>(db) + static_cast<uint64_t>(c0) * dldb * 2, dldb * 2,
+                                      static_cast<const char*>(b) + static_cast<uint64_t>(c0) * ldb * 2, ldb * 2,
+                                      static_cast<size_t>(k) * 2, cols, cudaMemcpyHostToDevice, ctx->h2d_stream);
+        }
+        if (e != cudaSuccess) break;
+        cudaEventRecord(ev_up[s], ctx->h2d_stream);
+        cudaStreamWaitEvent(ctx->stream, ev_up[s], 0);
+        // Row strip: the new rows against every panel uploaded so far.
+        if (rows) {
+            const uint32_t last_panel = std::min(s, npanels - 1);
+            const uint32_t c_end = std::min(n, (last_panel + 1) * panel_cols);
+            strip(r0, rows, 0, c_end, ev_row[s]);
+        }
+        // Column strip: the new panel against every row block uploaded before this step.
+        if (cols && s > 0 && e == cudaSuccess && rc == T0B_OK) {
+            const uint32_t last_chunk = std::min(s - 1, nchunks - 1);
+            const uint32_t r_end = std::min(m, (last_chunk + 1) * chunk_rows);
+            strip(0, r_end, c0, cols, ev_col[s]);
+        }
+    }
+    cudaError_t e1 = cudaStreamSynchronize(ctx->d2h_stream);
+    cudaError_t e2 = cudaStreamSynchronize(ctx->stream);
+    cudaError_t e3 = cudaStreamSynchronize(ctx->h2d_stream);
+    for (auto& x : ev) cudaEventDestroy(x);
+    t0b_recycle(ctx, da);
+    t0b_recycle(ctx, db);
+    t0b_recycle(ctx, dc);
+    if (rc != T0B_OK) return rc;
+    for (cudaError_t x : {e, e1, e2, e3})
+        if (x != cudaSuccess) return check_cuda(ctx, x, "gemm_host");
+    const int st = t0b_device_status(ctx, 0);
+    if (st != 0) return set_error(ctx, T0B_ERR_DEVICE, "gemm_host: device status %d (a bounded in-kernel wait ran out)", st);
+    return T0B_OK;
 }
 
 int32_t t0b_gemm_multi_dst(t0b_ctx* ctx, const t0b_gemm_config* cfg, int32_t trans_a, int32_t trans_b, uint64_t a,

@@ -62,6 +62,8 @@ struct t0b_ctx {
     // In-memory autotune results keyed by "MxNxK/ta/tb/out".
     std::unordered_map<std::string, t0b_gemm_config> tuned;
     std::string autotune_dir;   // empty: the disk cache is not consulted
+    // Copy streams of the host-buffer GEMM (created on first use).
+    cudaStream_t h2d_stream = nullptr, d2h_stream = nullptr;
 };
 
 namespace t0b {

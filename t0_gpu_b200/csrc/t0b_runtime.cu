@@ -109,6 +109,8 @@ void t0b_ctx_destroy(t0b_ctx* ctx) {
     for (auto& kv : ctx->pool_free) cudaFree(kv.second);
     for (auto& kv : ctx->live) cudaFree(kv.first);
     if (ctx->ws) cudaFree(ctx->ws);
+    if (ctx->h2d_stream) cudaStreamDestroy(ctx->h2d_stream);
+    if (ctx->d2h_stream) cudaStreamDestroy(ctx->d2h_stream);
     if (ctx->status_host) cudaFreeHost(ctx->status_host);
     if (ctx->own_stream) cudaStreamDestroy(ctx->own_stream);
     delete ctx;

@@ -474,3 +474,37 @@ def test_epilogue_chain(rt):
     too_long = (C.c_int32 * 5)(RELU, ABS, NEG, RELU, ABS)
     assert lib().t0b_gemm_chain(rt.handle, None, 0, 1, da.gpu_addr(), db.gpu_addr(), dc.gpu_addr(), m, n, k, k, k, n, 0, too_long, 5,
                                 0, 1.0, 0.0, 0.0, 0, 0, 0) == -1
+
+
+@pytest.mark.parametrize("m,n,k,ta,tb,chunk", [(1000, 520, 264, False, True, 256), (1000, 520, 264, False, False, 0),
+                                               (640, 300, 200, True, False, 128), (2048, 1024, 512, False, False, 512),
+                                               (77, 33, 100, False, True, 0), (300, 4100, 136, False, False, 0),
+                                               (1100, 2100, 72, True, True, 256), (1536, 1536, 64, False, True, 384)])
+def test_host_buffer_gemm_pipeline(rt, m, n, k, ta, tb, chunk):
+    """A, B and C in host memory: row blocks of A and column panels of B uploaded alternately, every strip of C
+    multiplied and copied back as soon as its operands are resident (more blocks than panels, more panels than
+    blocks, one of each)."""
+    from t0_gpu_b200._lib import lib
+
+    A = oracle.rand_bf16(m * k, 3 * m + k).reshape(m, k)
+    Bt = oracle.rand_bf16(n * k, 5 * n + k).reshape(n, k)
+    ref = oracle.gemm_bf16(A, Bt, m, n, k, threads=8)
+    a_h = np.ascontiguousarray(A.T) if ta else A
+    b_h = Bt if tb else np.ascontiguousarray(Bt.T)
+    ldc = n + 5
+    for out_dtype in (OUT_F32, OUT_BF16):
+        c_h = np.full((m, ldc), -9999.0, np.float32) if out_dtype == OUT_F32 else np.full((m, ldc), 0xC61C, np.uint16)
+        rt._check(lib().t0b_gemm_host(rt.handle, None, int(ta), int(tb), a_h.ctypes.data, b_h.ctypes.data, c_h.ctypes.data, m, n, k,
+                                      a_h.shape[1], b_h.shape[1], ldc, out_dtype, chunk))
+        got = c_h[:, :n] if out_dtype == OUT_F32 else oracle.bf16_to_f32(np.ascontiguousarray(c_h[:, :n]))
+        if out_dtype == OUT_F32:
+            check(got, ref, k, A, Bt)
+            assert np.all(c_h[:, n:] == -9999.0)            # the pitch padding of the host C is untouched
+            # Another row-block size gives the same bits: the blocking does not change the summation order.
+            got = got.copy()
+            rt._check(lib().t0b_gemm_host(rt.handle, None, int(ta), int(tb), a_h.ctypes.data, b_h.ctypes.data, c_h.ctypes.data,
+                                          m, n, k, a_h.shape[1], b_h.shape[1], ldc, out_dtype, 128 if chunk != 128 else 640))
+            assert np.array_equal(c_h[:, :n], got)
+        else:
+            assert np.linalg.norm(got - ref) / np.linalg.norm(ref) <= 5e-3
+            assert np.all(c_h[:, n:] == 0xC61C)

@@ -78,12 +78,24 @@ def test_tuner_returns_a_valid_config(rt):
 
 
 def test_launch_counter_counts_kernels(rt):
-    a = rt.alloc(64 * 64 * 2); c = rt.alloc(64 * 64 * 4)
+    a = rt.alloc(64 * 256 * 2); c = rt.alloc(64 * 64 * 4)
     n0 = rt.launch_count()
     rt.gemm(a, a, c, 64, 64, 64, cfg=t.GemmConfig.preset("b200_128x64"))
     assert rt.launch_count() == n0 + 1
     rt.gemm(a, a, c, 64, 64, 256, cfg=t.GemmConfig.preset("b200_128x64").with_(split_k=2))
     assert rt.launch_count() == n0 + 3      # GEMM + reduce
+
+
+def test_gemm_rejects_operands_larger_than_their_buffers(rt):
+    """An operand that starts one of the runtime's own allocations must fit in it; the call is refused on the host
+    and nothing is launched (the reference asserts the same way on GpuBuffer::write, src/kfd/mod.rs:962-975)."""
+    small = rt.alloc(1 << 20); big, big2, big3 = rt.alloc(4 << 20), rt.alloc(4 << 20), rt.alloc(4 << 20)
+    n0 = rt.launch_count()
+    for args in ((small, big2, big3), (big, small, big3), (big, big2, small)):
+        with pytest.raises(t.T0Error, match="does not fit"):
+            rt.gemm(args[0], args[1], args[2], 1024, 1024, 1024)
+    assert rt.launch_count() == n0 and not rt.is_poisoned()
+    rt.gemm(big, big2, big3, 1024, 1024, 1024)               # fitting operands pass
 
 
 def test_cuda_error_poisons_the_context_and_a_new_one_works():
