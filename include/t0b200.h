@@ -324,6 +324,52 @@ T0B_API int32_t t0b_adamw_step(t0b_ctx* ctx, uint64_t params, uint64_t grads, ui
                                float weight_decay, uint32_t t, float grad_scale, int32_t async);
 
 /* ------------------------------------------------------------------------------------------------
+ * tile_ir front end: TileGemm specs with M/N/K edge handling and an epilogue chain (src/t0/tile_ir.rs).
+ * ---------------------------------------------------------------------------------------------- */
+enum { T0B_TILE_NT = 0, T0B_TILE_NN = 1 };          /* TileTranspose, src/t0/tile_ir.rs:72-78 */
+#define T0B_TILE_MAX_EPILOGUE 4
+/* struct TileGemm, src/t0/tile_ir.rs:92-117.  `epilogue` holds T0B_EPI_* codes of the tile_ir members
+ * (BIAS, SCALE, RELU, SILU, GELU_SIGMOID, ABS, NEG, CLAMP), applied in order. */
+typedef struct t0b_tile_gemm {
+    uint32_t tile_m, tile_n, tile_k;
+    uint32_t wgp_mode, double_buffer;
+    uint32_t split_k;                                /* 1 = none */
+    uint32_t swap_grid;
+    uint32_t transpose;                              /* T0B_TILE_NT / T0B_TILE_NN */
+    uint32_t acc_swap;
+    uint32_t n_epilogue;
+    int32_t epilogue[T0B_TILE_MAX_EPILOGUE];
+} t0b_tile_gemm;
+/* The named constructors TileGemm::tile_*(), src/t0/tile_ir.rs:119-316: "128x64_k16", "64x64_k16", "64x64_k32",
+ * "64x64_k64", "32x64_k16", "128x64_k32", "64x128_k32", "64x128_k16", "128x128_k16", "128x128_k32", "128x128_k48",
+ * "128x128_k16_swap", "128x128_k32_swap", "256x64_k32_wgp", "256x64_k64_wgp", "128x128_k64", "128x64_k64". */
+T0B_API int32_t t0b_tile_preset(const char* name, t0b_tile_gemm* out);
+/* TileGemm::name(), src/t0/tile_ir.rs:406-433 (the kernel-cache key).  Returns the length written, <0 on error. */
+T0B_API int32_t t0b_tile_name(const t0b_tile_gemm* spec, char* buf, size_t cap);
+/* TileGemm::wg_size() / lds_total(), src/t0/tile_ir.rs:375-397. */
+T0B_API uint32_t t0b_tile_wg_size(const t0b_tile_gemm* spec);
+T0B_API uint32_t t0b_tile_lds_total(const t0b_tile_gemm* spec);
+/* tile_auto_select(m, k, n, transpose), src/t0/tile_ir.rs:471-568: same branch outcomes (tile and split_k). */
+T0B_API int32_t t0b_tile_auto_select(uint32_t m, uint32_t k, uint32_t n, uint32_t transpose, t0b_tile_gemm* out);
+/* tile_ir::compute_grid, src/t0/tile_ir.rs:3193-3202: [x threads, y workgroups * split_k, 1]. */
+T0B_API int32_t t0b_tile_compute_grid(const t0b_tile_gemm* spec, uint32_t m, uint32_t n, uint32_t grid[3]);
+/* The kernarg blob of a lowered TileGemm: the 44 bytes of build_kernargs_m (src/t0/tile_ir.rs:3173-3190; the
+ * split_k_shift field at 32..36 is filled from the spec) followed by the epilogue arguments in the order lower_gemm
+ * declares them (src/t0/tile_ir.rs:670-682), each naturally aligned: bias pointer (u64, at 48) if the chain has
+ * BiasAdd, scale (f32) if it has Scale, clamp_min and clamp_max (f32) if it has Clamp.  Returns the length written
+ * (44..68), <0 on error. */
+T0B_API int32_t t0b_tile_build_kernargs(const t0b_tile_gemm* spec, uint64_t x, uint64_t wt, uint64_t y, uint32_t k,
+                                        uint32_t n, uint32_t m, uint64_t bias, float scale, float clamp_min,
+                                        float clamp_max, uint8_t* out, size_t cap);
+/* lower_gemm(&spec) + ensure_kernel_t0 + dispatch (src/t0/tile_ir.rs:585, src/ignis/gpu_context.rs:196-332) in one
+ * call: runs the spec on the blob above.  NT reads WT[N,K] (pitch K), NN reads B[K,N] (pitch N); X has pitch K, Y
+ * pitch N.  Any M, N, K (edges are masked; no padding needed).  `grid` must equal t0b_tile_compute_grid for the M in
+ * the blob.  split_k > 1 produces the complete product in Y (slabs summed on the device in slab order); the
+ * reference's tile_ir kernels leave y_split_stride at 0 there and race on Y (src/t0/cost_model.rs:570-571). */
+T0B_API int32_t t0b_tile_dispatch(t0b_ctx* ctx, const t0b_tile_gemm* spec, const uint32_t grid[3], const uint8_t* kernargs,
+                                  size_t len, int32_t async);
+
+/* ------------------------------------------------------------------------------------------------
  * CUDA-graph capture for launch-bound shapes (takes the place of the AQL batch submit,
  * GpuRuntime::dispatch_async + wait_idle, gpu_context.rs:332, 297).
  * ---------------------------------------------------------------------------------------------- */

@@ -8,4 +8,5 @@ from .gemm_gen import (EpilogueOp, GemmConfig, GemmPlan, GemmTranspose, auto_sel
                        build_kernargs_backward_weight, build_kernargs_m, build_kernargs_with_bias, compute_grid,
                        compute_grid_auto, compute_grid_backward_data, compute_grid_backward_weight,
                        compute_grid_split_k, resolve_plan, standard_configs, sweep_configs)
+from . import tile_ir  # noqa: F401
 from .gpu_context import OUT_BF16, OUT_F32, GpuBuffer, GpuRuntime, T0Error  # noqa: F401

@@ -20,6 +20,12 @@ class GemmPlanC(C.Structure):
         "bm", "bn", "bk", "cta_group", "m_tiles", "n_tiles", "stages", "split_k", "kb_per_split", "use_tma", "grid", "smem_bytes")]
 
 
+class TileGemmC(C.Structure):
+    _fields_ = [(n, C.c_uint32) for n in (
+        "tile_m", "tile_n", "tile_k", "wgp_mode", "double_buffer", "split_k", "swap_grid", "transpose", "acc_swap",
+        "n_epilogue")] + [("epilogue", C.c_int32 * 4)]
+
+
 _u32, _u64, _i32, _sz, _f = C.c_uint32, C.c_uint64, C.c_int32, C.c_size_t, C.c_float
 _ctx = C.c_void_p
 _cfgp = C.POINTER(GemmConfigC)
@@ -84,6 +90,14 @@ SIGNATURES = {
     "t0b_gemm_slabs": (_i32, [_ctx, _cfgp, _u64, _u64, _u64, _u32, _u32, _u32, _u32, _i32]),
     "t0b_splitk_reduce": (_i32, [_ctx, _u64, _u32, _u32, _u32, _u64, _u64, _u64, _u64, _i32, _i32, _u64, _f, _i32]),
     "t0b_dispatch_kernargs": (_i32, [_ctx, _cfgp, _u32, _u32, _u8p, _sz, _i32]),
+    "t0b_tile_preset": (_i32, [C.c_char_p, C.POINTER(TileGemmC)]),
+    "t0b_tile_name": (_i32, [C.POINTER(TileGemmC), C.c_char_p, _sz]),
+    "t0b_tile_wg_size": (_u32, [C.POINTER(TileGemmC)]),
+    "t0b_tile_lds_total": (_u32, [C.POINTER(TileGemmC)]),
+    "t0b_tile_auto_select": (_i32, [_u32, _u32, _u32, _u32, C.POINTER(TileGemmC)]),
+    "t0b_tile_compute_grid": (_i32, [C.POINTER(TileGemmC), _u32, _u32, _u32p]),
+    "t0b_tile_build_kernargs": (_i32, [C.POINTER(TileGemmC), _u64, _u64, _u64, _u32, _u32, _u32, _u64, _f, _f, _f, _u8p, _sz]),
+    "t0b_tile_dispatch": (_i32, [_ctx, C.POINTER(TileGemmC), _u32p, _u8p, _sz, _i32]),
     "t0b_tune": (_i32, [_ctx, _u32, _u32, _u32, _i32, _i32, _i32, _cfgp, C.POINTER(_f)]),
     "t0b_tune_cache_save": (_i32, [C.c_char_p, _u32, _u32, _u32, _cfgp, _f]),
     "t0b_tune_cache_load": (_i32, [C.c_char_p, _u32, _u32, _u32, _cfgp, C.POINTER(_f)]),

@@ -16,7 +16,7 @@ OUT_DIR = os.path.join(HERE, "lib")
 OUT = os.path.join(OUT_DIR, "libt0b200.so")
 OBJ_DIR = os.path.join(OUT_DIR, "obj")
 
-SOURCES = ["t0b_runtime.cu", "t0b_gemm.cu", "t0b_rowops.cu", "t0b_gemm_gen.cpp"]
+SOURCES = ["t0b_runtime.cu", "t0b_gemm.cu", "t0b_rowops.cu", "t0b_gemm_gen.cpp", "t0b_tile_ir.cpp"]
 HEADERS = ["gemm_sm100.cuh", "ptx_sm100.cuh", "t0b_internal.hpp", os.path.join("..", "..", "include", "t0b200.h")]
 
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")

@@ -689,6 +689,51 @@ int32_t t0b_dispatch_kernargs(t0b_ctx* ctx, const t0b_gemm_config* cfg, uint32_t
     return finish(ctx, async, "t0b_dispatch_kernargs", 0);
 }
 
+int32_t t0b_tile_dispatch(t0b_ctx* ctx, const t0b_tile_gemm* spec, const uint32_t grid[3], const uint8_t* ka, size_t len,
+                          int32_t async) {
+    int32_t rc = precheck(ctx);
+    if (rc != T0B_OK) return rc;
+    if (!spec || !grid || !ka) return set_error(ctx, T0B_ERR_INVALID, "tile_dispatch: null spec, grid or kernargs");
+    if (!tile_spec_valid(spec)) return set_error(ctx, T0B_ERR_INVALID, "tile_dispatch: invalid TileGemm spec");
+    size_t bias_off = 0, scale_off = 0, clamp_off = 0;
+    const size_t want = tile_kernarg_layout(spec, &bias_off, &scale_off, &clamp_off);
+    if (len != want)
+        return set_error(ctx, T0B_ERR_INVALID, "tile_dispatch: this spec takes a %zu-byte kernarg blob, got %zu", want, len);
+    const uint64_t x = rd_u64(ka), wt = rd_u64(ka + 8), y = rd_u64(ka + 16);
+    const uint32_t k = rd_u32(ka + 24), n = rd_u32(ka + 28), m = rd_u32(ka + 40);
+    uint32_t expect[3];
+    t0b_tile_compute_grid(spec, m, n, expect);
+    if (grid[0] != expect[0] || grid[1] != expect[1] || grid[2] != 1)
+        return set_error(ctx, T0B_ERR_INVALID, "tile_dispatch: grid [%u,%u,%u] does not match compute_grid [%u,%u,1] for M=%u N=%u",
+                         grid[0], grid[1], grid[2], expect[0], expect[1], m, n);
+    uint64_t bias = 0;
+    float scale = 1.0f, clamp_min = 0.0f, clamp_max = 0.0f;
+    if (bias_off) {
+        bias = rd_u64(ka + bias_off);
+        if (!bias) return set_error(ctx, T0B_ERR_INVALID, "tile_dispatch: the epilogue has BiasAdd but the bias pointer is null");
+    }
+    auto rd_f32 = [&](size_t off) { uint32_t u = rd_u32(ka + off); float f; std::memcpy(&f, &u, 4); return f; };
+    if (scale_off) scale = rd_f32(scale_off);
+    if (clamp_off) { clamp_min = rd_f32(clamp_off); clamp_max = rd_f32(clamp_off + 4); }
+
+    std::lock_guard<std::recursive_mutex> lk(ctx->mu);
+    // The spec's tile becomes a B200 tile the same way a GemmConfig's does (resolve_plan).
+    t0b_gemm_config cfg{};
+    cfg.tile_m = spec->tile_m; cfg.tile_n = spec->tile_n; cfg.tile_k = spec->tile_k;
+    cfg.wg_size = t0b_tile_wg_size(spec); cfg.use_lds = 1; cfg.double_buffer = spec->double_buffer;
+    cfg.split_k = spec->split_k > 1 ? spec->split_k : 0; cfg.n_col_passes = 1; cfg.swap_grid = spec->swap_grid;
+    cfg.wgp_mode = spec->wgp_mode;
+    GemmCall g{};
+    g.cfg = &cfg; g.trans_a = 0; g.trans_b = spec->transpose == T0B_TILE_NT; g.a = x; g.b = wt; g.c_dst[0] = y; g.n_dst = 1;
+    g.m = m; g.n = n; g.k = k; g.lda = k; g.ldb = spec->transpose == T0B_TILE_NT ? k : n; g.ldc = n;
+    g.out_bf16 = 0;
+    rc = make_chain(ctx, spec->epilogue, static_cast<int32_t>(spec->n_epilogue), bias, scale, clamp_min, clamp_max, &g.epi);
+    if (rc != T0B_OK) return rc;
+    rc = run_gemm(ctx, g);
+    if (rc != T0B_OK) return rc;
+    return finish(ctx, async, "t0b_tile_dispatch", 0);
+}
+
 int32_t t0b_gemm_time(t0b_ctx* ctx, const t0b_gemm_config* cfg, int32_t trans_a, int32_t trans_b, uint64_t a, uint64_t b,
                       uint64_t c, uint32_t m, uint32_t n, uint32_t k, uint64_t lda, uint64_t ldb, uint64_t ldc,
                       int32_t out_dtype, int32_t warmup, int32_t iters, float* ms) {

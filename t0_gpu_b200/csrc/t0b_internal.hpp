@@ -85,5 +85,8 @@ struct PlanInput {
     int num_sms;
 };
 void resolve_plan(const t0b_gemm_config* cfg, const PlanInput& in, t0b_gemm_plan* out);
+// tile_ir front end (t0b_tile_ir.cpp): spec validation and the offsets of the epilogue arguments in its kernarg blob.
+bool tile_spec_valid(const t0b_tile_gemm* spec);
+size_t tile_kernarg_layout(const t0b_tile_gemm* spec, size_t* bias_off, size_t* scale_off, size_t* clamp_off);
 
 }  // namespace t0b

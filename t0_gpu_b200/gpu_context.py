@@ -182,15 +182,33 @@ class GpuRuntime:
         self._check(lib().t0b_splitk_reduce(self._ctx, _addr(partial), split_k, m, n, m * n, n, _addr(c), n, out_dtype,
                                             epilogue, _addr(bias), 1.0, int(async_)))
 
-    def dispatch(self, cfg: GemmConfig, grid, kernargs: bytes) -> None:
-        """`GpuRuntime::dispatch(kernel, grid, kernargs)` for GEMM kernels: synchronous (gpu_context.rs:264-288)."""
-        self._dispatch(cfg, grid, kernargs, False)
+    def ensure_kernel_t0(self, name: str, build, workgroup_size=None, lds_size: int = 0):
+        """`GpuRuntime::ensure_kernel_t0(name, || build(), wg, lds)` (gpu_context.rs:196-262): build once per name and
+        keep the kernel for the life of the runtime.  `build` returns a `T0Kernel` (gemm_gen::generate) or a
+        `TileKernel` (tile_ir::lower_gemm); workgroup size and LDS size are accepted and not needed here."""
+        cache = self.__dict__.setdefault("_kernels", {})
+        if name not in cache:
+            cache[name] = build()
+        return cache[name]
 
-    def dispatch_async(self, cfg: GemmConfig, grid, kernargs: bytes) -> None:
-        self._dispatch(cfg, grid, kernargs, True)
+    def dispatch(self, kernel, grid, kernargs: bytes) -> None:
+        """`GpuRuntime::dispatch(kernel, grid, kernargs)`: synchronous (gpu_context.rs:264-288).  `kernel` is a
+        GemmConfig / T0Kernel / GpuKernel (40/44/48-byte gemm_gen blobs) or a tile_ir TileKernel / TileGemm."""
+        self._dispatch(kernel, grid, kernargs, False)
 
-    def _dispatch(self, cfg, grid, kernargs, async_):
+    def dispatch_async(self, kernel, grid, kernargs: bytes) -> None:
+        self._dispatch(kernel, grid, kernargs, True)
+
+    def _dispatch(self, kernel, grid, kernargs, async_):
         blob = (C.c_uint8 * len(kernargs)).from_buffer_copy(kernargs)
+        spec = getattr(kernel, "spec", None)
+        if spec is None and hasattr(kernel, "acc_swap"):
+            spec = kernel
+        if spec is not None:
+            g = (C.c_uint32 * 3)(grid[0], grid[1], grid[2] if len(grid) > 2 else 1)
+            self._check(lib().t0b_tile_dispatch(self._ctx, C.byref(spec.to_c()), g, blob, len(kernargs), int(async_)))
+            return
+        cfg = getattr(kernel, "cfg", kernel)
         self._check(lib().t0b_dispatch_kernargs(self._ctx, C.byref(cfg.to_c()), grid[0], grid[1], blob, len(kernargs),
                                                 int(async_)))
 
