@@ -267,6 +267,7 @@ T0B_API int32_t t0b_tune_cache_load(const char* dir, uint32_t m, uint32_t n, uin
                                     float* tflops);
 /* GemmTuner::invalidate / clear (auto_gemm.rs:394-404). */
 T0B_API int32_t t0b_tune_cache_invalidate(const char* dir, uint32_t m, uint32_t n, uint32_t k);
+/* dir NULL = the default directory above; "" = stop consulting the disk cache (the state of a new context). */
 T0B_API int32_t t0b_set_autotune_dir(t0b_ctx* ctx, const char* dir);
 
 /* ------------------------------------------------------------------------------------------------

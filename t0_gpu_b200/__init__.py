@@ -9,4 +9,5 @@ from .gemm_gen import (EpilogueOp, GemmConfig, GemmPlan, GemmTranspose, auto_sel
                        compute_grid_auto, compute_grid_backward_data, compute_grid_backward_weight,
                        compute_grid_split_k, resolve_plan, standard_configs, sweep_configs)
 from . import tile_ir  # noqa: F401
+from .auto_gemm import GemmTuner, GemmTuneResult, auto_gemm, global_tuner  # noqa: F401
 from .gpu_context import OUT_BF16, OUT_F32, GpuBuffer, GpuRuntime, T0Error  # noqa: F401

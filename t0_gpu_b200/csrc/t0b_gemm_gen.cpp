@@ -474,7 +474,7 @@ int32_t t0b_tune_cache_invalidate(const char* dir, uint32_t m, uint32_t n, uint3
 
 int32_t t0b_set_autotune_dir(t0b_ctx* ctx, const char* dir) {
     if (!ctx) return T0B_ERR_INVALID;
-    ctx->autotune_dir = tune_dir(dir);
+    ctx->autotune_dir = (dir && !*dir) ? std::string() : tune_dir(dir);
     return T0B_OK;
 }
 

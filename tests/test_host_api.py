@@ -202,3 +202,47 @@ def test_autotune_cache_roundtrip(tmp_path):
     # invalidate removes the entry; loading a missing entry fails
     assert L.t0b_tune_cache_invalidate(d, 4096, 4096, 4096) == 0
     assert L.t0b_tune_cache_load(d, 4096, 4096, 4096, C.byref(out), C.byref(tf)) != 0
+
+
+def test_gemm_tuner_bookkeeping(tmp_path, capsys):
+    """GemmTuner's cache layers without a device (src/t0/auto_gemm.rs:325-417, test :581-610): a result saved in the
+    reference's JSON format is found by a fresh tuner as a `from_cache` entry, `invalidate` removes the memory and
+    the disk entry, `clear` removes the directory."""
+    from t0_gpu_b200.auto_gemm import GemmTuner, global_tuner
+
+    class FakeRuntime:                      # stands where the device would measure
+        handle = None
+        measured = 0
+
+        def _check(self, rc):
+            pass
+
+        def tune(self, m, n, k):
+            FakeRuntime.measured += 1
+            return GemmConfig.preset("b200_256x256"), 1234.5
+
+    d = tmp_path / "tuner"
+    tuner = GemmTuner.with_cache_dir(str(d))
+    assert tuner.max_candidates == 8 and tuner.n_iters == 5 and tuner.cache == {}
+    assert tuner.cache_path(4096, 1024, 512).endswith("gemm_4096x1024x512.json")
+    assert tuner.load_cache(64, 64, 64) is None
+    cfg = GemmConfig.preset("128x64_k16").with_(split_k=4, swap_grid=False)
+    assert _lib.lib().t0b_tune_cache_save(str(d).encode(), 64, 64, 64, C.byref(cfg.to_c()), 42.25) == 0
+    got = tuner.tune(FakeRuntime(), 64, 64, 64)                      # disk hit
+    assert (got.tile_m, got.tile_n, got.split_k, got.swap_grid) == (128, 64, 4, False)
+    r = tuner.cache[(64, 64, 64)]
+    assert r.from_cache and abs(r.best_tflops - 42.25) < 1e-3 and r.key == (64, 64, 64) and r.all == []
+    n_before = FakeRuntime.measured
+    assert tuner.tune(FakeRuntime(), 64, 64, 64) == got              # memory hit: the runtime is not asked again
+    assert FakeRuntime.measured == n_before
+    best = tuner.tune(FakeRuntime(), 128, 128, 128)                  # miss: measured
+    assert best.tile_m == 256 and not tuner.cache[(128, 128, 128)].from_cache
+    assert tuner.cache[(128, 128, 128)].all == [(best.name(), 1234.5)]
+    tuner.report()
+    text = capsys.readouterr().err
+    assert "2 entries" in text and "[cached]" in text and "[measured]" in text
+    tuner.invalidate(64, 64, 64)
+    assert (64, 64, 64) not in tuner.cache and tuner.load_cache(64, 64, 64) is None
+    tuner.clear()
+    assert tuner.cache == {} and not d.exists()
+    assert global_tuner() is global_tuner()

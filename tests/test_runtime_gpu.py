@@ -119,3 +119,32 @@ def test_cuda_error_poisons_the_context_and_a_new_one_works():
     r2.gemm(ones, ones, c, 64, 64, 64)
     assert np.all(c.read_as(np.float32, 64 * 64) == 64.0)
     r2.close()
+
+
+def test_gemm_tuner_and_auto_gemm(rt, tmp_path, monkeypatch):
+    """GemmTuner::tune + auto_gemm (src/t0/auto_gemm.rs:82-162, 445-480): the first call measures and writes
+    <dir>/gemm_MxNxK.json, a fresh tuner on the same directory answers from the file, and auto_gemm runs the
+    product with the chosen config."""
+    import importlib
+    ag = importlib.import_module("t0_gpu_b200.auto_gemm")      # the package also exports the function of that name
+
+    m, n, k = 512, 384, 256
+    tuner = ag.GemmTuner.with_cache_dir(str(tmp_path / "at"))
+    cfg = tuner.tune(rt, m, n, k)
+    res = tuner.cache[(m, n, k)]
+    assert not res.from_cache and res.best_tflops > 1.0 and res.all[0][0] == cfg.name()
+    assert (tmp_path / "at" / f"gemm_{m}x{n}x{k}.json").exists()
+    again = ag.GemmTuner.with_cache_dir(str(tmp_path / "at"))
+    cfg2 = again.tune(rt, m, n, k)
+    assert again.cache[(m, n, k)].from_cache
+    assert (cfg2.tile_m, cfg2.tile_n, cfg2.split_k, cfg2.swap_grid) == (cfg.tile_m, cfg.tile_n, cfg.split_k, cfg.swap_grid)
+    monkeypatch.setattr(ag, "_GLOBAL", again)
+    A = oracle.rand_bf16(m * k, 31).reshape(m, k)
+    Bt = oracle.rand_bf16(n * k, 32).reshape(n, k)
+    da, db, dc = rt.upload(A), rt.upload(Bt), rt.alloc(m * n * 4)
+    tflops = ag.auto_gemm(rt, da, db, dc, m, n, k)
+    assert abs(tflops - again.cache[(m, n, k)].best_tflops) < 1e-6
+    got = dc.read_as(np.float32, m * n).reshape(m, n)
+    ref = oracle.gemm_bf16(A, Bt, m, n, k, threads=8)
+    assert np.linalg.norm(got - ref) <= 5e-3 * np.linalg.norm(ref)
+    lib().t0b_set_autotune_dir(rt.handle, b"")       # back to the default for the tests that follow
