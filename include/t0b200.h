@@ -151,7 +151,8 @@ T0B_API const char* t0b_last_error(t0b_ctx* ctx);
 /* GpuRuntime::is_poisoned(), gpu_context.rs:149-157. */
 T0B_API int32_t t0b_is_poisoned(t0b_ctx* ctx);
 T0B_API int32_t t0b_num_sms(t0b_ctx* ctx);
-/* Device status word written by kernels whose bounded waits ran out (0 = none). Reading clears it when
+/* Device status word written by kernels whose bounded waits ran out (101..105) or that met an index outside its
+ * table (110); 0 = none.  A synchronous call that finds it set returns T0B_ERR_DEVICE.  Reading clears it when
  * `clear` is non-zero.  Takes the place of the reference's wait_read_ptr timeout (src/kfd/mod.rs:1607-1642). */
 T0B_API int32_t t0b_device_status(t0b_ctx* ctx, int32_t clear);
 /* Limit of every in-kernel wait, in nanoseconds (default 2e9). */
@@ -323,6 +324,22 @@ T0B_API int32_t t0b_residual_add(t0b_ctx* ctx, uint64_t y, uint64_t x, size_t n,
 T0B_API int32_t t0b_adamw_step(t0b_ctx* ctx, uint64_t params, uint64_t grads, uint64_t m, uint64_t v,
                                uint64_t params_bf16, size_t n, float lr, float beta1, float beta2, float eps,
                                float weight_decay, uint32_t t, float grad_scale, int32_t async);
+
+/* Embedding lookup and its gradient (src/t0/embedding_kernels.rs:30-96; Ignis: src/ignis/ops/embedding.rs:25-178).
+ * table f32[vocab, dim], ids u32[num_tokens], out / grad_out f32[num_tokens, dim], any dim.
+ *   fwd: out[t, :] = table[ids[t], :].
+ *   bwd: grad_table[ids[t], :] += grad_out[t, :], rows of one id added in ascending token order (the order of the
+ *        reference's CPU loop, :113-124), so the result is bit-identical to that loop and the same on every run; the
+ *        reference's GPU kernel uses unordered float atomics.  grad_table is accumulated into (zero it first for a
+ *        plain gradient, as the reference's caller does, embedding.rs:112-113).
+ * An id >= vocab touches no memory: its output row is zeros (fwd) / it is skipped (bwd), and the device status word is
+ * set to 110.  The backward sorts the token positions by id; scratch of t0b_embedding_bwd_scratch_bytes(num_tokens)
+ * bytes (256-byte aligned) may be passed, or 0 to take it from the context's pool. */
+T0B_API int32_t t0b_embedding_fwd(t0b_ctx* ctx, uint64_t table, uint64_t ids, uint64_t out, uint32_t num_tokens,
+                                  uint32_t dim, uint32_t vocab, int32_t async);
+T0B_API size_t t0b_embedding_bwd_scratch_bytes(uint32_t num_tokens);
+T0B_API int32_t t0b_embedding_bwd(t0b_ctx* ctx, uint64_t grad_table, uint64_t ids, uint64_t grad_out, uint32_t num_tokens,
+                                  uint32_t dim, uint32_t vocab, uint64_t scratch, size_t scratch_bytes, int32_t async);
 
 /* ------------------------------------------------------------------------------------------------
  * tile_ir front end: TileGemm specs with M/N/K edge handling and an epilogue chain (src/t0/tile_ir.rs).

@@ -63,6 +63,8 @@ def _declare(L: C.CDLL) -> None:
     L.t0o_silu_gate_forward.argtypes = [_P, _P, _P, _SZ]
     L.t0o_silu_gate_backward.argtypes = [_P, _P, _P, _P, _P, _SZ]
     L.t0o_residual_add.argtypes = [_P, _P, _SZ]
+    L.t0o_embedding_forward.argtypes = [_P, _P, _P, _SZ, _SZ]
+    L.t0o_embedding_backward.argtypes = [_P, _P, _P, _SZ, _SZ]
     L.t0o_adamw_step.argtypes = [_P, _P, _P, _P, _SZ, C.c_float, C.c_float, C.c_float, C.c_float, C.c_float, C.c_uint32]
 
 
@@ -282,6 +284,23 @@ def residual_add(y, x) -> np.ndarray:
     x = _f32(x)
     lib().t0o_residual_add(_ptr(y), _ptr(x), y.size)
     return y
+
+
+def embedding_forward(table, indices, dim: int) -> np.ndarray:
+    table = _f32(table)
+    idx = np.ascontiguousarray(indices, dtype=np.uint32)
+    out = np.empty((idx.size, dim), np.float32)
+    lib().t0o_embedding_forward(_ptr(table), _ptr(idx), _ptr(out), idx.size, dim)
+    return out
+
+
+def embedding_backward(grad_table, indices, grad_output, dim: int) -> np.ndarray:
+    """Returns grad_table + the scattered rows of grad_output (tokens added in ascending order)."""
+    gt = _f32(grad_table).copy()
+    idx = np.ascontiguousarray(indices, dtype=np.uint32)
+    go = _f32(grad_output)
+    lib().t0o_embedding_backward(_ptr(gt), _ptr(idx), _ptr(go), idx.size, dim)
+    return gt
 
 
 def adamw_step(params, grads, m, v, lr, beta1, beta2, eps, weight_decay, t):

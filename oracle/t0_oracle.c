@@ -372,6 +372,25 @@ T0O_API void t0o_residual_add(float *y, const float *x, size_t n) {
     for (size_t i = 0; i < n; ++i) y[i] = y[i] + x[i];
 }
 
+/* Embedding lookup: output[t, :] = table[indices[t], :].  src/t0/embedding_kernels.rs:100-110. */
+T0O_API void t0o_embedding_forward(const float *table, const uint32_t *indices, float *output, size_t num_tokens,
+                                   size_t dim) {
+    for (size_t t = 0; t < num_tokens; ++t) {
+        size_t idx = indices[t];
+        for (size_t d = 0; d < dim; ++d) output[t * dim + d] = table[idx * dim + d];
+    }
+}
+
+/* Embedding gradient: grad_table[indices[t], :] += grad_output[t, :], tokens in ascending order.
+ * src/t0/embedding_kernels.rs:113-124. */
+T0O_API void t0o_embedding_backward(float *grad_table, const uint32_t *indices, const float *grad_output,
+                                    size_t num_tokens, size_t dim) {
+    for (size_t t = 0; t < num_tokens; ++t) {
+        size_t idx = indices[t];
+        for (size_t d = 0; d < dim; ++d) grad_table[idx * dim + d] = grad_table[idx * dim + d] + grad_output[t * dim + d];
+    }
+}
+
 /* Fused AdamW step.  src/t0/adamw_kernels.rs:105-119. */
 T0O_API void t0o_adamw_step(float *params, const float *grads, float *m, float *v, size_t n, float lr, float beta1,
                             float beta2, float eps, float weight_decay, uint32_t t) {

@@ -90,6 +90,9 @@ SIGNATURES = {
     "t0b_gemm_slabs": (_i32, [_ctx, _cfgp, _u64, _u64, _u64, _u32, _u32, _u32, _u32, _i32]),
     "t0b_splitk_reduce": (_i32, [_ctx, _u64, _u32, _u32, _u32, _u64, _u64, _u64, _u64, _i32, _i32, _u64, _f, _i32]),
     "t0b_dispatch_kernargs": (_i32, [_ctx, _cfgp, _u32, _u32, _u8p, _sz, _i32]),
+    "t0b_embedding_fwd": (_i32, [_ctx, _u64, _u64, _u64, _u32, _u32, _u32, _i32]),
+    "t0b_embedding_bwd_scratch_bytes": (_sz, [_u32]),
+    "t0b_embedding_bwd": (_i32, [_ctx, _u64, _u64, _u64, _u32, _u32, _u32, _u64, _sz, _i32]),
     "t0b_tile_preset": (_i32, [C.c_char_p, C.POINTER(TileGemmC)]),
     "t0b_tile_name": (_i32, [C.POINTER(TileGemmC), C.c_char_p, _sz]),
     "t0b_tile_wg_size": (_u32, [C.POINTER(TileGemmC)]),

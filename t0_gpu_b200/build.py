@@ -16,8 +16,10 @@ OUT_DIR = os.path.join(HERE, "lib")
 OUT = os.path.join(OUT_DIR, "libt0b200.so")
 OBJ_DIR = os.path.join(OUT_DIR, "obj")
 
-SOURCES = ["t0b_runtime.cu", "t0b_gemm.cu", "t0b_rowops.cu", "t0b_gemm_gen.cpp", "t0b_tile_ir.cpp"]
-HEADERS = ["gemm_sm100.cuh", "ptx_sm100.cuh", "t0b_internal.hpp", os.path.join("..", "..", "include", "t0b200.h")]
+SOURCES = ["t0b_runtime.cu", "t0b_gemm.cu", "t0b_rowops.cu", "t0b_embedding.cu", "t0b_gemm_gen.cpp", "t0b_tile_ir.cpp"]
+# The GEMM kernel variants (BN, CG, MT, ND): gemm_variant.cu compiled once per entry, side by side.
+GEMM_VARIANTS = ["256,2,2,1", "256,2,2,0", "256,2,1,0", "128,2,1,0", "256,1,1,0", "128,1,1,0", "64,1,1,0"]
+HEADERS = ["gemm_sm100.cuh", "gemm_launch.cuh", "ptx_sm100.cuh", "t0b_internal.hpp", os.path.join("..", "..", "include", "t0b200.h")]
 
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
@@ -29,23 +31,35 @@ def _newest(paths) -> float:
 
 
 def build(force: bool = False, verbose: bool = False) -> str:
+    # Up to date already (e.g. a built library shipped without its object files): nothing to do.
+    all_inputs = [os.path.join(CSRC, f) for f in SOURCES + HEADERS + ["gemm_variant.cu"]]
+    if not force and os.path.exists(OUT) and os.path.getmtime(OUT) >= _newest(all_inputs):
+        return OUT
     os.makedirs(OBJ_DIR, exist_ok=True)
     hdr_time = _newest([os.path.join(CSRC, h) for h in HEADERS])
-    objs = []
-    for src in SOURCES:
+    objs, jobs = [], []
+    units = [(src, os.path.splitext(src)[0] + ".o", []) for src in SOURCES]
+    units += [("gemm_variant.cu", "gemm_variant_" + v.replace(",", "_") + ".o", ["-DT0B_V_%s=%s" % (k, x) for k, x in zip(("BN", "CG", "MT", "ND"), v.split(","))])
+              for v in GEMM_VARIANTS]
+    for src, obj_name, defines in units:
         sp = os.path.join(CSRC, src)
-        obj = os.path.join(OBJ_DIR, os.path.splitext(src)[0] + ".o")
+        obj = os.path.join(OBJ_DIR, obj_name)
         objs.append(obj)
         stale = force or not os.path.exists(obj) or os.path.getmtime(obj) < max(os.path.getmtime(sp), hdr_time)
         if stale:
-            cmd = [NVCC, *ARCH, *CFLAGS, "-c", sp, "-o", obj]
+            cmd = [NVCC, *ARCH, *CFLAGS, *defines, "-c", sp, "-o", obj]
             if src.endswith(".cpp"):
                 cmd.insert(1, "-x")
                 cmd.insert(2, "cu")
             if verbose:
                 cmd += ["-Xptxas", "-v"]
                 print(" ".join(cmd), flush=True)
-            subprocess.run(cmd, check=True)
+            jobs.append(cmd)
+    # The translation units are independent: compile them side by side.
+    procs = [subprocess.Popen(cmd) for cmd in jobs]
+    failed = [cmd for cmd, p in zip(jobs, procs) if p.wait() != 0]
+    if failed:
+        raise subprocess.CalledProcessError(1, failed[0])
     if force or not os.path.exists(OUT) or os.path.getmtime(OUT) < _newest(objs):
         cmd = [NVCC, *ARCH, "-shared", "-o", OUT, *objs, "-cudart", "static"]
         if verbose:

@@ -671,6 +671,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
     }
 }
 
+// The kernels below are not templates: they are compiled in the dispatch file only, not once per tile variant.
+#ifndef T0B_VARIANT
 // ---------------------------------------------------------------------------------------------------------
 // Deterministic split-K reduce: out[i] = epilogue(sum over s = 0..sk-1, in that order, of slab_s[i]),
 // starting from +0.0 -- the order of the reference's host-side slab sum
@@ -793,4 +795,5 @@ __global__ void bounded_wait_selftest_kernel(int* status, unsigned long long lim
     }
 }
 
+#endif  // T0B_VARIANT
 }  // namespace t0b

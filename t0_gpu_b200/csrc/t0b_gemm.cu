@@ -8,7 +8,7 @@
 #include <cstring>
 #include <vector>
 
-#include "gemm_sm100.cuh"
+#include "gemm_launch.cuh"
 #include "t0b_internal.hpp"
 
 using namespace t0b;
@@ -60,61 +60,6 @@ int32_t get_tmap(t0b_ctx* ctx, uint64_t ptr, uint64_t d0, uint64_t d1, uint64_t 
     if (ctx->tmaps.size() > 8192) ctx->tmaps.clear();
     ctx->tmaps.emplace(key, *out);
     return T0B_OK;
-}
-
-template <int BN, int CG, int MT, int ND = 0>
-int32_t launch_variant(t0b_ctx* ctx, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc,
-                       const GemmParams& p, int num_work) {
-    using T = GemmTraits<BN, CG, MT, ND>;
-    auto kfn = gemm_bf16_tcgen05_kernel<BN, CG, MT, ND>;
-    static bool configured[64] = {};
-    static int max_clusters[64] = {};
-    const int dev = ctx->device & 63;
-    if (!configured[dev]) {
-        int32_t rc = check_cuda(ctx, cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, T::kSmemBytes),
-                                "cudaFuncSetAttribute(smem)");
-        if (rc != T0B_OK) return rc;
-        if (CG == 2) {
-            rc = check_cuda(ctx, cudaFuncSetAttribute(kfn, cudaFuncAttributeNonPortableClusterSizeAllowed, 0),
-                            "cudaFuncSetAttribute(cluster)");
-            if (rc != T0B_OK) return rc;
-            cudaLaunchConfig_t qc{};
-            qc.gridDim = dim3(ctx->num_sms - (ctx->num_sms % 2), 1, 1);
-            qc.blockDim = dim3(T::kThreads, 1, 1);
-            qc.dynamicSmemBytes = T::kSmemBytes;
-            cudaLaunchAttribute qa[1];
-            qa[0].id = cudaLaunchAttributeClusterDimension;
-            qa[0].val.clusterDim.x = 2;
-            qa[0].val.clusterDim.y = 1;
-            qa[0].val.clusterDim.z = 1;
-            qc.attrs = qa;
-            qc.numAttrs = 1;
-            int nc = 0;
-            cudaError_t e = cudaOccupancyMaxActiveClusters(&nc, kfn, &qc);
-            if (e != cudaSuccess || nc <= 0) {
-                cudaGetLastError();
-                nc = ctx->num_sms / 2;
-            }
-            max_clusters[dev] = nc;
-        } else {
-            max_clusters[dev] = ctx->num_sms;
-        }
-        configured[dev] = true;
-    }
-    const int clusters = std::max(1, std::min(num_work, max_clusters[dev]));
-    cudaLaunchConfig_t cfg{};
-    cfg.gridDim = dim3(clusters * CG, 1, 1);
-    cfg.blockDim = dim3(T::kThreads, 1, 1);
-    cfg.dynamicSmemBytes = T::kSmemBytes;
-    cfg.stream = ctx->stream;
-    cudaLaunchAttribute attrs[1];
-    attrs[0].id = cudaLaunchAttributeClusterDimension;
-    attrs[0].val.clusterDim.x = CG;
-    attrs[0].val.clusterDim.y = 1;
-    attrs[0].val.clusterDim.z = 1;
-    cfg.attrs = attrs;
-    cfg.numAttrs = 1;
-    return check_cuda(ctx, cudaLaunchKernelEx(&cfg, kfn, ta, tb, tc, p), "cudaLaunchKernelEx(gemm)");
 }
 
 struct GemmCall {

@@ -70,6 +70,9 @@ namespace t0b {
 
 int32_t set_error(t0b_ctx* ctx, int32_t code, const char* fmt, ...);
 int32_t check_cuda(t0b_ctx* ctx, cudaError_t e, const char* what);
+// Status-word code of a kernel that met an index outside its table (the access is skipped); 101..105 are the GEMM's
+// bounded waits.
+constexpr int kDevBadIndex = 110;
 int32_t precheck(t0b_ctx* ctx);                 // null / poisoned checks, sets the device
 // Launch-error check (+ sync and status-word check when !async). `count` kernels are added to the launch counter.
 int32_t finish(t0b_ctx* ctx, int32_t async, const char* what, int count = 1);

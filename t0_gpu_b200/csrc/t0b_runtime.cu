@@ -49,7 +49,7 @@ int32_t finish(t0b_ctx* ctx, int32_t async, const char* what, int count) {
     e = cudaStreamSynchronize(ctx->stream);
     if (e != cudaSuccess) return check_cuda(ctx, e, what);
     const int st = *reinterpret_cast<volatile int*>(ctx->status_host);
-    if (st != 0) return set_error(ctx, T0B_ERR_DEVICE, "%s: device status %d (a bounded in-kernel wait ran out)", what, st);
+    if (st != 0) return set_error(ctx, T0B_ERR_DEVICE, "%s: device status %d (101-105: a bounded in-kernel wait ran out; 110: an index outside its table)", what, st);
     return T0B_OK;
 }
 
@@ -271,7 +271,7 @@ int32_t t0b_sync(t0b_ctx* ctx) {
     rc = check_cuda(ctx, cudaStreamSynchronize(ctx->stream), "cudaStreamSynchronize");
     if (rc != T0B_OK) return rc;
     const int st = *reinterpret_cast<volatile int*>(ctx->status_host);
-    if (st != 0) return set_error(ctx, T0B_ERR_DEVICE, "device status %d (a bounded in-kernel wait ran out)", st);
+    if (st != 0) return set_error(ctx, T0B_ERR_DEVICE, "device status %d (101-105: a bounded in-kernel wait ran out; 110: an index outside its table)", st);
     return T0B_OK;
 }
 

@@ -98,3 +98,20 @@ def cross_entropy(rt: GpuRuntime, logits: GpuBuffer, targets: GpuBuffer, batch: 
     loss = float(losses.read_as(np.float32, batch).mean())
     rt.recycle(losses)
     return loss, grad
+
+
+def embedding_forward(rt: GpuRuntime, table: GpuBuffer, ids: GpuBuffer, seq_len: int, dim: int, vocab_size: int):
+    """`ops::embedding::embedding_forward(table, ids_buf, seq_len, dim, runtime)` (embedding.rs:25-178): gathers
+    table rows; returns (out, backward) where backward(grad_out) -> grad_table, a zeroed [vocab, dim] buffer with the
+    rows of grad_out added in token order (the reference's scatter uses unordered atomics)."""
+    L = lib()
+    out = rt.alloc(max(seq_len * dim * 4, 16))
+    rt._check(L.t0b_embedding_fwd(rt.handle, table.gpu_addr(), ids.gpu_addr(), out.gpu_addr(), seq_len, dim, vocab_size, 0))
+
+    def backward(grad_out: GpuBuffer) -> GpuBuffer:
+        grad_table = rt.alloc_zero(max(vocab_size * dim * 4, 16))
+        rt._check(L.t0b_embedding_bwd(rt.handle, grad_table.gpu_addr(), ids.gpu_addr(), grad_out.gpu_addr(), seq_len, dim,
+                                      vocab_size, 0, 0, 0))
+        return grad_table
+
+    return out, backward

@@ -199,3 +199,13 @@ def test_silu_and_adamw_against_float64():
     # step 1: m_hat = grad, v_hat = grad^2 -> update = lr * sign(grad) (approximately)
     want = p * (1 - 1e-3 * 0.01) - 1e-3 * grad / (np.abs(grad) + 1e-8)
     assert np.allclose(p2, want, rtol=1e-4, atol=1e-6)
+
+
+def test_embedding_known_answers():
+    """src/t0/embedding_kernels.rs:137-165: the reference's two CPU known-answer tests."""
+    table = np.arange(1, 10, dtype=np.float32).reshape(3, 3)
+    out = oracle.embedding_forward(table, [2, 0, 1], 3)
+    assert np.array_equal(out, np.array([[7, 8, 9], [1, 2, 3], [4, 5, 6]], np.float32))
+    grad_out = np.array([[1, 1, 1], [2, 2, 2], [3, 3, 3]], np.float32)
+    gt = oracle.embedding_backward(np.zeros((2, 3), np.float32), [1, 0, 1], grad_out, 3)
+    assert np.array_equal(gt, np.array([[2, 2, 2], [4, 4, 4]], np.float32))      # row 0 = token 1, row 1 = tokens 0 + 2
