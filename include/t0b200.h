@@ -325,6 +325,24 @@ T0B_API int32_t t0b_adamw_step(t0b_ctx* ctx, uint64_t params, uint64_t grads, ui
                                uint64_t params_bf16, size_t n, float lr, float beta1, float beta2, float eps,
                                float weight_decay, uint32_t t, float grad_scale, int32_t async);
 
+/* Fusions of the memory-bound steps between two GEMMs of the MLP (no single reference counterpart: the reference runs
+ * each step as its own kernel, and lists such fusions as EpilogueOp chains, src/t0/tile_ir.rs:2213-2339).  Each gives
+ * the same values as the sequence of calls it replaces, with the intermediate f32 arrays never written to memory.
+ *   t0b_softmax_ce_bf16  = t0b_softmax_ce, then t0b_cast_f32_to_bf16 of the gradient (the operand of the dW and
+ *                          dX GEMMs): dlogits is bf16[rows, ld].
+ *   t0b_rmsnorm_silu_fwd = t0b_rmsnorm_fwd, t0b_silu_gate_fwd (no up operand), t0b_cast_f32_to_bf16:
+ *                          out_bf16[rows, cols] = bf16(silu(rmsnorm(x))); inv_rms f32[rows] optional.
+ *   t0b_rmsnorm_silu_bwd = t0b_silu_gate_bwd on the recomputed rmsnorm(x), t0b_rmsnorm_bwd, t0b_cast_f32_to_bf16:
+ *                          dh f32 is the gradient of the SiLU output; dx_bf16 = bf16(d loss / d x); dgamma f32[cols]
+ *                          optional, with scratch as for t0b_rmsnorm_bwd. */
+T0B_API int32_t t0b_softmax_ce_bf16(t0b_ctx* ctx, uint64_t logits, uint64_t targets, uint64_t losses, uint64_t dlogits_bf16,
+                                    uint32_t rows, uint32_t cols, uint64_t ld, float scale, int32_t async);
+T0B_API int32_t t0b_rmsnorm_silu_fwd(t0b_ctx* ctx, uint64_t x, uint64_t weight, uint64_t out_bf16, uint64_t inv_rms,
+                                     uint32_t rows, uint32_t cols, float eps, int32_t async);
+T0B_API int32_t t0b_rmsnorm_silu_bwd(t0b_ctx* ctx, uint64_t dh, uint64_t x, uint64_t weight, uint64_t dx_bf16, uint64_t dgamma,
+                                     uint64_t scratch, size_t scratch_bytes, uint32_t rows, uint32_t cols, float eps,
+                                     int32_t async);
+
 /* Embedding lookup and its gradient (src/t0/embedding_kernels.rs:30-96; Ignis: src/ignis/ops/embedding.rs:25-178).
  * table f32[vocab, dim], ids u32[num_tokens], out / grad_out f32[num_tokens, dim], any dim.
  *   fwd: out[t, :] = table[ids[t], :].

@@ -90,6 +90,9 @@ SIGNATURES = {
     "t0b_gemm_slabs": (_i32, [_ctx, _cfgp, _u64, _u64, _u64, _u32, _u32, _u32, _u32, _i32]),
     "t0b_splitk_reduce": (_i32, [_ctx, _u64, _u32, _u32, _u32, _u64, _u64, _u64, _u64, _i32, _i32, _u64, _f, _i32]),
     "t0b_dispatch_kernargs": (_i32, [_ctx, _cfgp, _u32, _u32, _u8p, _sz, _i32]),
+    "t0b_softmax_ce_bf16": (_i32, [_ctx, _u64, _u64, _u64, _u64, _u32, _u32, _u64, _f, _i32]),
+    "t0b_rmsnorm_silu_fwd": (_i32, [_ctx, _u64, _u64, _u64, _u64, _u32, _u32, _f, _i32]),
+    "t0b_rmsnorm_silu_bwd": (_i32, [_ctx, _u64, _u64, _u64, _u64, _u64, _u64, _sz, _u32, _u32, _f, _i32]),
     "t0b_embedding_fwd": (_i32, [_ctx, _u64, _u64, _u64, _u32, _u32, _u32, _i32]),
     "t0b_embedding_bwd_scratch_bytes": (_sz, [_u32]),
     "t0b_embedding_bwd": (_i32, [_ctx, _u64, _u64, _u64, _u32, _u32, _u32, _u64, _sz, _i32]),

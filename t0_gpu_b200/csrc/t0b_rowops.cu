@@ -150,11 +150,29 @@ __global__ void __launch_bounds__(kRowThreads) rmsnorm_fwd_kernel(const float* _
     }
 }
 
+__device__ __forceinline__ float sigmoidf_(float g) { return 1.0f / (1.0f + expf(-g)); }
+
+__device__ __forceinline__ void silu_bwd_one(float gr, float g, float u, float& dgate, float& dup) {
+    const float sig = sigmoidf_(g);
+    dup = gr * g * sig;
+    dgate = gr * u * sig * (1.0f + g * (1.0f - sig));
+}
+
+__device__ __forceinline__ uint2 pack_bf16x4(float a, float b, float c, float d) {
+    __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+    uint2 o;
+    o.x = *reinterpret_cast<uint32_t*>(&lo);
+    o.y = *reinterpret_cast<uint32_t*>(&hi);
+    return o;
+}
+
 // Register-resident forward for rows of up to 4 * VPT * blockDim.x columns: CTAs walk rows with a grid stride,
 // the weight stays in registers for all of them and each row's x is read exactly once.
-template <int VPT>
+// SILU16: the row is passed through SiLU and stored as bf16 (the input of the next GEMM) -- the values the
+// three-kernel sequence RMSNorm, SiLU, f32->bf16 cast would store, without the two f32 round trips through HBM.
+template <int VPT, bool SILU16 = false>
 __global__ void __launch_bounds__(kRowThreads) rmsnorm_fwd_reg_kernel(const float* __restrict__ x, const float* __restrict__ w,
-                                                                      float* __restrict__ y, float* __restrict__ inv_rms,
+                                                                      void* __restrict__ y, float* __restrict__ inv_rms,
                                                                       uint32_t rows, uint32_t cols, float eps) {
     __shared__ float red[64];
     const uint32_t n4 = cols / 4;
@@ -166,7 +184,8 @@ __global__ void __launch_bounds__(kRowThreads) rmsnorm_fwd_reg_kernel(const floa
     }
     for (uint32_t row = blockIdx.x; row < rows; row += gridDim.x) {
         const float4* xr = reinterpret_cast<const float4*>(x + static_cast<size_t>(row) * cols);
-        float4* yr = reinterpret_cast<float4*>(y + static_cast<size_t>(row) * cols);
+        float4* yr = reinterpret_cast<float4*>(static_cast<float*>(y) + static_cast<size_t>(row) * cols);
+        uint2* yh = reinterpret_cast<uint2*>(static_cast<__nv_bfloat16*>(y) + static_cast<size_t>(row) * cols);
         float4 xv[VPT];
         float ss = 0.0f, unused = 0.0f;
 #pragma unroll
@@ -181,9 +200,11 @@ __global__ void __launch_bounds__(kRowThreads) rmsnorm_fwd_reg_kernel(const floa
 #pragma unroll
         for (int j = 0; j < VPT; ++j) {
             const uint32_t i = threadIdx.x + j * blockDim.x;
-            if (i < n4)
-                yr[i] = make_float4(xv[j].x * rstd * wv[j].x, xv[j].y * rstd * wv[j].y, xv[j].z * rstd * wv[j].z,
-                                    xv[j].w * rstd * wv[j].w);
+            if (i >= n4) continue;
+            const float4 r = make_float4(xv[j].x * rstd * wv[j].x, xv[j].y * rstd * wv[j].y, xv[j].z * rstd * wv[j].z,
+                                         xv[j].w * rstd * wv[j].w);
+            if (SILU16) yh[i] = pack_bf16x4(r.x * sigmoidf_(r.x), r.y * sigmoidf_(r.y), r.z * sigmoidf_(r.z), r.w * sigmoidf_(r.w));
+            else yr[i] = r;
         }
     }
 }
@@ -250,15 +271,28 @@ __global__ void __launch_bounds__(256) rmsnorm_dgamma_partial_kernel(const float
     }
     partial[static_cast<size_t>(blockIdx.y) * cols + c] = acc;
 }
-// dgamma stage 2: sum the row-block partials in block order.
+// dgamma stage 2: sum the row-block partials in a fixed order.  A block owns 32 columns; its 8 warps each add every
+// 8th partial row (ascending), then warp 0 adds the 8 sums in warp order.  Launch with kDgammaFinalGrid(cols) blocks.
 __global__ void __launch_bounds__(256) rmsnorm_dgamma_final_kernel(const float* __restrict__ partial, float* __restrict__ dgamma,
                                                                    uint32_t cols, uint32_t nblocks) {
-    const uint32_t c = blockIdx.x * 256 + threadIdx.x;
-    if (c >= cols) return;
+    __shared__ float part[8][32];
+    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const uint32_t c = blockIdx.x * 32 + lane;
     float acc = 0.0f;
-    for (uint32_t b = 0; b < nblocks; ++b) acc += partial[static_cast<size_t>(b) * cols + c];
-    dgamma[c] = acc;
+    if (c < cols) {
+#pragma unroll 4
+        for (uint32_t b = warp; b < nblocks; b += 8) acc += partial[static_cast<size_t>(b) * cols + c];
+    }
+    part[warp][lane] = acc;
+    __syncthreads();
+    if (warp == 0 && c < cols) {
+        float total = part[0][lane];
+#pragma unroll
+        for (int w = 1; w < 8; ++w) total += part[w][lane];
+        dgamma[c] = total;
+    }
 }
+inline uint32_t kDgammaFinalGrid(uint32_t cols) { return (cols + 31) / 32; }
 
 constexpr uint32_t kDgammaRowBlocks = 64;
 
@@ -266,9 +300,11 @@ constexpr uint32_t kDgammaRowBlocks = 64;
 // dy in registers between the reduction sweep and the dx sweep (one HBM read of each), and accumulates its share of
 // dgamma[c] = sum_r dy*x*rstd in registers; per-CTA partials are then summed in CTA order by
 // rmsnorm_dgamma_final_kernel.  Every thread owns VPT float4 column groups: cols <= 4 * VPT * blockDim.x.
-template <int VPT>
+// SILU16: dy is the gradient of SiLU(RMSNorm(x)); the normalised row is recomputed from x, the SiLU derivative is
+// applied in registers and dx is stored as bf16 -- the values of the sequence SiLU backward, RMSNorm backward, cast.
+template <int VPT, bool SILU16 = false>
 __global__ void __launch_bounds__(kRowThreads) rmsnorm_bwd_fused_kernel(const float* __restrict__ dy, const float* __restrict__ x,
-                                                                        const float* __restrict__ w, float* __restrict__ dx,
+                                                                        const float* __restrict__ w, void* __restrict__ dx,
                                                                         float* __restrict__ partial, uint32_t rows,
                                                                         uint32_t cols, float eps) {
     __shared__ float red[64];
@@ -296,12 +332,32 @@ __global__ void __launch_bounds__(kRowThreads) rmsnorm_bwd_fused_kernel(const fl
                 dv[j] = make_float4(0.f, 0.f, 0.f, 0.f);
             }
             ss += xv[j].x * xv[j].x + xv[j].y * xv[j].y + xv[j].z * xv[j].z + xv[j].w * xv[j].w;
-            dot += xv[j].x * dv[j].x * wv[j].x + xv[j].y * dv[j].y * wv[j].y + xv[j].z * dv[j].z * wv[j].z + xv[j].w * dv[j].w * wv[j].w;
+            if (!SILU16)
+                dot += xv[j].x * dv[j].x * wv[j].x + xv[j].y * dv[j].y * wv[j].y + xv[j].z * dv[j].z * wv[j].z + xv[j].w * dv[j].w * wv[j].w;
         }
-        block_sum2(ss, dot, red);
-        const float rstd = 1.0f / sqrtf(ss / static_cast<float>(cols) + eps);
+        float rstd;
+        if (SILU16) {
+            float unused = 0.0f;
+            block_sum2(ss, unused, red);
+            rstd = 1.0f / sqrtf(ss / static_cast<float>(cols) + eps);
+#pragma unroll
+            for (int j = 0; j < VPT; ++j) {
+                float du;
+                silu_bwd_one(dv[j].x, xv[j].x * rstd * wv[j].x, 1.0f, dv[j].x, du);
+                silu_bwd_one(dv[j].y, xv[j].y * rstd * wv[j].y, 1.0f, dv[j].y, du);
+                silu_bwd_one(dv[j].z, xv[j].z * rstd * wv[j].z, 1.0f, dv[j].z, du);
+                silu_bwd_one(dv[j].w, xv[j].w * rstd * wv[j].w, 1.0f, dv[j].w, du);
+                dot += xv[j].x * dv[j].x * wv[j].x + xv[j].y * dv[j].y * wv[j].y + xv[j].z * dv[j].z * wv[j].z + xv[j].w * dv[j].w * wv[j].w;
+            }
+            unused = 0.0f;
+            block_sum2(dot, unused, red);
+        } else {
+            block_sum2(ss, dot, red);
+            rstd = 1.0f / sqrtf(ss / static_cast<float>(cols) + eps);
+        }
         const float coef = rstd * rstd * (dot / static_cast<float>(cols));
-        float4* dxr = dx ? reinterpret_cast<float4*>(dx + static_cast<size_t>(row) * cols) : nullptr;
+        float4* dxr = (dx && !SILU16) ? reinterpret_cast<float4*>(static_cast<float*>(dx) + static_cast<size_t>(row) * cols) : nullptr;
+        uint2* dxh = (dx && SILU16) ? reinterpret_cast<uint2*>(static_cast<__nv_bfloat16*>(dx) + static_cast<size_t>(row) * cols) : nullptr;
 #pragma unroll
         for (int j = 0; j < VPT; ++j) {
             const uint32_t i = threadIdx.x + j * blockDim.x;
@@ -309,9 +365,11 @@ __global__ void __launch_bounds__(kRowThreads) rmsnorm_bwd_fused_kernel(const fl
             acc[j].y += dv[j].y * xv[j].y * rstd;
             acc[j].z += dv[j].z * xv[j].z * rstd;
             acc[j].w += dv[j].w * xv[j].w * rstd;
-            if (dxr && i < n4)
-                dxr[i] = make_float4(rstd * (dv[j].x * wv[j].x - xv[j].x * coef), rstd * (dv[j].y * wv[j].y - xv[j].y * coef),
-                                     rstd * (dv[j].z * wv[j].z - xv[j].z * coef), rstd * (dv[j].w * wv[j].w - xv[j].w * coef));
+            if (i >= n4) continue;
+            const float4 o = make_float4(rstd * (dv[j].x * wv[j].x - xv[j].x * coef), rstd * (dv[j].y * wv[j].y - xv[j].y * coef),
+                                         rstd * (dv[j].z * wv[j].z - xv[j].z * coef), rstd * (dv[j].w * wv[j].w - xv[j].w * coef));
+            if (dxr) dxr[i] = o;
+            if (dxh) dxh[i] = pack_bf16x4(o.x, o.y, o.z, o.w);
         }
     }
     if (partial == nullptr) return;   // dx only
@@ -421,10 +479,11 @@ __global__ void __launch_bounds__(kRowThreads) softmax_bwd_kernel(const float* _
 
 // Fused softmax cross-entropy over one row per block: loss = log(sum exp(x - max)) + max - x[target];
 // dlogits = (exp(x - max) / sum - onehot) * scale.
-template <bool CACHE>
+// GRAD16: the gradient is stored as bf16 (round to nearest even of the same f32 values), ready to be a GEMM operand.
+template <bool CACHE, bool GRAD16 = false>
 __global__ void __launch_bounds__(kRowThreads) softmax_ce_kernel(const float* __restrict__ logits,
                                                                  const uint32_t* __restrict__ targets,
-                                                                 float* __restrict__ losses, float* __restrict__ dlogits,
+                                                                 float* __restrict__ losses, void* __restrict__ dlogits,
                                                                  uint32_t cols, size_t ld, float scale) {
     extern __shared__ __align__(16) float cache[];
     __shared__ float red[64];
@@ -435,10 +494,12 @@ __global__ void __launch_bounds__(kRowThreads) softmax_ce_kernel(const float* __
     const uint32_t t = targets[row];
     if (threadIdx.x == 0 && losses) losses[row] = (t < cols) ? (logf(s) + m - xr[t]) : 0.0f;
     if (!dlogits) return;
-    float* dr = dlogits + row * ld;
+    float* dr = static_cast<float*>(dlogits) + row * ld;
+    __nv_bfloat16* dh = static_cast<__nv_bfloat16*>(dlogits) + row * ld;
     const float inv = 1.0f / s;
     const float* src = CACHE ? cache : xr;
-    const bool vec = (cols % 4 == 0) && ((reinterpret_cast<uintptr_t>(xr) & 15) == 0) && ((reinterpret_cast<uintptr_t>(dr) & 15) == 0);
+    const bool vec = (cols % 4 == 0) && ((reinterpret_cast<uintptr_t>(xr) & 15) == 0) &&
+                     (GRAD16 ? (reinterpret_cast<uintptr_t>(dh) & 7) == 0 : (reinterpret_cast<uintptr_t>(dr) & 15) == 0);
     if (vec) {
         const uint32_t n4 = cols / 4;
         for (uint32_t i0 = threadIdx.x; i0 < n4; i0 += 4 * blockDim.x) {
@@ -461,18 +522,20 @@ __global__ void __launch_bounds__(kRowThreads) softmax_ce_kernel(const float* __
                     else if (t == c + 2) o.z -= 1.0f;
                     else o.w -= 1.0f;
                 }
-                reinterpret_cast<float4*>(dr)[i] = make_float4(o.x * scale, o.y * scale, o.z * scale, o.w * scale);
+                if (GRAD16) reinterpret_cast<uint2*>(dh)[i] = pack_bf16x4(o.x * scale, o.y * scale, o.z * scale, o.w * scale);
+                else reinterpret_cast<float4*>(dr)[i] = make_float4(o.x * scale, o.y * scale, o.z * scale, o.w * scale);
             }
         }
     } else {
-        for (uint32_t i = threadIdx.x; i < cols; i += blockDim.x)
-            dr[i] = (__expf(src[i] - m) * inv - (i == t ? 1.0f : 0.0f)) * scale;
+        for (uint32_t i = threadIdx.x; i < cols; i += blockDim.x) {
+            const float g = (__expf(src[i] - m) * inv - (i == t ? 1.0f : 0.0f)) * scale;
+            if (GRAD16) dh[i] = __float2bfloat16_rn(g);
+            else dr[i] = g;
+        }
     }
 }
 
 // ------------------------------------------------------------------------------------------------ element-wise
-
-__device__ __forceinline__ float sigmoidf_(float g) { return 1.0f / (1.0f + expf(-g)); }
 
 __global__ void __launch_bounds__(256) silu_gate_fwd_kernel(const float* __restrict__ gate, const float* __restrict__ up,
                                                             float* __restrict__ out, size_t n) {
@@ -496,12 +559,6 @@ __global__ void __launch_bounds__(256) silu_gate_fwd_kernel(const float* __restr
         const float g = gate[i];
         out[i] = g * sigmoidf_(g) * (up ? up[i] : 1.0f);
     }
-}
-
-__device__ __forceinline__ void silu_bwd_one(float gr, float g, float u, float& dgate, float& dup) {
-    const float sig = sigmoidf_(g);
-    dup = gr * g * sig;
-    dgate = gr * u * sig * (1.0f + g * (1.0f - sig));
 }
 
 __global__ void __launch_bounds__(256) silu_gate_bwd_kernel(const float* __restrict__ grad, const float* __restrict__ gate,
@@ -710,7 +767,7 @@ int32_t t0b_rmsnorm_bwd(t0b_ctx* ctx, uint64_t dy, uint64_t x, uint64_t weight, 
         if (rc != T0B_OK) return rc;
         if (dgamma) {
             ++ctx->launches;
-            rmsnorm_dgamma_final_kernel<<<(cols + 255) / 256, 256, 0, ctx->stream>>>(partial, reinterpret_cast<float*>(dgamma), cols, g);
+            rmsnorm_dgamma_final_kernel<<<kDgammaFinalGrid(cols), 256, 0, ctx->stream>>>(partial, reinterpret_cast<float*>(dgamma), cols, g);
         }
         return finish(ctx, async, "rmsnorm_bwd");
     }
@@ -730,7 +787,7 @@ int32_t t0b_rmsnorm_bwd(t0b_ctx* ctx, uint64_t dy, uint64_t x, uint64_t weight, 
         rc = check_cuda(ctx, cudaGetLastError(), "rmsnorm_dgamma_partial launch");
         if (rc != T0B_OK) return rc;
         ++ctx->launches;
-        rmsnorm_dgamma_final_kernel<<<(cols + 255) / 256, 256, 0, ctx->stream>>>(partial, reinterpret_cast<float*>(dgamma), cols, used);
+        rmsnorm_dgamma_final_kernel<<<kDgammaFinalGrid(cols), 256, 0, ctx->stream>>>(partial, reinterpret_cast<float*>(dgamma), cols, used);
     }
     return finish(ctx, async, "rmsnorm_bwd");
 }
@@ -797,7 +854,7 @@ int32_t t0b_rmsnorm_bwd_noalloc(t0b_ctx* ctx, uint64_t dy, uint64_t x, uint64_t 
                                                                  inv, partial, rows, cols, rpb);
     rc = check_cuda(ctx, cudaGetLastError(), "rmsnorm_bwd_noalloc partial launch");
     if (rc != T0B_OK) return rc;
-    rmsnorm_dgamma_final_kernel<<<(cols + 255) / 256, 256, 0, ctx->stream>>>(partial, reinterpret_cast<float*>(dgamma), cols, used);
+    rmsnorm_dgamma_final_kernel<<<kDgammaFinalGrid(cols), 256, 0, ctx->stream>>>(partial, reinterpret_cast<float*>(dgamma), cols, used);
     return finish(ctx, async, "rmsnorm_bwd_noalloc", 3);
 }
 
@@ -834,8 +891,8 @@ int32_t t0b_softmax_bwd(t0b_ctx* ctx, uint64_t dy, uint64_t y, uint64_t dx, uint
     return finish(ctx, async, "softmax_bwd");
 }
 
-int32_t t0b_softmax_ce(t0b_ctx* ctx, uint64_t logits, uint64_t targets, uint64_t losses, uint64_t dlogits, uint32_t rows,
-                       uint32_t cols, uint64_t ld, float scale, int32_t async) {
+static int32_t softmax_ce_impl(t0b_ctx* ctx, uint64_t logits, uint64_t targets, uint64_t losses, uint64_t dlogits, uint32_t rows,
+                               uint32_t cols, uint64_t ld, float scale, bool grad16, int32_t async) {
     int32_t rc = precheck(ctx);
     if (rc != T0B_OK) return rc;
     if (rows == 0) return T0B_OK;
@@ -843,25 +900,38 @@ int32_t t0b_softmax_ce(t0b_ctx* ctx, uint64_t logits, uint64_t targets, uint64_t
         return set_error(ctx, T0B_ERR_INVALID, "softmax_ce: null pointer, zero cols or pitch < cols");
     const int threads = cols >= 2048 ? kRowThreads : (cols >= 512 ? 128 : 32);
     const size_t bytes = static_cast<size_t>(cols) * 4;
+    const float* lp = reinterpret_cast<const float*>(logits);
+    const uint32_t* tp = reinterpret_cast<const uint32_t*>(targets);
+    float* losp = reinterpret_cast<float*>(losses);
+    void* dp = reinterpret_cast<void*>(dlogits);
     if (bytes <= kRowCacheMax && cols >= 2048) {
         static bool set[64] = {};
         if (!set[ctx->device & 63]) {
-            rc = check_cuda(ctx, cudaFuncSetAttribute(softmax_ce_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+            rc = check_cuda(ctx, cudaFuncSetAttribute(softmax_ce_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                       static_cast<int>(kRowCacheLimit)), "cudaFuncSetAttribute(softmax_ce)");
+            if (rc == T0B_OK)
+                rc = check_cuda(ctx, cudaFuncSetAttribute(softmax_ce_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                          static_cast<int>(kRowCacheLimit)), "cudaFuncSetAttribute(softmax_ce bf16)");
             if (rc != T0B_OK) return rc;
             set[ctx->device & 63] = true;
         }
-        softmax_ce_kernel<true><<<rows, threads, bytes, ctx->stream>>>(reinterpret_cast<const float*>(logits),
-                                                                       reinterpret_cast<const uint32_t*>(targets),
-                                                                       reinterpret_cast<float*>(losses), reinterpret_cast<float*>(dlogits),
-                                                                       cols, ld, scale);
+        if (grad16) softmax_ce_kernel<true, true><<<rows, threads, bytes, ctx->stream>>>(lp, tp, losp, dp, cols, ld, scale);
+        else softmax_ce_kernel<true, false><<<rows, threads, bytes, ctx->stream>>>(lp, tp, losp, dp, cols, ld, scale);
     } else {
-        softmax_ce_kernel<false><<<rows, threads, 0, ctx->stream>>>(reinterpret_cast<const float*>(logits),
-                                                                    reinterpret_cast<const uint32_t*>(targets),
-                                                                    reinterpret_cast<float*>(losses), reinterpret_cast<float*>(dlogits),
-                                                                    cols, ld, scale);
+        if (grad16) softmax_ce_kernel<false, true><<<rows, threads, 0, ctx->stream>>>(lp, tp, losp, dp, cols, ld, scale);
+        else softmax_ce_kernel<false, false><<<rows, threads, 0, ctx->stream>>>(lp, tp, losp, dp, cols, ld, scale);
     }
     return finish(ctx, async, "softmax_ce");
+}
+
+int32_t t0b_softmax_ce(t0b_ctx* ctx, uint64_t logits, uint64_t targets, uint64_t losses, uint64_t dlogits, uint32_t rows,
+                       uint32_t cols, uint64_t ld, float scale, int32_t async) {
+    return softmax_ce_impl(ctx, logits, targets, losses, dlogits, rows, cols, ld, scale, false, async);
+}
+
+int32_t t0b_softmax_ce_bf16(t0b_ctx* ctx, uint64_t logits, uint64_t targets, uint64_t losses, uint64_t dlogits_bf16, uint32_t rows,
+                            uint32_t cols, uint64_t ld, float scale, int32_t async) {
+    return softmax_ce_impl(ctx, logits, targets, losses, dlogits_bf16, rows, cols, ld, scale, true, async);
 }
 
 int32_t t0b_silu_gate_fwd(t0b_ctx* ctx, uint64_t gate, uint64_t up, uint64_t out, size_t n, int32_t async) {
@@ -909,6 +979,93 @@ int32_t t0b_adamw_step(t0b_ctx* ctx, uint64_t params, uint64_t grads, uint64_t m
                                                                  reinterpret_cast<__nv_bfloat16*>(params_bf16), n, lr, beta1, beta2, eps,
                                                                  weight_decay, bc1, bc2, grad_scale);
     return finish(ctx, async, "adamw_step");
+}
+
+// ------------------------------------------------------------------------------------------------
+// RMSNorm -> SiLU -> bf16 in one pass each way (the block between two Linear layers of the MLP).
+// ------------------------------------------------------------------------------------------------
+static bool rmsnorm_reg_path(uint64_t ptrs, uint32_t cols) {
+    return (ptrs & 15) == 0 && cols % 4 == 0 && cols >= 1024 && cols <= 4u * 4u * kRowThreads;
+}
+
+int32_t t0b_rmsnorm_silu_fwd(t0b_ctx* ctx, uint64_t x, uint64_t weight, uint64_t out_bf16, uint64_t inv_rms, uint32_t rows,
+                             uint32_t cols, float eps, int32_t async) {
+    int32_t rc = precheck(ctx);
+    if (rc != T0B_OK) return rc;
+    if (rows == 0) return T0B_OK;
+    if (cols == 0 || !x || !weight || !out_bf16) return set_error(ctx, T0B_ERR_INVALID, "rmsnorm_silu_fwd: null pointer or zero cols");
+    if (rmsnorm_reg_path(x | weight | out_bf16, cols)) {
+        const uint32_t g = std::min<uint32_t>(rows, static_cast<uint32_t>(ctx->num_sms) * 4u);
+        const uint32_t n4 = cols / 4;
+        const float* xp = reinterpret_cast<const float*>(x);
+        const float* wp = reinterpret_cast<const float*>(weight);
+        void* yp = reinterpret_cast<void*>(out_bf16);
+        float* ip = reinterpret_cast<float*>(inv_rms);
+        if (n4 <= 1u * kRowThreads) rmsnorm_fwd_reg_kernel<1, true><<<g, kRowThreads, 0, ctx->stream>>>(xp, wp, yp, ip, rows, cols, eps);
+        else if (n4 <= 2u * kRowThreads) rmsnorm_fwd_reg_kernel<2, true><<<g, kRowThreads, 0, ctx->stream>>>(xp, wp, yp, ip, rows, cols, eps);
+        else rmsnorm_fwd_reg_kernel<4, true><<<g, kRowThreads, 0, ctx->stream>>>(xp, wp, yp, ip, rows, cols, eps);
+        return finish(ctx, async, "rmsnorm_silu_fwd");
+    }
+    // Other shapes: the three kernels in sequence through a pooled f32 buffer (same values).
+    std::lock_guard<std::recursive_mutex> lk(ctx->mu);
+    const size_t n = static_cast<size_t>(rows) * cols;
+    uint64_t tmp = 0;
+    rc = t0b_alloc(ctx, n * 4, &tmp);
+    if (rc != T0B_OK) return rc;
+    rc = t0b_rmsnorm_fwd(ctx, x, weight, tmp, inv_rms, rows, cols, eps, 1);
+    if (rc == T0B_OK) rc = t0b_silu_gate_fwd(ctx, tmp, 0, tmp, n, 1);
+    if (rc == T0B_OK) rc = t0b_cast_f32_to_bf16(ctx, tmp, out_bf16, n, 1);
+    t0b_recycle(ctx, tmp);
+    if (rc != T0B_OK) return rc;
+    return finish(ctx, async, "rmsnorm_silu_fwd", 0);
+}
+
+int32_t t0b_rmsnorm_silu_bwd(t0b_ctx* ctx, uint64_t dh, uint64_t x, uint64_t weight, uint64_t dx_bf16, uint64_t dgamma,
+                             uint64_t scratch, size_t scratch_bytes, uint32_t rows, uint32_t cols, float eps, int32_t async) {
+    int32_t rc = precheck(ctx);
+    if (rc != T0B_OK) return rc;
+    if (rows == 0) {
+        if (dgamma && cols) return t0b_memset0(ctx, dgamma, static_cast<size_t>(cols) * 4);
+        return T0B_OK;
+    }
+    if (cols == 0 || !dh || !x || !weight || (!dx_bf16 && !dgamma))
+        return set_error(ctx, T0B_ERR_INVALID, "rmsnorm_silu_bwd: null pointer or zero cols");
+    if (dgamma && (!scratch || scratch_bytes < t0b_rmsnorm_bwd_scratch_bytes(rows, cols)))
+        return set_error(ctx, T0B_ERR_INVALID, "rmsnorm_silu_bwd: dgamma needs %zu bytes of scratch, got %zu",
+                         t0b_rmsnorm_bwd_scratch_bytes(rows, cols), scratch_bytes);
+    if (rmsnorm_reg_path(dh | x | weight | dx_bf16 | scratch, cols)) {
+        const uint32_t g = dgamma ? rmsnorm_fused_ctas(rows) : std::min<uint32_t>(rows, static_cast<uint32_t>(ctx->num_sms) * 4u);
+        const uint32_t n4 = cols / 4;
+        float* partial = dgamma ? reinterpret_cast<float*>(scratch) + ((static_cast<size_t>(rows) + 3) & ~static_cast<size_t>(3)) : nullptr;
+        const float* dp = reinterpret_cast<const float*>(dh);
+        const float* xp = reinterpret_cast<const float*>(x);
+        const float* wp = reinterpret_cast<const float*>(weight);
+        void* op = reinterpret_cast<void*>(dx_bf16);
+        if (n4 <= 1u * kRowThreads) rmsnorm_bwd_fused_kernel<1, true><<<g, kRowThreads, 0, ctx->stream>>>(dp, xp, wp, op, partial, rows, cols, eps);
+        else if (n4 <= 2u * kRowThreads) rmsnorm_bwd_fused_kernel<2, true><<<g, kRowThreads, 0, ctx->stream>>>(dp, xp, wp, op, partial, rows, cols, eps);
+        else rmsnorm_bwd_fused_kernel<4, true><<<g, kRowThreads, 0, ctx->stream>>>(dp, xp, wp, op, partial, rows, cols, eps);
+        rc = check_cuda(ctx, cudaGetLastError(), "rmsnorm_silu_bwd launch");
+        if (rc != T0B_OK) return rc;
+        if (dgamma) {
+            ++ctx->launches;
+            rmsnorm_dgamma_final_kernel<<<kDgammaFinalGrid(cols), 256, 0, ctx->stream>>>(partial, reinterpret_cast<float*>(dgamma), cols, g);
+        }
+        return finish(ctx, async, "rmsnorm_silu_bwd");
+    }
+    // Other shapes: recompute the normalised row, then SiLU backward, RMSNorm backward and the cast in sequence.
+    std::lock_guard<std::recursive_mutex> lk(ctx->mu);
+    const size_t n = static_cast<size_t>(rows) * cols;
+    uint64_t r = 0, dr = 0;
+    rc = t0b_alloc(ctx, n * 4, &r);
+    if (rc == T0B_OK) rc = t0b_alloc(ctx, n * 4, &dr);
+    if (rc == T0B_OK) rc = t0b_rmsnorm_fwd(ctx, x, weight, r, 0, rows, cols, eps, 1);
+    if (rc == T0B_OK) rc = t0b_silu_gate_bwd(ctx, dh, r, 0, dr, 0, n, 1);
+    if (rc == T0B_OK) rc = t0b_rmsnorm_bwd(ctx, dr, x, weight, dx_bf16 ? r : 0, dgamma, scratch, scratch_bytes, rows, cols, eps, 1);
+    if (rc == T0B_OK && dx_bf16) rc = t0b_cast_f32_to_bf16(ctx, r, dx_bf16, n, 1);
+    if (r) t0b_recycle(ctx, r);
+    if (dr) t0b_recycle(ctx, dr);
+    if (rc != T0B_OK) return rc;
+    return finish(ctx, async, "rmsnorm_silu_bwd", 0);
 }
 
 }  // extern "C"

@@ -106,16 +106,11 @@ class MlpTrainer:
         B = rows
         self.x16 = torch.empty((B, cfg.d_in), dtype=bf16, device=self.dev)
         self.z = [torch.empty((B, h), dtype=f32, device=self.dev) for h in cfg.hidden]        # Linear outputs
-        self.r = [torch.empty((B, h), dtype=f32, device=self.dev) for h in cfg.hidden]        # RMSNorm outputs
-        self.a = torch.empty((B, max(cfg.hidden)), dtype=f32, device=self.dev)                # SiLU output (scratch)
         self.h16 = [torch.empty((B, h), dtype=bf16, device=self.dev) for h in cfg.hidden]     # bf16 layer outputs
         self.logits = torch.empty((B, cfg.n_classes), dtype=f32, device=self.dev)
-        self.dlogits = torch.empty((B, cfg.n_classes), dtype=f32, device=self.dev)
         self.dlogits16 = torch.empty((B, cfg.n_classes), dtype=bf16, device=self.dev)
         self.losses = torch.empty(B, dtype=f32, device=self.dev)
         self.dh = torch.empty((B, max(cfg.hidden)), dtype=f32, device=self.dev)
-        self.dr = torch.empty((B, max(cfg.hidden)), dtype=f32, device=self.dev)
-        self.dz = torch.empty((B, max(cfg.hidden)), dtype=f32, device=self.dev)
         self.dz16 = torch.empty((B, max(cfg.hidden)), dtype=bf16, device=self.dev)
         self.scratch_bytes = self.L.t0b_rmsnorm_bwd_scratch_bytes(B, max(cfg.hidden))
         self.scratch = torch.empty(self.scratch_bytes, dtype=torch.uint8, device=self.dev)
@@ -150,17 +145,16 @@ class MlpTrainer:
         for l in range(nh):
             n = cfg.hidden[l]
             self._gemm(inp, self.w16[l], self.z[l], B, n, k, False, False, k, n)
-            self._ck(L.t0b_rmsnorm_fwd(h, self.z[l].data_ptr(), self.gamma[l].data_ptr(), self.r[l].data_ptr(), 0, B, n,
-                                       cfg.eps, 1))
-            self._ck(L.t0b_silu_gate_fwd(h, self.r[l].data_ptr(), 0, self.a.data_ptr(), B * n, 1))
-            self._cast(self.a, self.h16[l], B * n)
+            # RMSNorm, SiLU and the bf16 down-cast in one pass over z (the f32 intermediates never reach memory)
+            self._ck(L.t0b_rmsnorm_silu_fwd(h, self.z[l].data_ptr(), self.gamma[l].data_ptr(), self.h16[l].data_ptr(), 0, B, n,
+                                            cfg.eps, 1))
             inp, k = self.h16[l], n
         V = cfg.n_classes
         self._gemm(inp, self.w16[nh], self.logits, B, V, k, False, False, k, V)
-        self._ck(L.t0b_softmax_ce(h, self.logits.data_ptr(), targets.data_ptr(), self.losses.data_ptr(),
-                                  self.dlogits.data_ptr(), B, V, V, scale, 1))
+        # loss and its gradient, stored directly as the bf16 operand of the two GEMMs that follow
+        self._ck(L.t0b_softmax_ce_bf16(h, self.logits.data_ptr(), targets.data_ptr(), self.losses.data_ptr(),
+                                       self.dlogits16.data_ptr(), B, V, V, scale, 1))
         # backward
-        self._cast(self.dlogits, self.dlogits16, B * V)
         # dW_out[k, V] = h_last^T [k, B] * dlogits [B, V]: A stored [B, k] read transposed
         self._gemm(inp, self.dlogits16, self.dw[nh], k, V, B, True, False, k, V)
         self._start_allreduce(self.dw[nh])
@@ -170,11 +164,10 @@ class MlpTrainer:
             n = cfg.hidden[l]
             k = cfg.hidden[l - 1] if l > 0 else cfg.d_in
             prev = self.h16[l - 1] if l > 0 else self.x16
-            self._ck(L.t0b_silu_gate_bwd(h, self.dh.data_ptr(), self.r[l].data_ptr(), 0, self.dr.data_ptr(), 0, B * n, 1))
-            self._ck(L.t0b_rmsnorm_bwd(h, self.dr.data_ptr(), self.z[l].data_ptr(), self.gamma[l].data_ptr(),
-                                       self.dz.data_ptr(), self.dgamma[l].data_ptr(), self.scratch.data_ptr(),
-                                       self.scratch_bytes, B, n, cfg.eps, 1))
-            self._cast(self.dz, self.dz16, B * n)
+            # SiLU backward on the recomputed RMSNorm output, RMSNorm backward and the bf16 down-cast in one pass
+            self._ck(L.t0b_rmsnorm_silu_bwd(h, self.dh.data_ptr(), self.z[l].data_ptr(), self.gamma[l].data_ptr(),
+                                            self.dz16.data_ptr(), self.dgamma[l].data_ptr(), self.scratch.data_ptr(),
+                                            self.scratch_bytes, B, n, cfg.eps, 1))
             self._gemm(prev, self.dz16, self.dw[l], k, n, B, True, False, k, n)
             self._start_allreduce(self.dw[l])
             if l > 0:

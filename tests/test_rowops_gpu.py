@@ -159,3 +159,77 @@ def test_cast_transpose(rt, rows, cols):
     call(rt, lib().t0b_cast_f32_to_bf16_transpose, xb.gpu_addr(), ob.gpu_addr(), rows, cols, 0)
     got = ob.read_as(np.uint16, rows * cols).reshape(cols, rows)
     assert np.array_equal(got, oracle.f32_to_bf16_rne(x).T)
+
+
+@pytest.mark.parametrize("rows,cols", [(1024, 4096), (64, 1024), (37, 2052), (5, 8192), (16, 260), (3, 33), (9, 9000)])
+def test_fused_rmsnorm_silu_matches_the_unfused_sequence(rt, rows, cols):
+    """t0b_rmsnorm_silu_fwd / _bwd against (a) the sequence of calls they replace -- same bits -- and (b) the oracle
+    chain RMSNorm -> SiLU (src/t0/rmsnorm_kernels.rs:140-174, src/ignis/ops/silu.rs:118-130) at the row-kernel
+    tolerance.  Shapes cover the register-resident path (cols % 4 == 0, 1024..8192) and the fallback."""
+    L = lib()
+    rng = np.random.default_rng(rows * 13 + cols)
+    x = rng.standard_normal((rows, cols)).astype(np.float32) * 1.5
+    w = (1.0 + 0.1 * rng.standard_normal(cols)).astype(np.float32)
+    dh = rng.standard_normal((rows, cols)).astype(np.float32)
+    eps = 1e-6
+    n = rows * cols
+    dx_, dw_, ddh = rt.upload_f32(x), rt.upload_f32(w), rt.upload_f32(dh)
+    # unfused forward
+    r, a, h16 = rt.alloc(n * 4), rt.alloc(n * 4), rt.alloc(n * 2)
+    call(rt, L.t0b_rmsnorm_fwd, dx_.gpu_addr(), dw_.gpu_addr(), r.gpu_addr(), 0, rows, cols, eps, 1)
+    call(rt, L.t0b_silu_gate_fwd, r.gpu_addr(), 0, a.gpu_addr(), n, 1)
+    call(rt, L.t0b_cast_f32_to_bf16, a.gpu_addr(), h16.gpu_addr(), n, 0)
+    want_h = h16.read_as(np.uint16, n)
+    # fused forward
+    f16, inv = rt.alloc(n * 2), rt.alloc(max(rows * 4, 16))
+    call(rt, L.t0b_rmsnorm_silu_fwd, dx_.gpu_addr(), dw_.gpu_addr(), f16.gpu_addr(), inv.gpu_addr(), rows, cols, eps, 0)
+    got_h = f16.read_as(np.uint16, n)
+    assert np.array_equal(got_h, want_h)
+    y_ref, inv_ref = oracle.rmsnorm_forward(x, w, eps)
+    silu_ref = oracle.silu_gate_forward(y_ref, np.ones_like(y_ref))
+    assert rel_err(oracle.bf16_to_f32(got_h).reshape(rows, cols), silu_ref) <= 2.0 ** -8 + REL      # bf16 rounding of the output
+    assert rel_err(inv.read_as(np.float32, rows), np.asarray(inv_ref).reshape(-1)) <= REL
+    # unfused backward
+    dr, dz, dz16, dg = rt.alloc(n * 4), rt.alloc(n * 4), rt.alloc(n * 2), rt.alloc(max(cols * 4, 16))
+    sb = L.t0b_rmsnorm_bwd_scratch_bytes(rows, cols)
+    scratch = rt.alloc(sb)
+    call(rt, L.t0b_silu_gate_bwd, ddh.gpu_addr(), r.gpu_addr(), 0, dr.gpu_addr(), 0, n, 1)
+    call(rt, L.t0b_rmsnorm_bwd, dr.gpu_addr(), dx_.gpu_addr(), dw_.gpu_addr(), dz.gpu_addr(), dg.gpu_addr(), scratch.gpu_addr(), sb,
+         rows, cols, eps, 1)
+    call(rt, L.t0b_cast_f32_to_bf16, dz.gpu_addr(), dz16.gpu_addr(), n, 0)
+    want_dz, want_dg = dz16.read_as(np.uint16, n), dg.read_as(np.float32, cols)
+    # fused backward
+    fz16, fg = rt.alloc(n * 2), rt.alloc(max(cols * 4, 16))
+    call(rt, L.t0b_rmsnorm_silu_bwd, ddh.gpu_addr(), dx_.gpu_addr(), dw_.gpu_addr(), fz16.gpu_addr(), fg.gpu_addr(), scratch.gpu_addr(),
+         sb, rows, cols, eps, 0)
+    assert np.array_equal(fz16.read_as(np.uint16, n), want_dz)
+    assert np.array_equal(fg.read_as(np.float32, cols), want_dg)
+    dgate_ref, _ = oracle.silu_gate_backward(dh, y_ref, np.ones_like(y_ref))
+    dx_ref = oracle.rmsnorm_backward(dgate_ref, x, w, eps)
+    assert rel_err(oracle.bf16_to_f32(fz16.read_as(np.uint16, n)).reshape(rows, cols), dx_ref) <= 2.0 ** -8 + REL
+    assert rel_err(fg.read_as(np.float32, cols), oracle.rmsnorm_dgamma(dgate_ref, x, eps)) <= REL
+    # dx only (no dgamma, no scratch)
+    fz2 = rt.alloc(n * 2)
+    call(rt, L.t0b_rmsnorm_silu_bwd, ddh.gpu_addr(), dx_.gpu_addr(), dw_.gpu_addr(), fz2.gpu_addr(), 0, 0, 0, rows, cols, eps, 0)
+    assert rel_err(oracle.bf16_to_f32(fz2.read_as(np.uint16, n)).reshape(rows, cols), dx_ref) <= 2.0 ** -8 + REL
+
+
+@pytest.mark.parametrize("rows,cols", [(4, 32), (33, 1000), (8, 4099), (64, 32000), (1024, 32000)])
+def test_softmax_cross_entropy_bf16_gradient(rt, rows, cols):
+    """t0b_softmax_ce_bf16 stores the gradient of t0b_softmax_ce rounded to bf16 (RNE): same bits as ce + cast."""
+    L = lib()
+    rng = np.random.default_rng(cols + rows)
+    logits = (rng.standard_normal((rows, cols)) * 3).astype(np.float32)
+    targets = rng.integers(0, cols, rows).astype(np.uint32)
+    dl, dt = rt.upload_f32(logits), rt.upload(targets)
+    loss1, loss2 = rt.alloc(max(rows * 4, 16)), rt.alloc(max(rows * 4, 16))
+    g32, g16a, g16b = rt.alloc(rows * cols * 4), rt.alloc(rows * cols * 2), rt.alloc(rows * cols * 2)
+    scale = 1.0 / rows
+    call(rt, L.t0b_softmax_ce, dl.gpu_addr(), dt.gpu_addr(), loss1.gpu_addr(), g32.gpu_addr(), rows, cols, cols, scale, 1)
+    call(rt, L.t0b_cast_f32_to_bf16, g32.gpu_addr(), g16a.gpu_addr(), rows * cols, 0)
+    call(rt, L.t0b_softmax_ce_bf16, dl.gpu_addr(), dt.gpu_addr(), loss2.gpu_addr(), g16b.gpu_addr(), rows, cols, cols, scale, 0)
+    assert np.array_equal(g16a.read_as(np.uint16, rows * cols), g16b.read_as(np.uint16, rows * cols))
+    assert np.array_equal(loss1.read_as(np.float32, rows), loss2.read_as(np.float32, rows))
+    ref = oracle.ce_loss_backward(logits, targets, scale)
+    got = oracle.bf16_to_f32(g16b.read_as(np.uint16, rows * cols)).reshape(rows, cols)
+    assert np.abs(got - ref).max() <= (2.0 ** -8 + REL) * np.abs(ref).max()
