@@ -231,7 +231,38 @@ def context_measurements(torch, rt, L, stream, dev):
                                     rows, cols, 1e-6, 1))
 
     out["rmsnorm_bwd_dx_8192x4096"] = gbs(rms_bwd, 3 * rows * cols * 4)
-    del xs, ys, dy
+    h16 = [torch.empty(rows, cols, device=dev, dtype=torch.bfloat16) for _ in range(nbuf)]
+    dg = torch.empty(cols, device=dev)
+    sb = L.t0b_rmsnorm_bwd_scratch_bytes(rows, cols)
+    scratch = torch.empty(sb, dtype=torch.uint8, device=dev)
+
+    def fused_fwd():
+        j = i[0] % nbuf
+        i[0] += 1
+        rt._check(L.t0b_rmsnorm_silu_fwd(rt.handle, xs[j].data_ptr(), w.data_ptr(), h16[j].data_ptr(), 0, rows, cols, 1e-6, 1))
+
+    def fused_bwd():
+        j = i[0] % nbuf
+        i[0] += 1
+        rt._check(L.t0b_rmsnorm_silu_bwd(rt.handle, dy.data_ptr(), xs[j].data_ptr(), w.data_ptr(), h16[j].data_ptr(), dg.data_ptr(),
+                                         scratch.data_ptr(), sb, rows, cols, 1e-6, 1))
+
+    # algorithmic bytes: read x (f32) + write bf16; backward reads dh and x (f32), writes bf16 dx
+    out["rmsnorm_silu_bf16_fwd_8192x4096"] = gbs(fused_fwd, rows * cols * 6)
+    out["rmsnorm_silu_bf16_bwd_8192x4096"] = gbs(fused_bwd, rows * cols * 10)
+    del xs, ys, dy, h16
+    vocab, edim, tokens = 32000, 4096, 16384
+    table = torch.randn(vocab, edim, device=dev)
+    ids = torch.randint(0, vocab, (tokens,), device=dev, dtype=torch.int32)
+    eout = torch.empty(tokens, edim, device=dev)
+    gtab = torch.zeros(vocab, edim, device=dev)
+    out["embedding_fwd_16384x4096"] = gbs(lambda: rt._check(L.t0b_embedding_fwd(
+        rt.handle, table.data_ptr(), ids.data_ptr(), eout.data_ptr(), tokens, edim, vocab, 1)), 2 * tokens * edim * 4)
+    uniq = int(torch.unique(ids).numel())
+    out["embedding_bwd_16384x4096"] = gbs(lambda: rt._check(L.t0b_embedding_bwd(
+        rt.handle, gtab.data_ptr(), ids.data_ptr(), eout.data_ptr(), tokens, edim, vocab, 0, 0, 1)),
+        (tokens + 2 * uniq) * edim * 4)
+    del table, eout, gtab
     rows, cols = 1024, 32000
     nbuf = 4
     xs = [torch.randn(rows, cols, device=dev) * 3 for _ in range(nbuf)]

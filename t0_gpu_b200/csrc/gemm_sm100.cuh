@@ -108,7 +108,11 @@ struct GemmTraits {
     static constexpr int kBTileBytes = kBTiles * kBSubTileBytes;
     static constexpr int kStageBytes = kATileBytes + kBTileBytes;
     static constexpr int kCtrlBytes = 1024;   // keeps the transpose tiles behind it 1024-byte aligned (TMA swizzle)
-    static constexpr int kEpiWarps = 4 * MT;
+    // Single-accumulator tiles of at least 128 columns are drained by two groups of four warps, each taking half of the
+    // columns: the epilogue of the last tile of a CTA is exposed, and it is the store sequence of one warp per lane
+    // quarter, not the memory system, that bounds it.
+    static constexpr int kEpiSplit = (MT == 1 && BN >= 128) ? 2 : 1;
+    static constexpr int kEpiWarps = 4 * MT * kEpiSplit;
     static constexpr int kEpiStagingBytes = kEpiWarps * 4096;   // one 32x32 f32 transpose tile per epilogue warp
     static constexpr int kBudget = 227 * 1024 - 1024 - kCtrlBytes - kEpiStagingBytes;
     static constexpr int kStagesRaw = kBudget / kStageBytes;
@@ -335,7 +339,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
         }
         for (int a = 0; a < 2; ++a) {
             ptx::mbar_init(tfull_bar(a), 1);
-            ptx::mbar_init(tempty_bar(a), 4 * CG);   // one arrival per epilogue warp of the slot, from every CTA of the group
+            ptx::mbar_init(tempty_bar(a), 4 * CG * T::kEpiSplit);   // one arrival per epilogue warp of the slot, from every CTA of the group
         }
         *abort_flag = 0;
         ptx::fence_mbar_init();
@@ -500,8 +504,10 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
     } else {
         // ------------------------------------------------------------------ epilogue: one group of 4 warps per slot owner
         const int q = warp & 3;              // TMEM lane quarter this warp may read
-        const int group = (warp - 2) >> 2;   // MT == 2: group g drains slot g of every tile
+        const int group = (warp - 2) >> 2;   // MT == 2: group g drains slot g of every tile; else group g takes column half g
         int slot = (MT == 2) ? group : 0;
+        constexpr int kChunks = BN / 32 / T::kEpiSplit;          // 32-column chunks per warp and tile
+        const int c_begin = (T::kEpiSplit == 2) ? group * kChunks : 0;
         uint32_t slot_phase = 0;
         const bool to_slab = p.split_k > 1;
         const long long ld_out = to_slab ? p.ld_partial : p.ldc;
@@ -532,15 +538,15 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
             const uint32_t t_row = tmem_base + static_cast<uint32_t>(slot * BN) + (static_cast<uint32_t>(q * 32) << 16);
             // The TMEM read of chunk c+1 is in flight while chunk c is transposed and stored.
             uint32_t nxt[32];
-            ptx::tmem_ld_32x32(t_row, nxt);
+            ptx::tmem_ld_32x32(t_row + c_begin * 32, nxt);
 #pragma unroll 2
-            for (int c = 0; c < BN / 32; ++c) {
+            for (int c = c_begin; c < c_begin + kChunks; ++c) {
                 uint32_t raw[32];
                 ptx::tmem_ld_wait_regs(nxt);
 #pragma unroll
                 for (int j = 0; j < 32; ++j) raw[j] = nxt[j];
-                if (c + 1 < BN / 32) ptx::tmem_ld_32x32(t_row + (c + 1) * 32, nxt);
-                if (c == BN / 32 - 1) {
+                if (c + 1 < c_begin + kChunks) ptx::tmem_ld_32x32(t_row + (c + 1) * 32, nxt);
+                if (c == c_begin + kChunks - 1) {
                     // All of this warp's reads of the accumulator are done: hand it back to the MMA issuer.
                     ptx::tc_fence_before();
                     __syncwarp();

@@ -89,9 +89,12 @@ int stage_bytes(uint32_t bn, uint32_t cg, uint32_t mt) {
     return static_cast<int>(mt) * 128 * 64 * 2 + static_cast<int>(bn / cg) * 64 * 2;
 }
 
+// Epilogue warps of a variant: four per accumulator owner, doubled for single-accumulator tiles of >= 128 columns.
+int epi_warps(uint32_t bn, uint32_t mt) { return static_cast<int>(mt) * 4 * ((mt == 1 && bn >= 128) ? 2 : 1); }
+
 int stages_for(uint32_t bn, uint32_t cg, uint32_t mt) {
     const int stage = stage_bytes(bn, cg, mt);
-    const int budget = 227 * 1024 - 1024 - 1024 - static_cast<int>(mt) * 4 * 4096;   // minus the epilogue transpose tiles
+    const int budget = 227 * 1024 - 1024 - 1024 - epi_warps(bn, mt) * 4096;   // minus the epilogue transpose tiles
     return std::min(8, budget / stage);
 }
 
@@ -177,7 +180,7 @@ void resolve_plan(const t0b_gemm_config* cfg_in, const PlanInput& in, t0b_gemm_p
     const uint64_t clusters = static_cast<uint64_t>(num_sms) / p.cta_group;
     p.grid = static_cast<uint32_t>(std::min<uint64_t>(tiles, clusters) * p.cta_group);
     p.smem_bytes = p.stages * stage_bytes(p.n_tiles == 2 ? 256 : p.bn, p.cta_group, std::max(p.m_tiles, p.n_tiles)) + 1024 + 1024 +
-                   std::max(p.m_tiles, p.n_tiles) * 4 * 4096;
+                   epi_warps(p.n_tiles == 2 ? 256 : p.bn, std::max(p.m_tiles, p.n_tiles)) * 4096;
     *out = p;
 }
 

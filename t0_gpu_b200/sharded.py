@@ -93,8 +93,9 @@ class ColumnShardedGemm:
             self.rt._check(lib().t0b_ipc_open(self.rt.handle, blob, C.byref(p)))
             ptrs.append(p.value)
             self._opened.append(p.value)
-        # Own buffer first: destination 0 is the local store.
-        self._peer_ptrs = [ptrs[self.rank]] + [p for r, p in enumerate(ptrs) if r != self.rank]
+        # Own buffer first (destination 0 is the local store), then the peers starting at rank + 1: at any moment the
+        # ranks then write to different peers, which spreads the traffic over every GPU's NVLink ingress.
+        self._peer_ptrs = [ptrs[(self.rank + i) % self.world] for i in range(self.world)]
 
     def run(self, a: GpuBuffer, b_shard: GpuBuffer, async_: bool = True, gather: bool = True) -> None:
         """Launch this rank's GEMM.  With gather=False only the local C is written (GEMM-only timing)."""
