@@ -387,7 +387,7 @@ def run_single(args, local_rank):
     roofline = {"bound": "tensor", "achieved": value, "peak": peak, "unit": UNIT, "frac": value / peak,
                 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel on this workload, from the
                 # ncu capture summarised in profiles/gemm_bf16_tcgen05_8192cubed.md (algorithmic bytes: 536.9e6).
-                "traffic": 1.0766e9, "peak_kind": f"of {kind} ({'sustained' if long_region else 'burst'} cuBLAS bf16)",
+                "traffic": 1.1116e9, "peak_kind": f"of {kind} ({'sustained' if long_region else 'burst'} cuBLAS bf16)",
                 "kernel": "gemm_bf16_tcgen05_kernel (tile " + cfg.name() + ")", "flops_per_launch": flops,
                 "frac_of_nominal_dense_peak": value / DENSE_PEAK_TFLOPS}
 
