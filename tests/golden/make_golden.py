@@ -28,7 +28,9 @@ FILES = [
 
 
 def main() -> None:
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: python tests/golden/make_golden.py /path/to/reference")
+    ref = sys.argv[1]
     src_dir = os.path.join(ref, "benchmarks", "torch_ref")
     dst_dir = os.path.join(os.path.dirname(os.path.abspath(__file__)), "torch_ref")
     os.makedirs(dst_dir, exist_ok=True)
