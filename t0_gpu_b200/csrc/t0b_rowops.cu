@@ -150,7 +150,9 @@ __global__ void __launch_bounds__(kRowThreads) rmsnorm_fwd_kernel(const float* _
     }
 }
 
-__device__ __forceinline__ float sigmoidf_(float g) { return 1.0f / (1.0f + expf(-g)); }
+// Fast sigmoid (ex2.approx-based exponential and approximate reciprocal, relative error of a few 1e-7): the accurate
+// expf and division made the fused RMSNorm+SiLU kernels instruction-bound.
+__device__ __forceinline__ float sigmoidf_(float g) { return __fdividef(1.0f, 1.0f + __expf(-g)); }
 
 __device__ __forceinline__ void silu_bwd_one(float gr, float g, float u, float& dgate, float& dup) {
     const float sig = sigmoidf_(g);
@@ -171,7 +173,7 @@ __device__ __forceinline__ uint2 pack_bf16x4(float a, float b, float c, float d)
 // SILU16: the row is passed through SiLU and stored as bf16 (the input of the next GEMM) -- the values the
 // three-kernel sequence RMSNorm, SiLU, f32->bf16 cast would store, without the two f32 round trips through HBM.
 template <int VPT, bool SILU16 = false>
-__global__ void __launch_bounds__(kRowThreads) rmsnorm_fwd_reg_kernel(const float* __restrict__ x, const float* __restrict__ w,
+__global__ void __launch_bounds__(kRowThreads, VPT <= 2 ? 4 : 1) rmsnorm_fwd_reg_kernel(const float* __restrict__ x, const float* __restrict__ w,
                                                                       void* __restrict__ y, float* __restrict__ inv_rms,
                                                                       uint32_t rows, uint32_t cols, float eps) {
     __shared__ float red[64];
