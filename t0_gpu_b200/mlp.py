@@ -11,7 +11,10 @@ backward, AdamW) with the ops of the hot path: `matmul` forward / backward-data 
 (src/ignis/ops/cross_entropy.rs:34-115) with loss and gradient computed on the device, AdamW
 (src/t0/adamw_kernels.rs:35-119).  Data parallelism (rows split over ranks, fp32 gradient all-reduce) has no
 counterpart in the reference; `torch.distributed` carries the all-reduce, started per layer as soon as that
-layer's weight gradient is ready so it overlaps the rest of the backward pass.
+layer's weight gradient is ready so it overlaps the rest of the backward pass.  With `shard_optimizer=True` the
+gradients are reduce-scattered instead, every rank runs AdamW on its 1/world slice of each tensor and the updated
+copies are all-gathered: half the gradient bytes on NVLink and 1/world of the optimizer's HBM traffic per rank, the
+same update per element.
 
 Device memory comes from torch tensors (the all-reduce needs them); every kernel is a C-ABI call.
 """
@@ -61,7 +64,7 @@ class MlpTrainer:
     """One data-parallel replica.  `rows` is this rank's share of the batch, `rows_total` the global batch."""
 
     def __init__(self, rt: GpuRuntime, cfg: MlpConfig, rows: int, rows_total: Optional[int] = None, group=None,
-                 seed: int = 100):
+                 seed: int = 100, shard_optimizer: bool = False):
         import torch
         import torch.distributed as dist
 
@@ -85,13 +88,26 @@ class MlpTrainer:
         self.master = torch.empty(self.n_params, dtype=f32, device=self.dev)
         self.grads = torch.zeros(self.n_params, dtype=f32, device=self.dev)
         self.compute = torch.empty(self.n_params, dtype=bf16, device=self.dev)   # bf16 copies (gammas unused)
-        self.adam_m = torch.zeros(self.n_params, dtype=f32, device=self.dev)
-        self.adam_v = torch.zeros(self.n_params, dtype=f32, device=self.dev)
         offs, o = [], 0
         for s in sizes:
             offs.append(o)
             o += s
         nl = len(dims)
+        # Units of the gradient exchange: one per weight matrix, and one for all gammas together (stored consecutively).
+        self._units = [(offs[i], sizes[i]) for i in range(nl)] + [(offs[nl], sum(cfg.hidden))]
+        # Sharded optimizer (more than one rank): every unit's gradient is reduce-scattered instead of all-reduced, each
+        # rank keeps AdamW state for, and updates, its 1/world slice of every unit, and the updated bf16 copies (f32
+        # for the gammas) are all-gathered.  Per rank this moves half the gradient bytes over NVLink, a 1/world share
+        # of the AdamW traffic through HBM, and the same arithmetic per element as the replicated update.
+        self.sharded = bool(shard_optimizer) and self.world > 1 and all(n % self.world == 0 for _, n in self._units)
+        if self.sharded:
+            self.rank = dist.get_rank(group)
+            self.grad_shards = [torch.empty(n // self.world, dtype=f32, device=self.dev) for _, n in self._units]
+            self.m_shards = [torch.zeros(n // self.world, dtype=f32, device=self.dev) for _, n in self._units]
+            self.v_shards = [torch.zeros(n // self.world, dtype=f32, device=self.dev) for _, n in self._units]
+        else:
+            self.adam_m = torch.zeros(self.n_params, dtype=f32, device=self.dev)
+            self.adam_v = torch.zeros(self.n_params, dtype=f32, device=self.dev)
         self.w = [self.master[offs[i]:offs[i] + sizes[i]].view(dims[i]) for i in range(nl)]
         self.w16 = [self.compute[offs[i]:offs[i] + sizes[i]].view(dims[i]) for i in range(nl)]
         self.dw = [self.grads[offs[i]:offs[i] + sizes[i]].view(dims[i]) for i in range(nl)]
@@ -157,7 +173,7 @@ class MlpTrainer:
         # backward
         # dW_out[k, V] = h_last^T [k, B] * dlogits [B, V]: A stored [B, k] read transposed
         self._gemm(inp, self.dlogits16, self.dw[nh], k, V, B, True, False, k, V)
-        self._start_allreduce(self.dw[nh])
+        self._start_reduce(nh)
         # dh_last[B, k] = dlogits [B, V] * W_out^T: B operand stored [k, V] = [N_gemm, K_gemm]
         self._gemm(self.dlogits16, self.w16[nh], self.dh, B, k, V, False, True, V, V)
         for l in range(nh - 1, -1, -1):
@@ -169,24 +185,28 @@ class MlpTrainer:
                                             self.dz16.data_ptr(), self.dgamma[l].data_ptr(), self.scratch.data_ptr(),
                                             self.scratch_bytes, B, n, cfg.eps, 1))
             self._gemm(prev, self.dz16, self.dw[l], k, n, B, True, False, k, n)
-            self._start_allreduce(self.dw[l])
+            self._start_reduce(l)
             if l > 0:
                 self._gemm(self.dz16, self.w16[l], self.dh, B, k, n, False, True, n, n)
         if self.world > 1:
-            # the small gamma gradients go last, in one piece
-            g0 = self.dgamma[0]
-            flat = self.grads[g0.storage_offset():g0.storage_offset() + sum(cfg.hidden)]
-            self._start_allreduce(flat)
-        self._finish_allreduce()
+            self._start_reduce(len(self.w))      # the small gamma gradients go last, in one piece
+        self._finish_reduce()
 
-    def _start_allreduce(self, tensor):
+    def _start_reduce(self, unit: int):
+        """Start the exchange of one unit's gradient: all-reduce (replicated optimizer) or reduce-scatter (sharded)."""
         if self.world == 1:
             return
         import torch.distributed as dist
 
-        self._pending.append(dist.all_reduce(tensor, op=dist.ReduceOp.SUM, group=self.group, async_op=True))
+        off, n = self._units[unit]
+        flat = self.grads[off:off + n]
+        if self.sharded:
+            w = dist.reduce_scatter_tensor(self.grad_shards[unit], flat, op=dist.ReduceOp.SUM, group=self.group, async_op=True)
+        else:
+            w = dist.all_reduce(flat, op=dist.ReduceOp.SUM, group=self.group, async_op=True)
+        self._pending.append(w)
 
-    def _finish_allreduce(self):
+    def _finish_reduce(self):
         for w in self._pending:
             w.wait()
         self._pending = []
@@ -194,10 +214,44 @@ class MlpTrainer:
     def optimizer_step(self):
         cfg = self.cfg
         self.step_count += 1
-        self._ck(self.L.t0b_adamw_step(self.rt.handle, self.master.data_ptr(), self.grads.data_ptr(),
-                                       self.adam_m.data_ptr(), self.adam_v.data_ptr(), self.compute.data_ptr(),
-                                       self.n_params, cfg.lr, cfg.beta1, cfg.beta2, cfg.adam_eps, cfg.weight_decay,
-                                       self.step_count, 1.0, 1))
+        if not self.sharded:
+            self._ck(self.L.t0b_adamw_step(self.rt.handle, self.master.data_ptr(), self.grads.data_ptr(),
+                                           self.adam_m.data_ptr(), self.adam_v.data_ptr(), self.compute.data_ptr(),
+                                           self.n_params, cfg.lr, cfg.beta1, cfg.beta2, cfg.adam_eps, cfg.weight_decay,
+                                           self.step_count, 1.0, 1))
+            return
+        import torch.distributed as dist
+
+        gamma_unit = len(self.w)
+        works = []
+        for u, (off, n) in enumerate(self._units):
+            ns = n // self.world
+            lo = off + self.rank * ns
+            own_master, own_bf16 = self.master[lo:lo + ns], self.compute[lo:lo + ns]
+            self._ck(self.L.t0b_adamw_step(self.rt.handle, own_master.data_ptr(), self.grad_shards[u].data_ptr(),
+                                           self.m_shards[u].data_ptr(), self.v_shards[u].data_ptr(), own_bf16.data_ptr(), ns,
+                                           cfg.lr, cfg.beta1, cfg.beta2, cfg.adam_eps, cfg.weight_decay, self.step_count, 1.0, 1))
+            # Every rank's slice sits at its own offset of the full buffer, so the gather is in place.  The GEMMs read
+            # the bf16 copies; RMSNorm reads the f32 gammas, so that unit is gathered in f32.
+            if u == gamma_unit:
+                works.append(dist.all_gather_into_tensor(self.master[off:off + n], own_master, group=self.group, async_op=True))
+            else:
+                works.append(dist.all_gather_into_tensor(self.compute[off:off + n], own_bf16, group=self.group, async_op=True))
+        for w in works:
+            w.wait()
+
+    def gather_master(self):
+        """The full f32 master parameters (sharded optimizer: assembled from every rank's slices)."""
+        if not self.sharded:
+            return self.master.clone()
+        import torch.distributed as dist
+
+        out = self.master.clone()
+        for off, n in self._units:
+            ns = n // self.world
+            dist.all_gather_into_tensor(out[off:off + n], self.master[off + self.rank * ns:off + (self.rank + 1) * ns].clone(),
+                                        group=self.group)
+        return out
 
     def step(self, x, targets):
         self.forward_backward(x, targets)

@@ -169,3 +169,64 @@ def test_data_parallel_two_ranks_match_one(rt):
     grads1 = tr.grads.cpu().numpy()
     assert abs(loss2 - tr.mean_loss()) <= 1e-5 * abs(loss2) + 1e-6
     assert rel_fro(grads2, grads1) <= 1e-3
+
+
+def _sharded_worker(rank, world, port, q):
+    import torch
+    import torch.distributed as dist
+    import t0_gpu_b200 as t
+    from t0_gpu_b200.mlp import MlpConfig, MlpTrainer
+
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world,
+                            device_id=torch.device("cuda", rank))
+    rt = t.GpuRuntime(rank)
+    cfg = MlpConfig(d_in=256, hidden=[256, 256, 256], n_classes=512)
+    rows_total = 128
+    rows = rows_total // world
+    g = torch.Generator(device="cuda"); g.manual_seed(7)
+    x = torch.randn((rows_total, 256), generator=g, device="cuda")[rank * rows:(rank + 1) * rows].contiguous()
+    g2 = torch.Generator(device="cuda"); g2.manual_seed(8)
+    tg = torch.randint(0, 512, (rows_total,), generator=g2, device="cuda", dtype=torch.int32)[rank * rows:(rank + 1) * rows].contiguous()
+    out = {}
+    for mode in (False, True):
+        tr = MlpTrainer(rt, cfg, rows, rows_total=rows_total, shard_optimizer=mode)
+        assert tr.sharded == mode
+        losses = []
+        for _ in range(3):
+            tr.step(x, tg)
+            losses.append(tr.mean_loss())
+        rt.synchronize()
+        out[mode] = (losses, tr.gather_master().cpu().numpy(), tr.compute.view(torch.int16).cpu().numpy())
+    if rank == 0:
+        q.put(out)
+    dist.barrier()
+    dist.destroy_process_group()
+    rt.close()
+
+
+def test_sharded_optimizer_matches_replicated_optimizer():
+    """Reduce-scatter + per-rank AdamW on a slice + all-gather gives the parameters of all-reduce + replicated AdamW:
+    with two ranks every gradient sum has two terms, so the results are the same bits."""
+    import torch
+
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_sharded_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    out = q.get(timeout=300)
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    (loss_r, master_r, bf16_r), (loss_s, master_s, bf16_s) = out[False], out[True]
+    assert loss_r == loss_s and loss_r[2] < loss_r[0]
+    assert np.array_equal(master_r, master_s)
+    n_weights = 256 * 256 * 3 + 256 * 512        # the bf16 copies of the gammas (the tail) are not used by any kernel
+    assert np.array_equal(bf16_r[:n_weights], bf16_s[:n_weights])
