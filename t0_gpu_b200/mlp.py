@@ -93,13 +93,26 @@ class MlpTrainer:
             offs.append(o)
             o += s
         nl = len(dims)
-        # Units of the gradient exchange: one per weight matrix, and one for all gammas together (stored consecutively).
-        self._units = [(offs[i], sizes[i]) for i in range(nl)] + [(offs[nl], sum(cfg.hidden))]
+        # Units of the gradient exchange: one per weight matrix (the output layer's, by far the largest, in row panels
+        # when the optimizer is sharded, so that its exchange starts after the first panel's GEMM instead of after the
+        # whole gradient), and one for all gammas together (stored consecutively).
+        want_shard = bool(shard_optimizer) and self.world > 1
+        self._units, self._layer_units = [], []
+        for i, (k_i, n_i) in enumerate(dims):
+            panels = 4 if (want_shard and i == nl - 1 and k_i % 4 == 0) else 1
+            per = k_i // panels
+            ids = []
+            for pnl in range(panels):
+                ids.append(len(self._units))
+                self._units.append((offs[i] + pnl * per * n_i, per * n_i))
+            self._layer_units.append(ids)
+        self._gamma_unit = len(self._units)
+        self._units.append((offs[nl], sum(cfg.hidden)))
         # Sharded optimizer (more than one rank): every unit's gradient is reduce-scattered instead of all-reduced, each
         # rank keeps AdamW state for, and updates, its 1/world slice of every unit, and the updated bf16 copies (f32
         # for the gammas) are all-gathered.  Per rank this moves half the gradient bytes over NVLink, a 1/world share
         # of the AdamW traffic through HBM, and the same arithmetic per element as the replicated update.
-        self.sharded = bool(shard_optimizer) and self.world > 1 and all(n % self.world == 0 for _, n in self._units)
+        self.sharded = want_shard and all(n % self.world == 0 for _, n in self._units)
         if self.sharded:
             self.rank = dist.get_rank(group)
             self.grad_shards = [torch.empty(n // self.world, dtype=f32, device=self.dev) for _, n in self._units]
@@ -132,6 +145,7 @@ class MlpTrainer:
         self.scratch = torch.empty(self.scratch_bytes, dtype=torch.uint8, device=self.dev)
         self.step_count = 0
         self._pending = []
+        self._updates = {}
 
     # ------------------------------------------------------------------ helpers (each one C-ABI call)
     def _ck(self, rc):
@@ -158,22 +172,28 @@ class MlpTrainer:
         # forward
         self._cast(x, self.x16, B * cfg.d_in)
         inp, k = self.x16, cfg.d_in
+        self._wait_update(self._gamma_unit)      # gammas (read by every RMSNorm)
         for l in range(nh):
             n = cfg.hidden[l]
+            self._wait_layer(l)
             self._gemm(inp, self.w16[l], self.z[l], B, n, k, False, False, k, n)
             # RMSNorm, SiLU and the bf16 down-cast in one pass over z (the f32 intermediates never reach memory)
             self._ck(L.t0b_rmsnorm_silu_fwd(h, self.z[l].data_ptr(), self.gamma[l].data_ptr(), self.h16[l].data_ptr(), 0, B, n,
                                             cfg.eps, 1))
             inp, k = self.h16[l], n
         V = cfg.n_classes
+        self._wait_layer(nh)
         self._gemm(inp, self.w16[nh], self.logits, B, V, k, False, False, k, V)
         # loss and its gradient, stored directly as the bf16 operand of the two GEMMs that follow
         self._ck(L.t0b_softmax_ce_bf16(h, self.logits.data_ptr(), targets.data_ptr(), self.losses.data_ptr(),
                                        self.dlogits16.data_ptr(), B, V, V, scale, 1))
         # backward
         # dW_out[k, V] = h_last^T [k, B] * dlogits [B, V]: A stored [B, k] read transposed
-        self._gemm(inp, self.dlogits16, self.dw[nh], k, V, B, True, False, k, V)
-        self._start_reduce(nh)
+        ids = self._layer_units[nh]
+        per = k // len(ids)                     # rows of dW_out per panel = columns of h_last
+        for pnl, u in enumerate(ids):
+            self._gemm(inp[:, pnl * per:], self.dlogits16, self.dw[nh][pnl * per:], per, V, B, True, False, k, V)
+            self._start_reduce(u)
         # dh_last[B, k] = dlogits [B, V] * W_out^T: B operand stored [k, V] = [N_gemm, K_gemm]
         self._gemm(self.dlogits16, self.w16[nh], self.dh, B, k, V, False, True, V, V)
         for l in range(nh - 1, -1, -1):
@@ -185,11 +205,11 @@ class MlpTrainer:
                                             self.dz16.data_ptr(), self.dgamma[l].data_ptr(), self.scratch.data_ptr(),
                                             self.scratch_bytes, B, n, cfg.eps, 1))
             self._gemm(prev, self.dz16, self.dw[l], k, n, B, True, False, k, n)
-            self._start_reduce(l)
+            self._start_reduce(self._layer_units[l][0])
             if l > 0:
                 self._gemm(self.dz16, self.w16[l], self.dh, B, k, n, False, True, n, n)
         if self.world > 1:
-            self._start_reduce(len(self.w))      # the small gamma gradients go last, in one piece
+            self._start_reduce(self._gamma_unit) # the small gamma gradients go last, in one piece
         self._finish_reduce()
 
     def _start_reduce(self, unit: int):
@@ -222,9 +242,12 @@ class MlpTrainer:
             return
         import torch.distributed as dist
 
-        gamma_unit = len(self.w)
-        works = []
-        for u, (off, n) in enumerate(self._units):
+        gamma_unit = self._gamma_unit
+        # Units are updated and gathered in the order the next forward pass needs them (gammas, then the layers); the
+        # forward pass waits for a unit right before its first use, so the gathers of the later (larger) layers run
+        # behind the GEMMs of the earlier ones.
+        for u in [gamma_unit] + list(range(gamma_unit)):   # unit ids follow the layer order
+            off, n = self._units[u]
             ns = n // self.world
             lo = off + self.rank * ns
             own_master, own_bf16 = self.master[lo:lo + ns], self.compute[lo:lo + ns]
@@ -234,11 +257,24 @@ class MlpTrainer:
             # Every rank's slice sits at its own offset of the full buffer, so the gather is in place.  The GEMMs read
             # the bf16 copies; RMSNorm reads the f32 gammas, so that unit is gathered in f32.
             if u == gamma_unit:
-                works.append(dist.all_gather_into_tensor(self.master[off:off + n], own_master, group=self.group, async_op=True))
+                self._updates[u] = dist.all_gather_into_tensor(self.master[off:off + n], own_master, group=self.group, async_op=True)
             else:
-                works.append(dist.all_gather_into_tensor(self.compute[off:off + n], own_bf16, group=self.group, async_op=True))
-        for w in works:
+                self._updates[u] = dist.all_gather_into_tensor(self.compute[off:off + n], own_bf16, group=self.group, async_op=True)
+
+    def _wait_update(self, unit: int):
+        """Make the stream wait for the all-gather that delivers `unit`'s updated parameters (sharded optimizer)."""
+        w = self._updates.pop(unit, None)
+        if w is not None:
             w.wait()
+
+    def _wait_layer(self, layer: int):
+        for u in self._layer_units[layer]:
+            self._wait_update(u)
+
+    def finish_updates(self):
+        """Wait for every outstanding parameter gather (before reading `compute` or the gammas from outside a step)."""
+        for u in list(self._updates):
+            self._wait_update(u)
 
     def gather_master(self):
         """The full f32 master parameters (sharded optimizer: assembled from every rank's slices)."""
@@ -246,6 +282,7 @@ class MlpTrainer:
             return self.master.clone()
         import torch.distributed as dist
 
+        self.finish_updates()
         out = self.master.clone()
         for off, n in self._units:
             ns = n // self.world
