@@ -151,6 +151,10 @@ T0B_API const char* t0b_last_error(t0b_ctx* ctx);
 /* GpuRuntime::is_poisoned(), gpu_context.rs:149-157. */
 T0B_API int32_t t0b_is_poisoned(t0b_ctx* ctx);
 T0B_API int32_t t0b_num_sms(t0b_ctx* ctx);
+/* The GEMM kernels are persistent: by default one CTA (or CTA pair) per SM, which leaves a concurrently running
+ * kernel on another stream -- a collective of the data-parallel step -- no SM until the GEMM ends.  With a limit the
+ * GEMMs occupy at most `sms` SMs (0 = all).  No reference counterpart (single GPU, one queue). */
+T0B_API int32_t t0b_set_sm_limit(t0b_ctx* ctx, int32_t sms);
 /* Device status word written by kernels whose bounded waits ran out (101..105) or that met an index outside its
  * table (110); 0 = none.  A synchronous call that finds it set returns T0B_ERR_DEVICE.  Reading clears it when
  * `clear` is non-zero.  Takes the place of the reference's wait_read_ptr timeout (src/kfd/mod.rs:1607-1642). */

@@ -63,6 +63,7 @@ SIGNATURES = {
     "t0b_last_error": (C.c_char_p, [_ctx]),
     "t0b_is_poisoned": (_i32, [_ctx]),
     "t0b_num_sms": (_i32, [_ctx]),
+    "t0b_set_sm_limit": (_i32, [_ctx, _i32]),
     "t0b_device_status": (_i32, [_ctx, _i32]),
     "t0b_set_wait_limit_ns": (_i32, [_ctx, _u64]),
     "t0b_alloc": (_i32, [_ctx, _sz, C.POINTER(_u64)]),

@@ -48,7 +48,9 @@ int32_t launch_variant(t0b_ctx* ctx, const CUtensorMap& ta, const CUtensorMap& t
         }
         configured[dev] = true;
     }
-    const int clusters = std::max(1, std::min(num_work, max_clusters[dev]));
+    int avail = max_clusters[dev];
+    if (ctx->sm_limit > 0) avail = std::min(avail, std::max(1, ctx->sm_limit / CG));   // leave SMs to concurrent kernels
+    const int clusters = std::max(1, std::min(num_work, avail));
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(clusters * CG, 1, 1);
     cfg.blockDim = dim3(T::kThreads, 1, 1);

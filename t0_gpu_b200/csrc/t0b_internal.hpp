@@ -17,6 +17,7 @@
 struct t0b_ctx {
     int device = 0;
     int num_sms = 148;
+    int sm_limit = 0;           // > 0: the persistent GEMM kernels occupy at most this many SMs
     cudaStream_t own_stream = nullptr;
     cudaStream_t stream = nullptr;
     std::recursive_mutex mu;

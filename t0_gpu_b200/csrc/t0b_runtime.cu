@@ -131,6 +131,14 @@ int32_t t0b_is_poisoned(t0b_ctx* ctx) { return ctx && ctx->poisoned ? 1 : 0; }
 
 int32_t t0b_num_sms(t0b_ctx* ctx) { return ctx ? ctx->num_sms : 0; }
 
+int32_t t0b_set_sm_limit(t0b_ctx* ctx, int32_t sms) {
+    if (!ctx) return T0B_ERR_INVALID;
+    if (sms < 0 || sms > ctx->num_sms) return set_error(ctx, T0B_ERR_INVALID, "set_sm_limit: %d is outside 0..%d", sms, ctx->num_sms);
+    std::lock_guard<std::recursive_mutex> lk(ctx->mu);
+    ctx->sm_limit = sms;
+    return T0B_OK;
+}
+
 int32_t t0b_device_status(t0b_ctx* ctx, int32_t clear) {
     if (!ctx || !ctx->status_host) return 0;
     const int st = *reinterpret_cast<volatile int*>(ctx->status_host);

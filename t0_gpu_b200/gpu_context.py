@@ -105,6 +105,10 @@ class GpuRuntime:
     def num_sms(self) -> int:
         return lib().t0b_num_sms(self._ctx)
 
+    def set_sm_limit(self, sms: int) -> None:
+        """GEMM kernels occupy at most `sms` SMs (0 = all), leaving the rest to kernels running beside them."""
+        self._check(lib().t0b_set_sm_limit(self._ctx, sms))
+
     def is_poisoned(self) -> bool:
         return bool(lib().t0b_is_poisoned(self._ctx))
 

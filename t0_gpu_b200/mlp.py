@@ -80,6 +80,14 @@ class MlpTrainer:
         else:
             self.stream = torch.cuda.current_stream()
         rt.set_stream(self.stream.cuda_stream)
+        # With several ranks the collectives run beside the persistent GEMMs.  T0B_COMM_SMS=n keeps n SMs out of the
+        # GEMMs' grids for them; measured on two GPUs it does not pay (step 2.53 ms with 0, 2.55-2.62 ms with 8-32),
+        # so the default is 0.
+        if self.world > 1:
+            import os
+            spare = int(os.environ.get("T0B_COMM_SMS", "0"))
+            if spare > 0:
+                rt.set_sm_limit(max(2, rt.num_sms() - spare))
         dims = cfg.dims()
         f32, bf16 = torch.float32, torch.bfloat16
         # Parameters: W_l stored [fan_in, fan_out] (row-major [K, N], the layout `Linear` uses), gamma_l = 1.
