@@ -148,3 +148,22 @@ def test_gemm_tuner_and_auto_gemm(rt, tmp_path, monkeypatch):
     ref = oracle.gemm_bf16(A, Bt, m, n, k, threads=8)
     assert np.linalg.norm(got - ref) <= 5e-3 * np.linalg.norm(ref)
     lib().t0b_set_autotune_dir(rt.handle, b"")       # back to the default for the tests that follow
+
+
+def test_sm_limit_changes_the_grid_not_the_result(rt):
+    """t0b_set_sm_limit caps the SMs of the persistent GEMM grids (room for a collective running beside them); the
+    tiles are the same, so the product has the same bits."""
+    m, n, k = 1024, 1536, 512
+    A = oracle.rand_bf16(m * k, 41).reshape(m, k)
+    Bt = oracle.rand_bf16(n * k, 42).reshape(n, k)
+    da, db, dc = rt.upload(A), rt.upload(Bt), rt.alloc(m * n * 4)
+    outs = []
+    for limit in (0, 64, 2, 0):
+        rt.set_sm_limit(limit)
+        for cfg in (None, t.GemmConfig.preset("b200_256x256"), t.GemmConfig.preset("b200_128x128")):
+            rt.gemm(da, db, dc, m, n, k, cfg=cfg)
+            outs.append(dc.read_as(np.float32, m * n))
+    for o in outs[1:]:
+        assert np.array_equal(o, outs[0])
+    assert lib().t0b_set_sm_limit(rt.handle, -1) == -1 and lib().t0b_set_sm_limit(rt.handle, 100000) == -1
+    rt.set_sm_limit(0)
