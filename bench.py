@@ -345,6 +345,28 @@ def run_single(args, local_rank):
             f()
         t_ms = time_steps(torch, f, max(args.steps, 20), stream)
         also[f"square_{s}_nn_f32out"] = {"ms": t_ms, "tflops": 2.0 * s ** 3 / (t_ms * 1e-3) / 1e12}
+    # 256^3 is launch-bound: time it as a stream of launches and as one CUDA graph of 64 launches replayed.
+    import ctypes as C
+    s = 256
+    aa, bb = a[:s, :s].contiguous(), b[:s, :s].contiguous()
+    ccs = [torch.empty((s, s), dtype=torch.float32, device=dev) for _ in range(64)]
+    f = lambda: gemm(aa, bb, ccs[0], s, s, s)
+    for _ in range(3):
+        f()
+    t_stream = time_steps(torch, f, 200, stream)
+    rt._check(L.t0b_graph_begin(rt.handle))
+    for cc in ccs:
+        gemm(aa, bb, cc, s, s, s)
+    gh = C.c_uint64()
+    rt._check(L.t0b_graph_end(rt.handle, C.byref(gh)))
+    replay = lambda: rt._check(L.t0b_graph_launch(rt.handle, gh.value, 1))
+    for _ in range(3):
+        replay()
+    t_graph = time_steps(torch, replay, 20, stream) / len(ccs)
+    rt._check(L.t0b_graph_destroy(rt.handle, gh.value))
+    also["square_256_nn_f32out"] = {"us_per_gemm_stream": t_stream * 1e3, "us_per_gemm_graph_of_64": t_graph * 1e3,
+                                    "tflops_graph": 2.0 * s ** 3 / (t_graph * 1e-3) / 1e12}
+    del ccs
     if not args.quick:
         bm, bn, bk = 32768, 32768, 8192
         a4 = device_normal_bf16(torch, (bm, bk), 4321, 1.0 / bk ** 0.5, dev)
