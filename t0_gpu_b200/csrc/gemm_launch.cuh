@@ -56,13 +56,17 @@ int32_t launch_variant(t0b_ctx* ctx, const CUtensorMap& ta, const CUtensorMap& t
     cfg.blockDim = dim3(T::kThreads, 1, 1);
     cfg.dynamicSmemBytes = T::kSmemBytes;
     cfg.stream = ctx->stream;
-    cudaLaunchAttribute attrs[1];
+    cudaLaunchAttribute attrs[2];
     attrs[0].id = cudaLaunchAttributeClusterDimension;
     attrs[0].val.clusterDim.x = CG;
     attrs[0].val.clusterDim.y = 1;
     attrs[0].val.clusterDim.z = 1;
+    // The kernel's set-up (barriers, TMEM allocation) overlaps the tail of the previous kernel in the stream; the
+    // kernel itself waits (griddepcontrol.wait) before its first access to global memory.
+    attrs[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attrs[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attrs;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = ctx->pdl ? 2 : 1;
     return check_cuda(ctx, cudaLaunchKernelEx(&cfg, kfn, ta, tb, tc, p), "cudaLaunchKernelEx(gemm)");
 }
 

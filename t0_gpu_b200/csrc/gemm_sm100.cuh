@@ -360,6 +360,10 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
     }
     ptx::tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    // Programmatic dependent launch: everything above (barriers, TMEM, descriptor prefetch) may run while the previous
+    // kernel of the stream drains; nothing below may touch global memory before that kernel has completed.
+    ptx::grid_dependency_wait();
+    ptx::grid_launch_dependents();   // the next GEMM's CTAs may take over SMs as this grid's CTAs exit
 
     const WaitCtl ctl{abort_flag, p.status, p.wait_limit_ns};
     const int num_work = p.tiles_m * p.tiles_n * p.split_k;

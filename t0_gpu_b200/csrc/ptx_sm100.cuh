@@ -204,5 +204,12 @@ __device__ __forceinline__ void tmem_ld_wait_regs(uint32_t (&v)[32]) {
                  : "memory");
 }
 
+// Programmatic dependent launch: wait until the grids this one depends on have completed and their writes are visible.
+// A no-op when the kernel was launched without the programmatic-serialization attribute.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+// Let the next kernel of the stream (if it was launched with programmatic serialization) be scheduled as soon as every
+// CTA of this grid has got here; it still waits for this grid's completion before touching memory.
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 }  // namespace ptx
 }  // namespace t0b

@@ -17,6 +17,7 @@
 struct t0b_ctx {
     int device = 0;
     int num_sms = 148;
+    bool pdl = true;            // launch GEMMs with programmatic stream serialization (T0B_PDL=0 turns it off)
     int sm_limit = 0;           // > 0: the persistent GEMM kernels occupy at most this many SMs
     cudaStream_t own_stream = nullptr;
     cudaStream_t stream = nullptr;

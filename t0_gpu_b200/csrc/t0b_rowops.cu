@@ -10,6 +10,7 @@
 #include <cfloat>
 #include <cstdlib>
 
+#include "ptx_sm100.cuh"
 #include "t0b_internal.hpp"
 
 using namespace t0b;
@@ -79,6 +80,7 @@ __device__ __forceinline__ void block_online(float& m, float& s, float* red) {
 
 __global__ void __launch_bounds__(256) cast_f32_bf16_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst,
                                                             size_t n) {
+    ptx::grid_launch_dependents();
     const size_t n4 = n / 4;
     const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
     const bool vec = ((reinterpret_cast<uintptr_t>(src) & 15) == 0) && ((reinterpret_cast<uintptr_t>(dst) & 7) == 0);
@@ -176,6 +178,7 @@ template <int VPT, bool SILU16 = false>
 __global__ void __launch_bounds__(kRowThreads, VPT <= 2 ? 4 : 1) rmsnorm_fwd_reg_kernel(const float* __restrict__ x, const float* __restrict__ w,
                                                                       void* __restrict__ y, float* __restrict__ inv_rms,
                                                                       uint32_t rows, uint32_t cols, float eps) {
+    ptx::grid_launch_dependents();
     __shared__ float red[64];
     const uint32_t n4 = cols / 4;
     float4 wv[VPT];
@@ -277,6 +280,7 @@ __global__ void __launch_bounds__(256) rmsnorm_dgamma_partial_kernel(const float
 // 8th partial row (ascending), then warp 0 adds the 8 sums in warp order.  Launch with kDgammaFinalGrid(cols) blocks.
 __global__ void __launch_bounds__(256) rmsnorm_dgamma_final_kernel(const float* __restrict__ partial, float* __restrict__ dgamma,
                                                                    uint32_t cols, uint32_t nblocks) {
+    ptx::grid_launch_dependents();
     __shared__ float part[8][32];
     const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const uint32_t c = blockIdx.x * 32 + lane;
@@ -309,6 +313,7 @@ __global__ void __launch_bounds__(kRowThreads) rmsnorm_bwd_fused_kernel(const fl
                                                                         const float* __restrict__ w, void* __restrict__ dx,
                                                                         float* __restrict__ partial, uint32_t rows,
                                                                         uint32_t cols, float eps) {
+    ptx::grid_launch_dependents();
     __shared__ float red[64];
     const uint32_t n4 = cols / 4;
     float4 wv[VPT], acc[VPT];
@@ -487,6 +492,7 @@ __global__ void __launch_bounds__(kRowThreads) softmax_ce_kernel(const float* __
                                                                  const uint32_t* __restrict__ targets,
                                                                  float* __restrict__ losses, void* __restrict__ dlogits,
                                                                  uint32_t cols, size_t ld, float scale) {
+    ptx::grid_launch_dependents();
     extern __shared__ __align__(16) float cache[];
     __shared__ float red[64];
     const size_t row = blockIdx.x;
@@ -541,6 +547,7 @@ __global__ void __launch_bounds__(kRowThreads) softmax_ce_kernel(const float* __
 
 __global__ void __launch_bounds__(256) silu_gate_fwd_kernel(const float* __restrict__ gate, const float* __restrict__ up,
                                                             float* __restrict__ out, size_t n) {
+    ptx::grid_launch_dependents();
     const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
     const size_t i0 = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x;
     const bool vec = ((reinterpret_cast<uintptr_t>(gate) & 15) == 0) && ((reinterpret_cast<uintptr_t>(out) & 15) == 0) &&
@@ -566,6 +573,7 @@ __global__ void __launch_bounds__(256) silu_gate_fwd_kernel(const float* __restr
 __global__ void __launch_bounds__(256) silu_gate_bwd_kernel(const float* __restrict__ grad, const float* __restrict__ gate,
                                                             const float* __restrict__ up, float* __restrict__ dgate,
                                                             float* __restrict__ dup, size_t n) {
+    ptx::grid_launch_dependents();
     const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
     const size_t i0 = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x;
     const bool vec = ((reinterpret_cast<uintptr_t>(grad) & 15) == 0) && ((reinterpret_cast<uintptr_t>(gate) & 15) == 0) &&
@@ -626,6 +634,7 @@ __global__ void __launch_bounds__(256) adamw_kernel(float* __restrict__ p, const
                                                     float* __restrict__ v, __nv_bfloat16* __restrict__ p_bf16, size_t n,
                                                     float lr, float beta1, float beta2, float eps, float wd, float bc1,
                                                     float bc2, float grad_scale) {
+    ptx::grid_launch_dependents();
     const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
     const size_t i0 = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x;
     const bool vec = (((reinterpret_cast<uintptr_t>(p) | reinterpret_cast<uintptr_t>(g) | reinterpret_cast<uintptr_t>(m) |
