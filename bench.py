@@ -572,6 +572,70 @@ def run_multi(args, rank, local_rank, world):
     dist.destroy_process_group()
 
 
+def run_mlp(args, rank, local_rank, world):
+    """--workload mlp: the data-parallel MLP training step of the fifth benchmark config (1024 rows per GPU,
+    4096 -> 3 x [Linear 4096, RMSNorm, SiLU] -> Linear 32000 -> cross-entropy, AdamW), weak scaling over the ranks.
+    A step = forward, backward, gradient exchange and optimizer update.  Inputs are resident; the value counts the
+    GEMM FLOPs of forward and backward over all ranks."""
+    import torch
+    import torch.distributed as dist
+
+    import t0_gpu_b200 as t
+    from t0_gpu_b200.mlp import MlpConfig, MlpTrainer
+
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    rt = t.GpuRuntime(local_rank)
+    cfg = MlpConfig()
+    rows = 1024
+    tr = MlpTrainer(rt, cfg, rows, rows_total=rows * world, shard_optimizer=not args.replicated_optimizer)
+    g = torch.Generator(device=dev)
+    g.manual_seed(7 + rank)
+    x = torch.randn((rows, cfg.d_in), generator=g, device=dev)
+    tg = torch.randint(0, cfg.n_classes, (rows,), generator=g, device=dev, dtype=torch.int32)
+
+    def timed(fn, steps):
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        ms = time_steps(torch, fn, steps, tr.stream)
+        if world > 1:
+            tms = torch.tensor([ms], device=dev)
+            dist.all_reduce(tms, op=dist.ReduceOp.MAX)
+            dist.barrier()
+            ms = tms.item()
+        return ms
+
+    step = lambda: tr.step(x, tg)
+    for _ in range(max(args.warmup, 3)):
+        step()
+    sampler = ClockSampler(physical_gpu_index(local_rank))
+    launches0 = rt.launch_count()
+    sampler.start()
+    ms = timed(step, args.steps)
+    clocks = sampler.stop()
+    launches = rt.launch_count() - launches0
+    ms_fb = timed(lambda: tr.forward_backward(x, tg), max(3, min(args.steps, 10)))
+    loss = tr.mean_loss()
+    flops = cfg.flops_per_row() * rows * world
+    if rank == 0:
+        print(json.dumps({
+            "metric": "MLP training step, GEMM TFLOP/s (forward + backward FLOPs / step time)", "value": flops / (ms * 1e-3) / 1e12,
+            "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": "mlp_step_4096x3_32000_rows1024_per_gpu", "rows_per_gpu": rows, "global_batch": rows * world,
+                       "optimizer": "AdamW, " + ("sharded over the ranks (reduce-scatter, all-gather)" if tr.sharded else
+                                                 ("replicated (all-reduce)" if world > 1 else "single rank")),
+                       "l2": "weights 363 MB bf16 + 726 MB f32 master per step > L2, no flush"},
+            "fwd_bwd_ms": ms_fb, "loss": loss, "clocks": clocks, "gpu_launches": launches,
+        }))
+    if world > 1:
+        dist.destroy_process_group()
+    rt.close()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -580,6 +644,10 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--quick", action="store_true", help="skip the 32768^2 single-GPU context measurement")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--workload", default="gemm", choices=["gemm", "mlp"],
+                    help="gemm: the headline GEMM (default); mlp: the data-parallel MLP training step")
+    ap.add_argument("--replicated-optimizer", action="store_true",
+                    help="--workload mlp on several GPUs: all-reduce + replicated AdamW instead of the sharded optimizer")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -589,6 +657,9 @@ def main():
         return
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    if args.workload == "mlp":
+        run_mlp(args, rank, local_rank, world)
+    elif world > 1:
         run_multi(args, rank, local_rank, world)
     else:
         run_single(args, local_rank)
