@@ -64,7 +64,7 @@ class MlpTrainer:
     """One data-parallel replica.  `rows` is this rank's share of the batch, `rows_total` the global batch."""
 
     def __init__(self, rt: GpuRuntime, cfg: MlpConfig, rows: int, rows_total: Optional[int] = None, group=None,
-                 seed: int = 100, shard_optimizer: bool = False):
+                 seed: int = 100, shard_optimizer: bool = False, autotune: bool = True):
         import torch
         import torch.distributed as dist
 
@@ -154,6 +154,26 @@ class MlpTrainer:
         self.step_count = 0
         self._pending = []
         self._updates = {}
+        if autotune:
+            self._tune_gemms()
+
+    def _tune_gemms(self):
+        """Measure the tile candidates for every GEMM shape of the step once (the reference's `auto_gemm` does the same
+        on first use, src/t0/auto_gemm.rs:445-480); config-less GEMM calls of these shapes then use the winners."""
+        cfg, B = self.cfg, self.rows
+        shapes = set()
+        k = cfg.d_in
+        for n in cfg.hidden:
+            shapes.add((B, n, k, False, False))          # forward
+            shapes.add((k, n, B, True, False))           # dW
+            shapes.add((B, k, n, False, True))           # dX
+            k = n
+        V = cfg.n_classes
+        shapes.add((B, V, k, False, False))
+        shapes.add((k // len(self._layer_units[-1]), V, B, True, False))
+        shapes.add((B, k, V, False, True))
+        for (m, n, kk, ta, tb) in sorted(shapes):
+            self.rt.tune(m, n, kk, trans_a=ta, trans_b=tb)
 
     # ------------------------------------------------------------------ helpers (each one C-ABI call)
     def _ck(self, rc):
