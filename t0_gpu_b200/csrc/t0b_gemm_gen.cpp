@@ -117,7 +117,7 @@ void default_b200_config(uint32_t m, uint32_t k, uint32_t n, int num_sms, t0b_ge
     };
     static const Cand cands[] = {
         {256, 512, 2, 1165.0, 10000.0, 0.0}, {512, 256, 2, 1175.0, 10000.0, 0.0}, {256, 256, 2, 650.0, 0.0, 8000.0},
-        {128, 256, 1, 640.0, 0.0, 8000.0},   {128, 128, 1, 700.0, 0.0, 5000.0},   {128, 64, 1, 550.0, 0.0, 3500.0},
+        {128, 256, 1, 700.0, 0.0, 8000.0},   {128, 128, 1, 700.0, 0.0, 5000.0},   {128, 64, 1, 550.0, 0.0, 3500.0},
     };
     if (num_sms <= 0) num_sms = 148;
     const uint32_t kb_total = std::max(1u, (k + 63) / 64);
