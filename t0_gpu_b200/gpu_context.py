@@ -203,6 +203,12 @@ class GpuRuntime:
     def dispatch_async(self, kernel, grid, kernargs: bytes) -> None:
         self._dispatch(kernel, grid, kernargs, True)
 
+    def dispatch_bench(self, kernel, grid, kernargs: bytes) -> None:
+        """`GpuRuntime::dispatch_bench` (gpu_context.rs:297-307): the reference's low-overhead submit + spin-wait for
+        benchmarks.  A stream launch followed by a stream synchronise has no cheaper form here, so it is `dispatch`;
+        batches are better timed with `gemm_time` or a captured graph."""
+        self._dispatch(kernel, grid, kernargs, False)
+
     def _dispatch(self, kernel, grid, kernargs, async_):
         blob = (C.c_uint8 * len(kernargs)).from_buffer_copy(kernargs)
         spec = getattr(kernel, "spec", None)
