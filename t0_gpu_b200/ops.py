@@ -67,6 +67,18 @@ def matmul(rt: GpuRuntime, x: GpuBuffer, w: GpuBuffer, m: int, k: int, n: int):
     return y, backward
 
 
+def matmul_with_wt_bf16(rt: GpuRuntime, x: GpuBuffer, wt_bf16: GpuBuffer, m: int, k: int, n: int) -> GpuBuffer:
+    """`ops::bf16_matmul::matmul_with_wt_bf16` (bf16_matmul.rs:102-134): Y[M,N] f32 = X[M,K] f32 (cast to bf16 on the
+    device) times a weight already stored transposed as bf16 WT[N,K] -- the inference / repeated-forward form.
+    No padding of M or N is needed."""
+    x16 = _bf16_of(rt, x, m * k)
+    y = rt.alloc(max(m * n * 4, 16))
+    rt.gemm(x16, wt_bf16, y, m, n, k, trans_a=False, trans_b=True, async_=True)
+    rt.synchronize()
+    rt.recycle(x16)
+    return y
+
+
 def rmsnorm(rt: GpuRuntime, x: GpuBuffer, gamma: GpuBuffer, rows: int, dim: int, eps: float = RMSNORM_EPS):
     """`ops::rmsnorm::rmsnorm` (rmsnorm.rs:26-305): returns (y, backward) with backward(dy) -> (dx, dgamma)."""
     L = lib()

@@ -33,6 +33,31 @@ def test_matmul_forward_and_backward_closures(rt, m, k, n):
     assert rel_fro(dw.read_as(np.float32, k * n).reshape(k, n), ref_dw) <= 5e-3
 
 
+def test_matmul_with_pretransposed_bf16_weight(rt):
+    """bf16_matmul.rs:102-134; shape deliberately not a multiple of any tile (the reference pads, this build masks)."""
+    m, k, n = 70, 200, 130
+    rng = np.random.default_rng(5)
+    x = rng.standard_normal((m, k)).astype(np.float32)
+    wt16 = oracle.f32_to_bf16_rne((rng.standard_normal((n, k)) / np.sqrt(k)).astype(np.float32))
+    y = ops.matmul_with_wt_bf16(rt, rt.upload_f32(x), rt.upload(wt16), m, k, n)
+    ref = oracle.gemm_bf16(oracle.f32_to_bf16_rne(x), wt16, m, n, k, trans_a=False, trans_b=True)
+    assert rel_fro(y.read_as(np.float32, m * n).reshape(m, n), ref) <= 5e-3
+
+
+def test_embedding_op_closure(rt):
+    """`ops::embedding::embedding_forward` + its recorded backward (src/ignis/ops/embedding.rs:25-178)."""
+    vocab, dim, seq = 50, 24, 17
+    rng = np.random.default_rng(9)
+    table = rng.standard_normal((vocab, dim)).astype(np.float32)
+    ids = rng.integers(0, vocab, seq).astype(np.uint32)
+    out, backward = ops.embedding_forward(rt, rt.upload_f32(table), rt.upload(ids), seq, dim, vocab)
+    assert np.array_equal(out.read_as(np.float32, seq * dim).reshape(seq, dim), table[ids])
+    go = rng.standard_normal((seq, dim)).astype(np.float32)
+    gt = backward(rt.upload_f32(go))
+    ref = oracle.embedding_backward(np.zeros((vocab, dim), np.float32), ids, go, dim)
+    assert np.array_equal(gt.read_as(np.float32, vocab * dim).reshape(vocab, dim), ref)
+
+
 def test_rmsnorm_and_cross_entropy_ops(rt):
     rows, dim, V = 6, 2, 11
     x = np.array([[1, 2], [3, 4], [0.5, -1], [2, 2], [-3, 1], [0.1, 0.2]], np.float32)
