@@ -60,6 +60,35 @@ def kaiming_uniform_(torch, w, fan_in: int, seed: int):
     return w
 
 
+def exchange_units(dims, hidden, want_shard: bool, out_panels: int = 4):
+    """Units of the data-parallel gradient exchange over the flat parameter buffer (weights layer by layer, then all
+    gammas): a list of (offset, numel), the unit ids of every layer, and the id of the gamma unit.  One unit per weight
+    matrix; the output layer's (by far the largest) is cut into `out_panels` row panels when the optimizer is sharded,
+    so that its exchange starts after the first panel's GEMM instead of after the whole gradient; one unit for all
+    gammas together."""
+    units, layer_units, off = [], [], 0
+    nl = len(dims)
+    for i, (k_i, n_i) in enumerate(dims):
+        panels = out_panels if (want_shard and i == nl - 1 and k_i % out_panels == 0) else 1
+        per = k_i // panels
+        ids = []
+        for pnl in range(panels):
+            ids.append(len(units))
+            units.append((off + pnl * per * n_i, per * n_i))
+        layer_units.append(ids)
+        off += k_i * n_i
+    gamma_unit = len(units)
+    units.append((off, sum(hidden)))
+    return units, layer_units, gamma_unit
+
+
+def shard_range(unit, rank: int, world: int):
+    """[lo, hi) of the slice of `unit` = (offset, numel) that `rank` owns under the sharded optimizer."""
+    off, n = unit
+    ns = n // world
+    return off + rank * ns, off + (rank + 1) * ns
+
+
 class MlpTrainer:
     """One data-parallel replica.  `rows` is this rank's share of the batch, `rows_total` the global batch."""
 
@@ -101,21 +130,8 @@ class MlpTrainer:
             offs.append(o)
             o += s
         nl = len(dims)
-        # Units of the gradient exchange: one per weight matrix (the output layer's, by far the largest, in row panels
-        # when the optimizer is sharded, so that its exchange starts after the first panel's GEMM instead of after the
-        # whole gradient), and one for all gammas together (stored consecutively).
         want_shard = bool(shard_optimizer) and self.world > 1
-        self._units, self._layer_units = [], []
-        for i, (k_i, n_i) in enumerate(dims):
-            panels = 4 if (want_shard and i == nl - 1 and k_i % 4 == 0) else 1
-            per = k_i // panels
-            ids = []
-            for pnl in range(panels):
-                ids.append(len(self._units))
-                self._units.append((offs[i] + pnl * per * n_i, per * n_i))
-            self._layer_units.append(ids)
-        self._gamma_unit = len(self._units)
-        self._units.append((offs[nl], sum(cfg.hidden)))
+        self._units, self._layer_units, self._gamma_unit = exchange_units(dims, cfg.hidden, want_shard)
         # Sharded optimizer (more than one rank): every unit's gradient is reduce-scattered instead of all-reduced, each
         # rank keeps AdamW state for, and updates, its 1/world slice of every unit, and the updated bf16 copies (f32
         # for the gammas) are all-gathered.  Per rank this moves half the gradient bytes over NVLink, a 1/world share
@@ -276,9 +292,9 @@ class MlpTrainer:
         # behind the GEMMs of the earlier ones.
         for u in [gamma_unit] + list(range(gamma_unit)):   # unit ids follow the layer order
             off, n = self._units[u]
-            ns = n // self.world
-            lo = off + self.rank * ns
-            own_master, own_bf16 = self.master[lo:lo + ns], self.compute[lo:lo + ns]
+            lo, hi = shard_range(self._units[u], self.rank, self.world)
+            ns = hi - lo
+            own_master, own_bf16 = self.master[lo:hi], self.compute[lo:hi]
             self._ck(self.L.t0b_adamw_step(self.rt.handle, own_master.data_ptr(), self.grad_shards[u].data_ptr(),
                                            self.m_shards[u].data_ptr(), self.v_shards[u].data_ptr(), own_bf16.data_ptr(), ns,
                                            cfg.lr, cfg.beta1, cfg.beta2, cfg.adam_eps, cfg.weight_decay, self.step_count, 1.0, 1))
@@ -312,10 +328,10 @@ class MlpTrainer:
 
         self.finish_updates()
         out = self.master.clone()
-        for off, n in self._units:
-            ns = n // self.world
-            dist.all_gather_into_tensor(out[off:off + n], self.master[off + self.rank * ns:off + (self.rank + 1) * ns].clone(),
-                                        group=self.group)
+        for unit in self._units:
+            off, n = unit
+            lo, hi = shard_range(unit, self.rank, self.world)
+            dist.all_gather_into_tensor(out[off:off + n], self.master[lo:hi].clone(), group=self.group)
         return out
 
     def step(self, x, targets):

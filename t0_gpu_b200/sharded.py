@@ -44,6 +44,13 @@ def column_shard(n: int, world: int, rank: int, align: int = 64) -> ColumnShard:
     return ColumnShard(rank, world, col0, col1 - col0)
 
 
+def peer_order(rank: int, world: int) -> List[int]:
+    """Order in which a rank's epilogue writes the destinations of a finished tile: its own buffer first (destination
+    0 is the local store), then the peers starting at rank + 1, so that at any moment the ranks write to different
+    peers and the traffic is spread over every GPU's NVLink ingress."""
+    return [(rank + i) % world for i in range(world)]
+
+
 def exchange_handles(handle: bytes, group=None) -> List[bytes]:
     """All-gather one small byte string per rank over torch.distributed (any backend)."""
     import torch.distributed as dist
@@ -93,9 +100,7 @@ class ColumnShardedGemm:
             self.rt._check(lib().t0b_ipc_open(self.rt.handle, blob, C.byref(p)))
             ptrs.append(p.value)
             self._opened.append(p.value)
-        # Own buffer first (destination 0 is the local store), then the peers starting at rank + 1: at any moment the
-        # ranks then write to different peers, which spreads the traffic over every GPU's NVLink ingress.
-        self._peer_ptrs = [ptrs[(self.rank + i) % self.world] for i in range(self.world)]
+        self._peer_ptrs = [ptrs[r] for r in peer_order(self.rank, self.world)]
 
     def run(self, a: GpuBuffer, b_shard: GpuBuffer, async_: bool = True, gather: bool = True) -> None:
         """Launch this rank's GEMM.  With gather=False only the local C is written (GEMM-only timing)."""

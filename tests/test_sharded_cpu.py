@@ -1,11 +1,12 @@
-"""Host-side logic of the column-sharded GEMM, on CPU: the shard arithmetic and the handle exchange between
-two `gloo` ranks (the GPU kernels are not involved)."""
+"""Host-side logic of the multi-GPU paths, on CPU: the column-shard arithmetic and the handle exchange of the sharded
+GEMM between two `gloo` ranks, the peer write order, and the unit / slice arithmetic of the data-parallel MLP step with
+its sharded optimizer (emulated with gloo collectives and the oracle's AdamW; the GPU kernels are not involved)."""
 import os
 import socket
 
 import pytest
 
-from t0_gpu_b200.sharded import column_shard, exchange_handles
+from t0_gpu_b200.sharded import column_shard, exchange_handles, peer_order
 
 
 def test_column_shards_tile_the_columns():
@@ -40,8 +41,7 @@ def _worker(rank: int, world: int, port: int, q):
         mine = bytes([rank]) * 64                                         # stands in for a 64-byte IPC handle
         got = exchange_handles(mine)
         shard = column_shard(1024, world, rank)
-        # destination order used by the fused epilogue: own buffer first, then the peers in rank order
-        order = [rank] + [r for r in range(world) if r != rank]
+        order = peer_order(rank, world)      # destination order used by the fused epilogue
         q.put((rank, [h[0] for h in got], len(got[0]), shard.col0, shard.n_local, order))
     finally:
         dist.destroy_process_group()
@@ -65,3 +65,90 @@ def test_handle_exchange_between_two_gloo_ranks():
         assert firsts == [0, 1] and hlen == 64                            # every rank sees every handle, in rank order
         assert (col0, n_local) == (rank * 512, 512)
         assert order[0] == rank and sorted(order) == [0, 1]
+
+
+def test_peer_order_spreads_the_writes():
+    for world in (1, 2, 4, 8):
+        orders = [peer_order(r, world) for r in range(world)]
+        for r, o in enumerate(orders):
+            assert o[0] == r and sorted(o) == list(range(world))          # own buffer first, every rank once
+        for step in range(world):                                         # at every step the ranks hit distinct targets
+            assert sorted(o[step] for o in orders) == list(range(world))
+
+
+def test_exchange_units_cover_the_parameters():
+    from t0_gpu_b200.mlp import exchange_units, shard_range
+
+    dims = [(4096, 4096), (4096, 4096), (4096, 4096), (4096, 32000)]
+    hidden = [4096, 4096, 4096]
+    n_params = sum(k * n for k, n in dims) + sum(hidden)
+    for want_shard in (False, True):
+        units, layer_units, gamma_unit = exchange_units(dims, hidden, want_shard)
+        assert units[0][0] == 0 and units[-1][0] + units[-1][1] == n_params
+        for (o0, n0), (o1, _) in zip(units, units[1:]):
+            assert o0 + n0 == o1                                          # contiguous, no gaps, no overlap
+        assert [len(x) for x in layer_units] == ([1, 1, 1, 4] if want_shard else [1, 1, 1, 1])
+        assert gamma_unit == len(units) - 1 and units[gamma_unit][1] == sum(hidden)
+        assert sum(units[u][1] for u in layer_units[3]) == 4096 * 32000
+        for world in (2, 4, 8):
+            for unit in units:
+                assert unit[1] % world == 0
+                slices = [shard_range(unit, r, world) for r in range(world)]
+                assert slices[0][0] == unit[0] and slices[-1][1] == unit[0] + unit[1]
+                for a, b in zip(slices, slices[1:]):
+                    assert a[1] == b[0]
+    # a layer whose row count is not a multiple of the panel count stays in one piece
+    units, layer_units, _ = exchange_units([(6, 10), (7, 9)], [10], True)
+    assert layer_units == [[0], [1]] and units[1] == (60, 63)
+
+
+def _dp_worker(rank: int, world: int, port: int, q):
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+
+    import oracle
+    from t0_gpu_b200.mlp import exchange_units, shard_range
+
+    dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world)
+    try:
+        dims, hidden = [(8, 12), (12, 12), (12, 16)], [12, 12]
+        units, _, _ = exchange_units(dims, hidden, True)
+        n = units[-1][0] + units[-1][1]
+        rng = np.random.default_rng(3)                                   # same parameters on every rank
+        params = rng.standard_normal(n).astype(np.float32)
+        local_grads = np.random.default_rng(100 + rank).standard_normal(n).astype(np.float32)
+        hp = dict(lr=1e-2, beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=0.01, t=1)
+        # replicated optimizer: all-reduce, then AdamW over everything
+        g = torch.from_numpy(local_grads.copy())
+        dist.all_reduce(g)
+        full_p, _, _ = oracle.adamw_step(params, g.numpy(), np.zeros(n, np.float32), np.zeros(n, np.float32), **hp)
+        # sharded optimizer: every rank updates its slice of every unit (the reduce-scatter is emulated by slicing the
+        # all-reduced gradient, which is what it delivers), then the slices are gathered
+        out = torch.from_numpy(params.copy())
+        for unit in units:
+            lo, hi = shard_range(unit, rank, world)
+            p, _, _ = oracle.adamw_step(params[lo:hi], g.numpy()[lo:hi], np.zeros(hi - lo, np.float32), np.zeros(hi - lo, np.float32), **hp)
+            pieces = [torch.empty(hi - lo) for _ in range(world)]
+            dist.all_gather(pieces, torch.from_numpy(p))
+            out[unit[0]:unit[0] + unit[1]] = torch.cat(pieces)
+        q.put((rank, bool(np.array_equal(out.numpy(), full_p)), float(np.abs(full_p - params).max())))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_sharded_optimizer_indexing_between_two_gloo_ranks():
+    import torch.multiprocessing as mp
+
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_dp_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = sorted(q.get(timeout=120) for _ in range(2))
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    for rank, same, moved in results:
+        assert same and moved > 0          # gathered slices == the replicated update, and the update did something
