@@ -246,3 +246,22 @@ def test_gemm_tuner_bookkeeping(tmp_path, capsys):
     tuner.clear()
     assert tuner.cache == {} and not d.exists()
     assert global_tuner() is global_tuner()
+
+
+def test_bench_reference_arm_prints_the_contract_line():
+    """`bench.py --impl reference` needs no GPU: it times the CPU restatement on a bounded sample and prints one JSON
+    line with the keys the measurement contract names."""
+    import json
+    import subprocess
+    import sys
+
+    out = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--steps", "1", "--warmup", "0"],
+                         capture_output=True, text=True, timeout=600, cwd=ROOT)
+    assert out.returncode == 0, out.stderr[-2000:]
+    line = json.loads(out.stdout.strip().splitlines()[-1])
+    assert line["impl"] == "reference" and line["metric"] == "bf16 GEMM TFLOP/s" and line["unit"] == "TFLOP/s"
+    assert line["value"] > 0 and line["steps"] == 1 and line["higher_is_better"] is True
+    assert line["config"]["workload"] == "square_8192_nn_f32out"
+    assert line["cpu_baseline"]["kind"] == "port" and line["cpu_baseline"]["cores"] >= 1
+    assert line["e2e"]["h2d_bytes_per_step"] == 0 and line["e2e"]["d2h_bytes_per_step"] == 0
+    assert abs(line["e2e"]["value"] - line["value"]) < 1e-12
