@@ -698,6 +698,8 @@ struct ReduceParams {
 };
 
 __global__ void __launch_bounds__(256) splitk_reduce_kernel(const ReduceParams p) {
+    ptx::grid_launch_dependents();
+    ptx::grid_dependency_wait();   // launched behind the GEMM that writes the slabs (programmatic serialization)
     const int n4 = (p.N + 3) / 4;
     const long long total = static_cast<long long>(p.M) * n4;
     const bool vec_in = (p.ld_partial % 4 == 0) && (p.slab_stride % 4 == 0) &&

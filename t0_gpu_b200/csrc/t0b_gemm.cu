@@ -107,7 +107,16 @@ int32_t launch_reduce(t0b_ctx* ctx, const float* partial, uint32_t sk, uint32_t 
                     static_cast<int>(sk), out_bf16};
     const long long total = static_cast<long long>(m) * ((n + 3) / 4);
     const int blocks = static_cast<int>(std::min<long long>((total + 255) / 256, static_cast<long long>(ctx->num_sms) * 8));
-    splitk_reduce_kernel<<<std::max(blocks, 1), 256, 0, ctx->stream>>>(rp);
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(std::max(blocks, 1));
+    cfg.blockDim = dim3(256);
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;   // scheduled as the GEMM's CTAs exit
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = ctx->pdl ? 1 : 0;
+    cudaLaunchKernelEx(&cfg, splitk_reduce_kernel, rp);
     return check_cuda(ctx, cudaGetLastError(), "splitk_reduce launch");
 }
 
