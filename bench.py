@@ -16,7 +16,8 @@ device -> host copy of the result inside the timed region.
 
 `--impl reference` times the reference's CPU path for this GEMM (the C restatement of its host-side f32
 reference matmul; the reference itself is Rust and cannot be built here) on all host threads, each step a
-bounded row-slice of the same workload.
+bounded row-slice of the same workload, in the reference's own NT form (both operands K-contiguous, B transposed
+once on the host outside the timed region as Ignis does).
 """
 from __future__ import annotations
 
@@ -36,7 +37,15 @@ if ROOT not in sys.path:
 METRIC = "bf16 GEMM TFLOP/s"
 UNIT = "TFLOP/s"
 DENSE_PEAK_TFLOPS = 2250.0          # nominal B200 dense bf16
-FALLBACK_PEAK_TFLOPS = 1590.0       # earlier measurement on this pool, used when MEASURED_PEAKS.json is absent
+FALLBACK_PEAK_TFLOPS = 1590.0       # cuBLAS bf16 burst on a B200, used when MEASURED_PEAKS.json is absent
+FALLBACK_HBM_GBS = 6650.0
+
+# dram__bytes_read.sum + dram__bytes_write.sum of ONE launch of the GEMM kernel on the 8192^3 workload, from an ncu
+# capture of `python bench.py --quick --no-cpu --steps 2 --warmup 1`, keyed by the tile the run chose (algorithmic
+# bytes: 536.9e6).  A tile without a capture reports traffic null.
+NCU_DRAM_TRAFFIC_8192 = {
+    "t0_gemm_256x512_k64_ldsdb_wgp": 1.1116e9,
+}
 
 
 def measured_peak():
@@ -47,6 +56,14 @@ def measured_peak():
         return float(d["bf16_tflops"]), float(d.get("bf16_tflops_sustained", d["bf16_tflops"])), "measured"
     except Exception:
         return FALLBACK_PEAK_TFLOPS, 1400.0, "fallback"
+
+
+def measured_hbm():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return FALLBACK_HBM_GBS, "fallback"
 
 
 # ------------------------------------------------------------------------------------------------ clocks
@@ -119,41 +136,53 @@ def physical_gpu_index(local: int) -> int:
 
 # ------------------------------------------------------------------------------------------------ CPU side
 
-def cpu_gemm_sample(m, n, k, seed_a, seed_b, target_s, threads):
-    """Time the oracle's bf16 GEMM (k-ascending, unfused f32 mul+add) on a bounded row slice."""
+def cpu_gemm_sample(m, n, k, seed_a, seed_b, target_s, threads, layout="NT"):
+    """Operands and a row count for timing the oracle's bf16 GEMM (k-ascending, unfused f32 mul+add) on a bounded row
+    slice.  layout "NT": B stored [N, K] like the reference's own CPU loop (examples/test_gemm_correctness.rs:28-42;
+    Ignis transposes W once on the host first, src/ignis/ops/bf16_matmul.rs:390-424) -- the transpose is done here,
+    outside every timed region.  layout "NN": B stored [K, N], read with a stride of N (the layout the GPU arm is given)."""
     import numpy as np
     import oracle
 
     a_rows_max = min(m, 4096)
     scale = 1.0 / (k ** 0.5)
-    b = oracle.normal_bf16((k, n), seed_b, scale)          # [K, N] row-major ("NN")
+    b = oracle.normal_bf16((k, n), seed_b, scale)          # [K, N] row-major
+    if layout == "NT":
+        b = np.ascontiguousarray(b.T)                      # [N, K]
     a = oracle.normal_bf16((a_rows_max, k), seed_a, scale)
+    tb = layout == "NT"
     probe = max(threads, 8)
     t0 = time.perf_counter()
-    oracle.gemm_bf16(a, b, probe, n, k, trans_a=False, trans_b=False, threads=threads, row_end=probe)
+    oracle.gemm_bf16(a, b, probe, n, k, trans_a=False, trans_b=tb, threads=threads, row_end=probe)
     dt = time.perf_counter() - t0
     rows = int(max(probe, min(a_rows_max, probe * target_s / max(dt, 1e-6))))
     rows -= rows % max(threads, 1) if rows >= 2 * threads else 0
     return a, b, rows
 
 
+def cpu_gemm_time(a, b, rows, n, k, threads, layout):
+    import oracle
+
+    t0 = time.perf_counter()
+    oracle.gemm_bf16(a, b, rows, n, k, trans_a=False, trans_b=(layout == "NT"), threads=threads, row_end=rows)
+    return time.perf_counter() - t0
+
+
 def run_reference_arm(args, rank, world):
     """The reference's CPU implementation of the path, all host threads, bounded sample per step."""
     if rank != 0:
         return
-    import oracle
-
     threads = os.cpu_count() or 1
     if world == 1:
         m, n, k, workload = 8192, 8192, 8192, "square_8192_nn_f32out"
     else:
         m, n, k, workload = 32768, 32768, 8192, f"colshard_32768x32768x8192_bf16out_g{world}"
-    a, b, rows = cpu_gemm_sample(m, n, k, 1234, 1235, 1.5, threads)
+    a, b, rows = cpu_gemm_sample(m, n, k, 1234, 1235, 1.5, threads, "NT")
     for _ in range(min(args.warmup, 1)):
-        oracle.gemm_bf16(a, b, rows, n, k, trans_a=False, trans_b=False, threads=threads, row_end=rows)
+        cpu_gemm_time(a, b, rows, n, k, threads, "NT")
     t0 = time.perf_counter()
     for _ in range(args.steps):
-        oracle.gemm_bf16(a, b, rows, n, k, trans_a=False, trans_b=False, threads=threads, row_end=rows)
+        cpu_gemm_time(a, b, rows, n, k, threads, "NT")
     dt = (time.perf_counter() - t0) / args.steps
     val = 2.0 * rows * n * k / dt / 1e12
     sample = f"{rows} of {m} output rows x {n} cols, K={k}, per step"
@@ -161,8 +190,9 @@ def run_reference_arm(args, rank, world):
         "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
         "scaling": "strong" if world > 1 else "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": workload, "M": m, "N": n, "K": k, "sample": sample},
-        "cpu_baseline": {"value": val, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
+        "config": {"workload": workload, "M": m, "N": n, "K": k, "sample": sample,
+                   "layout": "NT (B stored [N, K], transposed once on the host outside the timed region)"},
+        "cpu_baseline": {"value": val, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample, "layout": "NT"},
         "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -195,12 +225,7 @@ def context_measurements(torch, rt, L, stream, dev):
     from t0_gpu_b200.mlp import MlpConfig, MlpTrainer
 
     out = {}
-    hbm_peak = None
-    try:
-        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
-            hbm_peak = float(json.load(f)["hbm_gbs"])
-    except Exception:
-        pass
+    hbm_peak, _ = measured_hbm()
 
     def gbs(fn, nbytes, steps=20):
         for _ in range(3):
@@ -291,6 +316,69 @@ def context_measurements(torch, rt, L, stream, dev):
     return out
 
 
+def skinny_splitk_measurements(torch, t, rt, L, stream, dev):
+    """The third benchmark config: skinny GEMMs and the deep-K GEMM with split_k 4 and 8 (uniform[-1,1) bf16 inputs in
+    the reference's NT layout, f32 output).  One timed call = everything t0b_gemm launches for the shape -- with
+    split-K that is the GEMM AND the fixed-order reduce.  These shapes are HBM-bound (35 / 35 / 33 MiB of operands and
+    output per call), so each also reports GB/s over its algorithmic bytes 2(MK + KN) + 4MN against the measured
+    copy bandwidth; eight operand sets are rotated so that consecutive calls do not find their data in L2."""
+    hbm_peak, hbm_kind = measured_hbm()
+    out = {}
+    nset = 8
+    cases = [("skinny_m128_k4096_n4096", 128, 4096, 4096, 0), ("skinny_m4096_k4096_n128", 4096, 4096, 128, 0),
+             ("splitk4_m512_k16384_n512", 512, 16384, 512, 4), ("splitk8_m512_k16384_n512", 512, 16384, 512, 8)]
+    for name, m, k, n, sk in cases:
+        g = torch.Generator(device=dev)
+        g.manual_seed(m * 1000 + k)
+        xs = [(torch.rand((m, k), generator=g, device=dev) * 2 - 1).to(torch.bfloat16) for _ in range(nset)]
+        ws = [(torch.rand((n, k), generator=g, device=dev) * 2 - 1).to(torch.bfloat16) for _ in range(nset)]
+        ys = [torch.empty((m, n), dtype=torch.float32, device=dev) for _ in range(nset)]
+        cfg = t.auto_select(m, k, n)
+        if sk:
+            cfg = cfg.with_(split_k=sk)
+        cc = cfg.to_c()
+        i = [0]
+
+        def call():
+            j = i[0] % nset
+            i[0] += 1
+            rt._check(L.t0b_gemm(rt.handle, C.byref(cc), 0, 1, xs[j].data_ptr(), ws[j].data_ptr(), ys[j].data_ptr(), m, n, k,
+                                 k, k, n, t.OUT_F32, 0, 0, 1.0, 0, 0, 1))
+
+        for _ in range(nset):
+            call()
+        l0 = rt.launch_count()
+        ms = statistics.median(time_steps(torch, call, 40, stream) for _ in range(5))
+        launches_per_call = (rt.launch_count() - l0) / 200.0
+        ref = xs[(i[0] - 1) % nset][:4].double() @ ws[(i[0] - 1) % nset].double().T
+        err = (ys[(i[0] - 1) % nset][:4].double() - ref).abs().max().item()
+        if not err < 2 ** -7 * k ** 0.5:
+            raise SystemExit(f"bench: {name} failed its sanity check: max err {err}")
+        nbytes = 2 * (m * k + k * n) + 4 * m * n
+        gbs = nbytes / ms / 1e6
+        out[name] = {"us": ms * 1e3, "tflops": 2.0 * m * n * k / (ms * 1e-3) / 1e12, "gbs": gbs,
+                     "frac_of_hbm": gbs / hbm_peak, "hbm_peak_kind": hbm_kind, "algorithmic_bytes": nbytes,
+                     "config": cfg.name(), "launches_per_call": launches_per_call,
+                     "timed": "GEMM + split-K reduce together" if (cfg.split_k or 0) > 1 else "GEMM"}
+        del xs, ws, ys
+    return out
+
+
+def sustained_measurement(torch, step, ms_estimate, flops, stream, gpu_index, seconds=2.5):
+    """The headline GEMM back to back for `seconds` (power-capped clocks), with the SM clock sampled beside it."""
+    n = max(50, int(seconds * 1e3 / ms_estimate))
+    sampler = ClockSampler(gpu_index, period_s=0.02)
+    sampler.start()
+    ms = time_steps(torch, step, n, stream)
+    clk = sampler.stop()
+    burst, sustained, kind = measured_peak()
+    tf = flops / (ms * 1e-3) / 1e12
+    mhz = clk.get("sm_mhz")
+    return {"launches": n, "seconds": ms * n / 1e3, "ms": ms, "tflops": tf, "frac_of_sustained_cublas": tf / sustained,
+            "peak_kind": f"of {kind} (sustained cuBLAS bf16)", "sm_mhz_median": mhz,
+            "ms_x_mhz": (ms * mhz) if mhz else None, "reasons": clk.get("reasons"), "power_w_max": clk.get("power_w_max")}
+
+
 def run_single(args, local_rank):
     import torch
 
@@ -329,12 +417,14 @@ def run_single(args, local_rank):
     flops = 2.0 * m * n * k
     value = flops / (ms * 1e-3) / 1e12
 
-    # Quick sanity of the timed output (the parity suite is tests/): a few rows against a f64 product.
+    # Quick sanity of the timed output (the parity suite is tests/): a few rows against a f64 product, within the
+    # GEMM tolerance 2^-7 * sqrt(K) * max|a| * max|b|.
     rows = [0, 4097, 8191]
     ref = (a[rows].double() @ b.double()).float()
     err = (c[rows] - ref).abs().max().item()
-    if not err < 2 ** -7 * k ** 0.5 * 0.01:
-        raise SystemExit(f"bench output failed its sanity check: max err {err}")
+    bound = 2 ** -7 * k ** 0.5 * a.abs().max().item() * b.abs().max().item()
+    if not err < bound:
+        raise SystemExit(f"bench output failed its sanity check: max err {err} (bound {bound})")
 
     # The other sizes of the sweep and the 1-GPU time of the sharded workload, for context.
     also = {}
@@ -379,7 +469,9 @@ def run_single(args, local_rank):
         also["colshard_32768x32768x8192_bf16out_g1"] = {"ms": t_ms, "tflops": 2.0 * bm * bn * bk / (t_ms * 1e-3) / 1e12}
         del a4, b4, c4
 
+    also.update(skinny_splitk_measurements(torch, t, rt, L, stream, dev))
     if not args.quick:
+        also["sustained_8192"] = sustained_measurement(torch, step, ms, flops, stream, physical_gpu_index(local_rank))
         also.update(context_measurements(torch, rt, L, stream, dev))
 
     # End to end through the C ABI with host buffers.
@@ -406,23 +498,28 @@ def run_single(args, local_rank):
     burst, sustained, kind = measured_peak()
     long_region = ms * args.steps > 1000.0
     peak = sustained if long_region else burst
+    traffic = NCU_DRAM_TRAFFIC_8192.get(cfg.name())
     roofline = {"bound": "tensor", "achieved": value, "peak": peak, "unit": UNIT, "frac": value / peak,
-                # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel on this workload, from the
-                # ncu capture summarised in profiles/gemm_bf16_tcgen05_8192cubed.md (algorithmic bytes: 536.9e6).
-                "traffic": 1.1116e9, "peak_kind": f"of {kind} ({'sustained' if long_region else 'burst'} cuBLAS bf16)",
+                "traffic": traffic, "traffic_note": ("ncu capture of this tile" if traffic else "no capture for this tile"),
+                "algorithmic_bytes": 2.0 * (m * k + k * n) + 4.0 * m * n,
+                "peak_kind": f"of {kind} ({'sustained' if long_region else 'burst'} cuBLAS bf16)",
                 "kernel": "gemm_bf16_tcgen05_kernel (tile " + cfg.name() + ")", "flops_per_launch": flops,
                 "frac_of_nominal_dense_peak": value / DENSE_PEAK_TFLOPS}
 
     cpu = None
     if not args.no_cpu:
-        import oracle
         threads = os.cpu_count() or 1
-        a_s, b_s, rows_s = cpu_gemm_sample(m, n, k, 1234, 1235, 12.0, threads)
-        t0 = time.perf_counter()
-        oracle.gemm_bf16(a_s, b_s, rows_s, n, k, trans_a=False, trans_b=False, threads=threads, row_end=rows_s)
-        dt = time.perf_counter() - t0
-        cpu = {"value": 2.0 * rows_s * n * k / dt / 1e12, "unit": UNIT, "cores": threads, "kind": "port",
+        # The reference's own form first: NT, both operands K-contiguous.  Then, on a smaller sample, the NN form the
+        # GPU arm is given (B read with a stride of N), to show how much of the difference is layout.
+        a_s, b_s, rows_s = cpu_gemm_sample(m, n, k, 1234, 1235, 10.0, threads, "NT")
+        dt = cpu_gemm_time(a_s, b_s, rows_s, n, k, threads, "NT")
+        cpu = {"value": 2.0 * rows_s * n * k / dt / 1e12, "unit": UNIT, "cores": threads, "kind": "port", "layout": "NT",
                "sample": f"{rows_s} of {m} output rows x {n} cols, K={k} ({dt:.1f} s)"}
+        a_s, b_s, rows_n = cpu_gemm_sample(m, n, k, 1234, 1235, 4.0, threads, "NN")
+        dt = cpu_gemm_time(a_s, b_s, rows_n, n, k, threads, "NN")
+        cpu["nn_layout"] = {"value": 2.0 * rows_n * n * k / dt / 1e12,
+                            "sample": f"{rows_n} of {m} output rows x {n} cols, K={k} ({dt:.1f} s)"}
+        del a_s, b_s
 
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3),
@@ -436,6 +533,82 @@ def run_single(args, local_rank):
     }
     print(json.dumps(line), flush=True)
     rt.close()
+
+
+def mlp_measurement(torch, dist, rt, rank, world, dev, steps, warmup, replicated):
+    """The data-parallel MLP training step of the fifth benchmark config at `world` ranks (1024 rows per GPU,
+    4096 -> 3 x [Linear 4096, RMSNorm, SiLU] -> Linear 32000 -> cross-entropy, AdamW).  A step = forward, backward,
+    gradient exchange and optimizer update; inputs are resident.  Returns rank-identical numbers (max over ranks)."""
+    from t0_gpu_b200.mlp import MlpConfig, MlpTrainer
+
+    cfg = MlpConfig()
+    rows = 1024
+    tr = MlpTrainer(rt, cfg, rows, rows_total=rows * world, shard_optimizer=not replicated)
+    g = torch.Generator(device=dev)
+    g.manual_seed(7 + rank)
+    x = torch.randn((rows, cfg.d_in), generator=g, device=dev)
+    tg = torch.randint(0, cfg.n_classes, (rows,), generator=g, device=dev, dtype=torch.int32)
+
+    def timed(fn, n):
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        ms = time_steps(torch, fn, n, tr.stream)
+        if world > 1:
+            tms = torch.tensor([ms], device=dev)
+            dist.all_reduce(tms, op=dist.ReduceOp.MAX)
+            dist.barrier()
+            ms = tms.item()
+        return ms
+
+    step = lambda: tr.step(x, tg)
+    for _ in range(max(warmup, 3)):
+        step()
+    launches0 = rt.launch_count()
+    ms = timed(step, steps)
+    launches = rt.launch_count() - launches0
+    ms_fb = timed(lambda: tr.forward_backward(x, tg), max(3, min(steps, 10)))
+    loss = tr.mean_loss()
+    tr.finish_updates()
+    rt.synchronize()
+    flops = cfg.flops_per_row() * rows * world
+    out = {"ms_per_step": ms, "fwd_bwd_ms": ms_fb, "gemm_tflops_whole_job": flops / (ms * 1e-3) / 1e12, "loss": loss,
+           "rows_per_gpu": rows, "global_batch": rows * world, "launches_per_step": launches / steps,
+           "optimizer": "AdamW, " + ("sharded over the ranks (reduce-scatter, all-gather)" if tr.sharded else
+                                     ("replicated (fp32 gradient all-reduce)" if world > 1 else "single rank"))}
+    del tr, x, tg
+    torch.cuda.empty_cache()
+    return out
+
+
+def dp_equivalence_check(torch, dist, rt, rank, world, dev):
+    """`world` ranks, each with its slice of a 128-row batch of a reduced MLP (256-wide, 512 classes), must give the
+    gradients and the loss of one rank that sees the whole batch: relative Frobenius error <= 1e-3 (the row-kernel
+    tolerance; the sums are reassociated across ranks), loss to 1e-5."""
+    from t0_gpu_b200.mlp import MlpConfig, MlpTrainer
+
+    cfg = MlpConfig(d_in=256, hidden=[256, 256, 256], n_classes=512)
+    rows_total = 128
+    rows = rows_total // world
+    g = torch.Generator(device=dev)
+    g.manual_seed(7)
+    x = torch.randn((rows_total, 256), generator=g, device=dev)
+    g.manual_seed(8)
+    tg = torch.randint(0, 512, (rows_total,), generator=g, device=dev, dtype=torch.int32)
+    tr = MlpTrainer(rt, cfg, rows, rows_total=rows_total, autotune=False)
+    tr.forward_backward(x[rank * rows:(rank + 1) * rows].contiguous(), tg[rank * rows:(rank + 1) * rows].contiguous())
+    rt.synchronize()
+    loss_dp = tr.mean_loss()
+    one = MlpTrainer(rt, cfg, rows_total, rows_total=rows_total, autotune=False, local_only=True)
+    one.forward_backward(x, tg)
+    rt.synchronize()
+    loss_one = one.mean_loss()
+    rel = ((tr.grads - one.grads).norm() / one.grads.norm()).item()
+    ok = rel <= 1e-3 and abs(loss_dp - loss_one) <= 1e-5 * abs(loss_one) + 1e-6
+    okt = torch.tensor([1 if ok else 0], device=dev)
+    dist.all_reduce(okt, op=dist.ReduceOp.MIN)
+    return {"ranks_equal_one_rank": bool(okt.item() == 1), "grad_rel_frobenius": rel, "loss_dp": loss_dp, "loss_one_rank": loss_one,
+            "shape": "128 rows, 256 -> 3 x 256 -> 512"}
 
 
 def run_multi(args, rank, local_rank, world):
@@ -456,6 +629,7 @@ def run_multi(args, rank, local_rank, world):
     L = lib()
 
     m, n, k = 32768, 32768, 8192
+    elem = 2
     op = ColumnShardedGemm(rt, m, n, k, out_dtype=t.OUT_BF16)
     sh = op.shard
     a = device_normal_bf16(torch, (m, k), 4321, 1.0 / k ** 0.5, dev)                  # replicated (same seed)
@@ -498,78 +672,150 @@ def run_multi(args, rank, local_rank, world):
     flops = 2.0 * m * n * k
     value = flops / (ms * 1e-3) / 1e12
 
-    # Every rank must now hold the same full C: compare a checksum of sampled rows across ranks, and a few
-    # elements against an f64 product on rank 0.
+    # ---- checks on the WHOLE output, outside every timed region.
+    # (1) every rank holds the same full C: block-wise checksums of all 2 GiB, computed on the device, compared across ranks.
+    op.c.zero()
+    barrier()
     full()
-    barrier()
-    torch.cuda.synchronize()
-    barrier()
-    elem = 2
+    op.finish()
+    block = 1 << 20
+    nblocks = (m * n * elem + block - 1) // block
+    sums = torch.zeros(2 * nblocks, dtype=torch.int64, device=dev)
+    rt._check(L.t0b_hash_blocks(rt.handle, op.c.gpu_addr(), m * n * elem, block, sums.data_ptr(), 0))
+    gathered = [torch.zeros_like(sums) for _ in range(world)]
+    dist.all_gather(gathered, sums)
+    full_c_equal = all(torch.equal(gathered[0], g) for g in gathered)
+    # (2) this rank's own column block equals, bit for bit, what a plain single-destination GEMM computes for it.
+    own = torch.empty((m, sh.n_local), dtype=torch.bfloat16, device=dev)
+    rt._check(L.t0b_gemm(rt.handle, None, 0, 0, a.data_ptr(), b.data_ptr(), own.data_ptr(), m, sh.n_local, k, k, sh.n_local,
+                         sh.n_local, t.OUT_BF16, 0, 0, 1.0, 0, 0, 0))
+    got = torch.empty_like(own)
+    rt._check(L.t0b_copy_d2d(rt.handle, got.data_ptr(), sh.n_local * elem, op.c.gpu_addr() + sh.col0 * elem, n * elem,
+                             sh.n_local * elem, m, 0))
+    own_block_bit_identical = bool(torch.equal(own.view(torch.int16), got.view(torch.int16)))
+    # (3) and a few rows of it against an f64 product, within the GEMM tolerance (+ bf16 output rounding).
     rows = [0, 12345, m - 1]
-    sample = torch.empty((len(rows), n), dtype=torch.bfloat16, device=dev)
-    row_h = torch.empty(n, dtype=torch.bfloat16).pin_memory()
-    for i, r in enumerate(rows):
-        rt._check(L.t0b_memcpy_d2h(rt.handle, row_h.data_ptr(), op.c.gpu_addr() + r * n * elem, n * elem))
-        sample[i] = row_h.to(dev)
-    gathered = [torch.zeros_like(sample) for _ in range(world)]
-    dist.all_gather(gathered, sample)
-    same = all(torch.equal(gathered[0], g) for g in gathered)
-    # each rank checks its own column block of the sampled rows against an f64 product of its operands
     ref = (a[rows].double() @ b.double()).to(torch.float32)
-    got = sample[:, sh.col0:sh.col0 + sh.n_local].float()
-    err = (got - ref).abs().max().item() if sh.n_local else 0.0
-    ok = bool(same) and err < 0.02
+    err = (got[rows].float() - ref).abs().max().item()
+    bound = 2 ** -7 * k ** 0.5 * a.abs().max().item() * b.abs().max().item() + 2 ** -8 * ref.abs().max().item()
+    ok = full_c_equal and own_block_bit_identical and err < bound
     okt = torch.tensor([1 if ok else 0], device=dev)
     dist.all_reduce(okt, op=dist.ReduceOp.MIN)
     if okt.item() != 1:
-        raise SystemExit(f"rank {rank}: sharded GEMM output failed its check (same={same}, err={err})")
+        raise SystemExit(f"rank {rank}: sharded GEMM output failed its check (full_c_equal={full_c_equal}, "
+                         f"own_block_bit_identical={own_block_bit_identical}, err={err}, bound={bound})")
+    checks = {"full_c_equal": True, "own_block_bit_identical": True, "max_abs_err_vs_f64_rows": err,
+              "how": f"{nblocks} block checksums of each rank's 2 GiB C compared across ranks; own column block "
+                     "recomputed by a plain t0b_gemm and compared bit for bit"}
+    del own, got, sums, gathered
 
-    # End to end with host buffers: operands host -> device, this rank's output block device -> host.
-    a_h = a.cpu().pin_memory()
+    # ---- the NVLink store rate the fused all-gather is bounded by: this library's own copy kernel (SM-issued 16-byte
+    # stores, like the epilogue's) writing this rank's column block into the next rank's C, all ranks at once.
+    peer_gbs = None
+    if world > 1 and sh.n_local:
+        src = op.c.gpu_addr() + sh.col0 * elem
+        dst = op._peer_ptrs[1] + sh.col0 * elem            # the same block in the peer's C: the bytes are already equal
+        cp = lambda: rt._check(L.t0b_copy_d2d(rt.handle, dst, n * elem, src, n * elem, sh.n_local * elem, m, 1))
+        cp()
+        ms_cp = timed(cp, 3)
+        peer_gbs = m * sh.n_local * elem / ms_cp / 1e6
+        op.finish()
+
+    # ---- end to end from pinned HOST buffers.  A is replicated, so every rank uploads only its 1/world row slice of A
+    # (and its B shard) over PCIe and the slices are all-gathered over NVLink; the GEMM then runs in row strips and each
+    # finished strip of this rank's output block travels to the host while the next strip is multiplied.
+    a_rows = m // world
+    a_h = a[rank * a_rows:(rank + 1) * a_rows].cpu().pin_memory()
     b_h = b.cpu().pin_memory()
     c_h = torch.empty((m, sh.n_local), dtype=torch.bfloat16).pin_memory()
+    a_slice = a[rank * a_rows:(rank + 1) * a_rows]
+    strips = 8
+    srows = m // strips
 
     def e2e_step():
-        rt._check(L.t0b_memcpy_h2d(rt.handle, a.data_ptr(), a_h.data_ptr(), a_h.numel() * 2))
-        rt._check(L.t0b_memcpy_h2d(rt.handle, b.data_ptr(), b_h.data_ptr(), b_h.numel() * 2))
-        op.run(A, B, async_=False, gather=True)
-        rt._check(L.t0b_memcpy2d_d2h(rt.handle, c_h.data_ptr(), sh.n_local * elem, op.c.gpu_addr() + sh.col0 * elem,
-                                     n * elem, sh.n_local * elem, m))
+        rt._check(L.t0b_memcpy_h2d_async(rt.handle, a_slice.data_ptr(), a_h.data_ptr(), a_h.numel() * 2))
+        rt._check(L.t0b_memcpy_h2d_async(rt.handle, b.data_ptr(), b_h.data_ptr(), b_h.numel() * 2))
+        dist.all_gather_into_tensor(a, a_slice)                      # in place: slice r sits at rows [r*a_rows, ...)
+        for i in range(strips):
+            op.run(A, B, async_=True, gather=True, rows=(i * srows, srows))
+            rt._check(L.t0b_memcpy2d_d2h_async(rt.handle, c_h.data_ptr() + i * srows * sh.n_local * elem, sh.n_local * elem,
+                                               op.c.gpu_addr() + (i * srows * n + sh.col0) * elem, n * elem,
+                                               sh.n_local * elem, srows))
+        rt.synchronize()
 
     e2e_step()
+    barrier()
     e2e_steps = max(2, min(args.steps, 5))
     e2e_ms = timed(e2e_step, e2e_steps)
+    if not torch.equal(c_h[12345].to(dev).view(torch.int16), ref_row_bits(torch, op, rt, L, sh, n, elem, 12345, dev)):
+        raise SystemExit(f"rank {rank}: the host copy of C differs from the device copy")
+    # each leg alone, once, for the record
+    legs = {}
+    legs["h2d_a_slice_b_shard"] = timed(lambda: (rt._check(L.t0b_memcpy_h2d_async(rt.handle, a_slice.data_ptr(), a_h.data_ptr(), a_h.numel() * 2)),
+                                                 rt._check(L.t0b_memcpy_h2d_async(rt.handle, b.data_ptr(), b_h.data_ptr(), b_h.numel() * 2)),
+                                                 rt.synchronize()), 2)
+    legs["allgather_a_nvlink"] = timed(lambda: dist.all_gather_into_tensor(a, a_slice), 2)
+    legs["gemm_fused_gather"] = ms
+    legs["d2h_own_block"] = timed(lambda: (rt._check(L.t0b_memcpy2d_d2h_async(rt.handle, c_h.data_ptr(), sh.n_local * elem,
+                                                                              op.c.gpu_addr() + sh.col0 * elem, n * elem, sh.n_local * elem, m)),
+                                           rt.synchronize()), 2)
     e2e = {"value": flops / (e2e_ms * 1e-3) / 1e12, "unit": UNIT,
            "h2d_bytes_per_step": (a_h.numel() + b_h.numel()) * 2, "d2h_bytes_per_step": c_h.numel() * 2,
-           "ms_per_step": e2e_ms, "steps": e2e_steps, "note": "bytes are per rank"}
+           "ms_per_step": e2e_ms, "steps": e2e_steps, "note": "bytes are per rank", "legs_alone_ms": legs,
+           "api": "t0b_memcpy_h2d_async (1/world row slice of A + the B shard), NCCL all-gather of A over NVLink, "
+                  f"t0b_gemm_multi_dst in {strips} row strips, t0b_memcpy2d_d2h_async of each strip, t0b_sync"}
+    op.close()
+    del a, b, a_h, b_h, c_h, A, B
+    torch.cuda.empty_cache()
+
+    # ---- the data-parallel MLP training step (fifth config) at the same ranks: the all-reduce form and the sharded optimizer.
+    mlp = {"allreduce_replicated_adamw": mlp_measurement(torch, dist, rt, rank, world, dev, 10, 3, True),
+           "sharded_optimizer": mlp_measurement(torch, dist, rt, rank, world, dev, 10, 3, False),
+           "equivalence": dp_equivalence_check(torch, dist, rt, rank, world, dev)}
+    if not mlp["equivalence"]["ranks_equal_one_rank"]:
+        raise SystemExit(f"rank {rank}: the data-parallel gradients differ from the one-rank gradients: {mlp['equivalence']}")
 
     if rank == 0:
         burst, sustained, kind = measured_peak()
         per_gpu = value / world
-        egress = (world - 1) * m * sh.n_local * elem
+        ingress = (world - 1) * m * sh.n_local * elem           # = egress: (G-1)/G * 2 GiB per GPU
+        link_gbs = peer_gbs if peer_gbs else 713.0
+        link_ms = ingress / (link_gbs * 1e9) * 1e3
+        compute_ms = flops / world / (sustained * 1e12) * 1e3
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": f"colshard_32768x32768x8192_bf16out_g{world}", "M": m, "N": n, "K": k,
                        "parallelism": f"B column-sharded x{world}, A replicated, all-gather fused into the GEMM epilogue (peer stores)",
+                       "gemm_config": t.sharded.multi_dst_config(m, k, sh.n_local, world, rt.num_sms()).name(),
                        "l2": "operands 0.5 GiB + output 2 GiB per GPU > L2, no flush", "output": "bf16"},
             "pct_of_dense_peak": 100.0 * per_gpu / DENSE_PEAK_TFLOPS,
-            "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches),
+            "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches), "checks": checks,
             "roofline": {"bound": "tensor", "achieved": per_gpu, "peak": sustained, "unit": UNIT,
                          "frac": per_gpu / sustained, "traffic": None,
                          "peak_kind": f"of {kind} (sustained cuBLAS bf16), per GPU",
-                         "nvlink_egress_bytes_per_gpu": egress,
-                         "nvlink_bound_ms": egress / 770e9 * 1e3,
-                         "compute_bound_ms": flops / world / (sustained * 1e12) * 1e3,
-                         "frac_of_fused_bound": max(egress / 770e9 * 1e3, flops / world / (sustained * 1e12) * 1e3) / ms},
+                         "nvlink_ingress_bytes_per_gpu": ingress,
+                         "nvlink_store_gbs_measured": peer_gbs,
+                         "nvlink_store_how": "t0b_copy_d2d of this rank's column block into the next rank's C, all ranks at once",
+                         "nvlink_bound_ms": link_ms, "compute_bound_ms": compute_ms,
+                         "frac_of_fused_bound": max(link_ms, compute_ms) / ms},
             "gemm_only": {"ms_per_step": ms_local, "tflops": flops / (ms_local * 1e-3) / 1e12},
             "cpu_baseline": None,
+            "also": {"mlp_step": mlp},
         }
         print(json.dumps(line), flush=True)
-    op.close()
     barrier()
     dist.destroy_process_group()
+    rt.close()
+
+
+def ref_row_bits(torch, op, rt, L, sh, n, elem, row, dev):
+    """Row `row` of this rank's own column block, read from the device copy of C, as int16 bit patterns."""
+    out = torch.empty(sh.n_local, dtype=torch.bfloat16, device=dev)
+    rt._check(L.t0b_copy_d2d(rt.handle, out.data_ptr(), sh.n_local * elem, op.c.gpu_addr() + (row * n + sh.col0) * elem,
+                             sh.n_local * elem, sh.n_local * elem, 1, 0))
+    return out.view(torch.int16)
 
 
 def run_mlp(args, rank, local_rank, world):
@@ -581,55 +827,26 @@ def run_mlp(args, rank, local_rank, world):
     import torch.distributed as dist
 
     import t0_gpu_b200 as t
-    from t0_gpu_b200.mlp import MlpConfig, MlpTrainer
 
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     rt = t.GpuRuntime(local_rank)
-    cfg = MlpConfig()
-    rows = 1024
-    tr = MlpTrainer(rt, cfg, rows, rows_total=rows * world, shard_optimizer=not args.replicated_optimizer)
-    g = torch.Generator(device=dev)
-    g.manual_seed(7 + rank)
-    x = torch.randn((rows, cfg.d_in), generator=g, device=dev)
-    tg = torch.randint(0, cfg.n_classes, (rows,), generator=g, device=dev, dtype=torch.int32)
-
-    def timed(fn, steps):
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-        ms = time_steps(torch, fn, steps, tr.stream)
-        if world > 1:
-            tms = torch.tensor([ms], device=dev)
-            dist.all_reduce(tms, op=dist.ReduceOp.MAX)
-            dist.barrier()
-            ms = tms.item()
-        return ms
-
-    step = lambda: tr.step(x, tg)
-    for _ in range(max(args.warmup, 3)):
-        step()
     sampler = ClockSampler(physical_gpu_index(local_rank))
-    launches0 = rt.launch_count()
     sampler.start()
-    ms = timed(step, args.steps)
+    r = mlp_measurement(torch, dist, rt, rank, world, dev, args.steps, args.warmup, args.replicated_optimizer)
     clocks = sampler.stop()
-    launches = rt.launch_count() - launches0
-    ms_fb = timed(lambda: tr.forward_backward(x, tg), max(3, min(args.steps, 10)))
-    loss = tr.mean_loss()
-    flops = cfg.flops_per_row() * rows * world
     if rank == 0:
         print(json.dumps({
-            "metric": "MLP training step, GEMM TFLOP/s (forward + backward FLOPs / step time)", "value": flops / (ms * 1e-3) / 1e12,
-            "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms,
+            "metric": "MLP training step, GEMM TFLOP/s (forward + backward FLOPs / step time)", "value": r["gemm_tflops_whole_job"],
+            "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": r["ms_per_step"],
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": "mlp_step_4096x3_32000_rows1024_per_gpu", "rows_per_gpu": rows, "global_batch": rows * world,
-                       "optimizer": "AdamW, " + ("sharded over the ranks (reduce-scatter, all-gather)" if tr.sharded else
-                                                 ("replicated (all-reduce)" if world > 1 else "single rank")),
+            "config": {"workload": "mlp_step_4096x3_32000_rows1024_per_gpu", "rows_per_gpu": r["rows_per_gpu"],
+                       "global_batch": r["global_batch"], "optimizer": r["optimizer"],
                        "l2": "weights 363 MB bf16 + 726 MB f32 master per step > L2, no flush"},
-            "fwd_bwd_ms": ms_fb, "loss": loss, "clocks": clocks, "gpu_launches": launches,
+            "fwd_bwd_ms": r["fwd_bwd_ms"], "loss": r["loss"], "clocks": clocks,
+            "gpu_launches": int(r["launches_per_step"] * args.steps),
         }))
     if world > 1:
         dist.destroy_process_group()

@@ -92,9 +92,16 @@ T0B_API uint32_t t0b_config_lds_total(const t0b_gemm_config* cfg);
 T0B_API uint32_t t0b_config_estimated_vgprs(const t0b_gemm_config* cfg);
 T0B_API int32_t t0b_config_is_feasible(const t0b_gemm_config* cfg);
 
-/* auto_select(m, k, n): gemm_gen.rs:320-322.  NOTE the argument order (M, K, N).  Returns the config the
- * measured B200 table picks for the shape (cost_model::predict_best in the reference). */
+/* auto_select(m, k, n): gemm_gen.rs:320-322.  NOTE the argument order (M, K, N).  Answers, in this order, from
+ * (2) what t0b_tune measured for the shape in this process, (1) the table measured on B200 that is compiled into the
+ * library (csrc/t0b_tuned_table.inc: the benchmark shapes and their backward shapes), (0) a cost model whose
+ * constants were measured on B200 -- the reference's predict_best over its tune cache
+ * (src/t0/cost_model.rs:593-601, 788-1078).  The call carries no layout: the NT / f32 row is preferred.
+ * t0b_auto_select_source is the same lookup for one layout and output type and returns which source answered
+ * (2, 1 or 0; negative on error); config-less t0b_gemm calls use exactly this lookup. */
 T0B_API int32_t t0b_auto_select(uint32_t m, uint32_t k, uint32_t n, t0b_gemm_config* out);
+T0B_API int32_t t0b_auto_select_source(uint32_t m, uint32_t k, uint32_t n, int32_t trans_a, int32_t trans_b,
+                                       int32_t out_dtype, t0b_gemm_config* out);
 /* auto_select_legacy(m, k, n): gemm_gen.rs:331-379, the 7-branch heuristic kept for A/B comparison. */
 T0B_API int32_t t0b_auto_select_legacy(uint32_t m, uint32_t k, uint32_t n, t0b_gemm_config* out);
 /* auto_select_backward_{data,weight}(m, n_orig, k_orig): gemm_gen.rs:482-486, 517-521. */
@@ -156,8 +163,11 @@ T0B_API int32_t t0b_num_sms(t0b_ctx* ctx);
  * GEMMs occupy at most `sms` SMs (0 = all).  No reference counterpart (single GPU, one queue). */
 T0B_API int32_t t0b_set_sm_limit(t0b_ctx* ctx, int32_t sms);
 /* Device status word written by kernels whose bounded waits ran out (101..105) or that met an index outside its
- * table (110); 0 = none.  A synchronous call that finds it set returns T0B_ERR_DEVICE.  Reading clears it when
- * `clear` is non-zero.  Takes the place of the reference's wait_read_ptr timeout (src/kfd/mod.rs:1607-1642). */
+ * table (110); 0 = none.  The first synchronous call (or t0b_sync) that finds it set returns T0B_ERR_DEVICE once and
+ * takes the code out of the word, so later calls are not failed by it; the context is not poisoned.  This function
+ * returns the code still in the word, else the code most recently taken, and keeps returning it until a call with
+ * a non-zero `clear` forgets both.  Asynchronous calls never look at the word: after a batch of them call t0b_sync.
+ * Takes the place of the reference's wait_read_ptr timeout (src/kfd/mod.rs:1607-1642). */
 T0B_API int32_t t0b_device_status(t0b_ctx* ctx, int32_t clear);
 /* Limit of every in-kernel wait, in nanoseconds (default 2e9). */
 T0B_API int32_t t0b_set_wait_limit_ns(t0b_ctx* ctx, uint64_t ns);
@@ -178,6 +188,15 @@ T0B_API int32_t t0b_memset0(t0b_ctx* ctx, uint64_t dst, size_t bytes);
 /* Strided device -> host copy of `height` rows of `width_bytes` (a column block of a row-major matrix). */
 T0B_API int32_t t0b_memcpy2d_d2h(t0b_ctx* ctx, void* dst, size_t dst_pitch, uint64_t src, size_t src_pitch,
                                  size_t width_bytes, size_t height);
+/* Asynchronous forms for pinned host memory, the batched counterpart of the reference's write / dispatch_async /
+ * wait_idle pattern (src/ignis/gpu_context.rs:297-332).  t0b_memcpy_h2d_async: the copy runs on the context's upload
+ * stream behind the work queued so far; launches made after the call wait for it.  t0b_memcpy2d_d2h_async: the
+ * read-back runs on the context's download stream behind the work queued so far, launches made after the call do NOT
+ * wait for it (a strip of C travels to the host while the next strip is multiplied); t0b_sync waits for it.  The host
+ * buffers must stay valid until t0b_sync returns. */
+T0B_API int32_t t0b_memcpy_h2d_async(t0b_ctx* ctx, uint64_t dst, const void* src, size_t bytes);
+T0B_API int32_t t0b_memcpy2d_d2h_async(t0b_ctx* ctx, void* dst, size_t dst_pitch, uint64_t src, size_t src_pitch,
+                                       size_t width_bytes, size_t height);
 /* GpuRuntime::synchronize / wait_idle, gpu_context.rs:297-332.  Also checks the device status word. */
 T0B_API int32_t t0b_sync(t0b_ctx* ctx);
 
@@ -197,8 +216,13 @@ T0B_API int32_t t0b_ipc_close(t0b_ctx* ctx, uint64_t dptr);
  *   trans_b = 0: B is [K,N] with row pitch ldb ("NN");  1: B is [N,K] with row pitch ldb ("NT", the
  *   reference kernels' only native layout, src/t0/gemm_gen.rs:25).
  *   cfg may be NULL (auto_select).  out_dtype: T0B_OUT_F32 / T0B_OUT_BF16 (RNE).  epilogue: T0B_EPI_*; bias f32[N].
- *   Split-K (cfg->split_k > 1) needs split_k*M*N*4 bytes of workspace: pass one, or 0 to let the context keep
- *   a grow-only workspace.  The partial slabs are summed in slab order by a second kernel (deterministic).
+ *   Split-K (cfg->split_k > 1) on a single-CTA tile (tile_m <= 128) with 2, 4 or 8 K ranges runs as thread-block
+ *   clusters: the CTAs of a cluster take the K ranges of one tile, keep the partial tiles in shared memory and sum
+ *   them over distributed shared memory in K-range order, in the same launch; no workspace is used.  Otherwise
+ *   (CTA-pair tiles, 16 ranges) it needs split_k*M*N*4 bytes of workspace -- pass one, or 0 to let the context keep a
+ *   grow-only workspace -- and a second kernel sums the slabs in slab order.  Either way the sum runs over the K
+ *   ranges in order from +0.0, so both paths, t0b_gemm_slabs + t0b_splitk_reduce and the reference's host-side slab
+ *   sum (examples/test_gemm_correctness.rs:203-207) give the same bits, run after run.
  *   async = 0 waits for completion (GpuRuntime::dispatch, gpu_context.rs:264); 1 only enqueues (dispatch_async, :332).
  * Entry point behind ops::bf16_matmul::dispatch_gemm_forward / gemm_backward_data / gemm_backward_weight
  * (src/ignis/ops/bf16_matmul.rs:162-308), which stage transposes on the host instead. */
@@ -229,6 +253,23 @@ T0B_API int32_t t0b_gemm_host(t0b_ctx* ctx, const t0b_gemm_config* cfg, int32_t 
                               const void* b, void* c, uint32_t m, uint32_t n, uint32_t k, uint64_t lda, uint64_t ldb,
                               uint64_t ldc, int32_t out_dtype, uint32_t chunk_rows);
 
+/* Block-wise checksum of a device buffer: for every block of `block_bytes` (the last may be short) two 64-bit values
+ * are written to out[2*b], out[2*b+1] (a position-mixed wrapping sum and XOR of the block's 64-bit words).  Equal
+ * buffers give equal checksums; it lets ranks compare whole outputs (2 GiB per rank in the sharded GEMM) by exchanging
+ * a few KiB.  bytes, block_bytes, src and out must be multiples of 8.  No counterpart in the reference, whose tests
+ * read the full result through mapped VRAM (examples/test_gemm_correctness.rs:198-211). */
+T0B_API int32_t t0b_hash_blocks(t0b_ctx* ctx, uint64_t src, size_t bytes, size_t block_bytes, uint64_t out, int32_t async);
+/* Copy `rows` rows of `width_bytes` between device buffers with SM-issued 16-byte loads and stores (all sizes, pitches
+ * and pointers multiples of 16).  Either side may be a peer-mapped pointer (t0b_ipc_open): with a peer destination it
+ * measures the NVLink store rate that bounds the fused all-gather of t0b_gemm_multi_dst.  No reference counterpart. */
+T0B_API int32_t t0b_copy_d2d(t0b_ctx* ctx, uint64_t dst, size_t dst_pitch, uint64_t src, size_t src_pitch,
+                             size_t width_bytes, size_t rows, int32_t async);
+/* The config t0b_gemm_multi_dst uses when it is given none: the auto_select tile for (m, k, n_local), except that
+ * with more than one destination a tile that keeps both TMEM accumulators for one tile (256x512, 512x256) becomes
+ * 256x256, whose accumulators double-buffer, so that the peer stores of one tile retire while the next is multiplied.
+ * Never split-K.  No counterpart in the reference (single GPU). */
+T0B_API int32_t t0b_multi_dst_config(uint32_t m, uint32_t k, uint32_t n_local, int32_t n_dst, int32_t num_sms,
+                                     t0b_gemm_config* out);
 /* Column-sharded GEMM with the all-gather folded into the epilogue: this rank computes C[:, col0 : col0+n_local]
  * and stores every finished tile into each of the n_dst row-major [M, ldc] destinations (its own and its
  * peers', as peer-mapped device pointers).  No counterpart in the reference (single GPU). */
@@ -279,6 +320,17 @@ T0B_API int32_t t0b_set_autotune_dir(t0b_ctx* ctx, const char* dir);
  * Element-wise and row kernels around the GEMMs (f32 activations)
  * ---------------------------------------------------------------------------------------------- */
 
+/* bf16 weight cache: GpuRuntime::get_or_create_bf16 / invalidate_bf16 / clear_bf16_cache
+ * (src/ignis/gpu_context.rs:392-432).  The first call for a tensor id converts the f32 buffer on the device
+ * (stream-ordered, no synchronisation) and keeps the bf16 copy; later calls return the same copy until the id is
+ * invalidated -- which the caller does after every update of the weights (an optimizer step).  The copies live in
+ * the context's buffer pool.  t0b_bf16_cache_stats counts entries, conversions run and hits. */
+T0B_API int32_t t0b_get_or_create_bf16(t0b_ctx* ctx, uint64_t tensor_id, uint64_t f32_ptr, size_t n_elems,
+                                       uint64_t* bf16_ptr);
+T0B_API int32_t t0b_invalidate_bf16(t0b_ctx* ctx, uint64_t tensor_id);
+T0B_API int32_t t0b_clear_bf16_cache(t0b_ctx* ctx);
+T0B_API int32_t t0b_bf16_cache_stats(t0b_ctx* ctx, uint64_t* entries, uint64_t* conversions, uint64_t* hits);
+
 /* f32 -> bf16, round to nearest even (src/ignis/ops/bf16_matmul.rs:357-384, done on the host there). */
 T0B_API int32_t t0b_cast_f32_to_bf16(t0b_ctx* ctx, uint64_t src, uint64_t dst, size_t n, int32_t async);
 /* f32 [rows, cols] -> bf16 [cols, rows] (f32_to_bf16_transpose_gpu_padded, bf16_matmul.rs:390-424). */
@@ -295,7 +347,8 @@ T0B_API int32_t t0b_rmsnorm_bwd(t0b_ctx* ctx, uint64_t dy, uint64_t x, uint64_t 
                                 uint64_t scratch, size_t scratch_bytes, uint32_t rows, uint32_t cols, float eps,
                                 int32_t async);
 T0B_API size_t t0b_rmsnorm_bwd_scratch_bytes(uint32_t rows, uint32_t cols);
-/* RMSNorm backward (dx and dgamma, same results as t0b_rmsnorm_bwd) for callers that cannot allocate device
+/* RMSNorm backward (dx and dgamma; the same values as t0b_rmsnorm_bwd up to the order of the fp32 sums, and bit for
+ * bit the same where both take the same kernels: cols < 1024 or unaligned rows) for callers that cannot allocate device
  * memory -- a host runtime that handed its whole device budget to fixed buffers at start-up, or a step loop that
  * must avoid the device-wide synchronisation cudaMalloc / cudaFree bring -- and so have no scratch to pass.
  * Has no counterpart in the reference.  The dgamma scratch lives in a 2 MiB array inside the library image

@@ -42,6 +42,7 @@ SIGNATURES = {
     "t0b_config_estimated_vgprs": (_u32, [_cfgp]),
     "t0b_config_is_feasible": (_i32, [_cfgp]),
     "t0b_auto_select": (_i32, [_u32, _u32, _u32, _cfgp]),
+    "t0b_auto_select_source": (_i32, [_u32, _u32, _u32, _i32, _i32, _i32, _cfgp]),
     "t0b_auto_select_legacy": (_i32, [_u32, _u32, _u32, _cfgp]),
     "t0b_auto_select_backward_data": (_i32, [_u32, _u32, _u32, _cfgp]),
     "t0b_auto_select_backward_weight": (_i32, [_u32, _u32, _u32, _cfgp]),
@@ -75,6 +76,8 @@ SIGNATURES = {
     "t0b_memcpy_d2h": (_i32, [_ctx, C.c_void_p, _u64, _sz]),
     "t0b_memset0": (_i32, [_ctx, _u64, _sz]),
     "t0b_memcpy2d_d2h": (_i32, [_ctx, C.c_void_p, _sz, _u64, _sz, _sz, _sz]),
+    "t0b_memcpy_h2d_async": (_i32, [_ctx, _u64, C.c_void_p, _sz]),
+    "t0b_memcpy2d_d2h_async": (_i32, [_ctx, C.c_void_p, _sz, _u64, _sz, _sz, _sz]),
     "t0b_sync": (_i32, [_ctx]),
     "t0b_ipc_export": (_i32, [_ctx, _u64, _u8p]),
     "t0b_ipc_open": (_i32, [_ctx, _u8p, C.POINTER(_u64)]),
@@ -86,6 +89,9 @@ SIGNATURES = {
     "t0b_gemm_workspace_bytes": (_sz, [_cfgp, _u32, _u32, _u32]),
     "t0b_gemm_host": (_i32, [_ctx, _cfgp, _i32, _i32, C.c_void_p, C.c_void_p, C.c_void_p, _u32, _u32, _u32, _u64, _u64, _u64,
                              _i32, _u32]),
+    "t0b_hash_blocks": (_i32, [_ctx, _u64, _sz, _sz, _u64, _i32]),
+    "t0b_copy_d2d": (_i32, [_ctx, _u64, _sz, _u64, _sz, _sz, _sz, _i32]),
+    "t0b_multi_dst_config": (_i32, [_u32, _u32, _u32, _i32, _i32, _cfgp]),
     "t0b_gemm_multi_dst": (_i32, [_ctx, _cfgp, _i32, _i32, _u64, _u64, C.POINTER(_u64), _i32, _u32, _u32, _u32, _u64,
                                   _u64, _u64, _u64, _i32, _i32]),
     "t0b_gemm_slabs": (_i32, [_ctx, _cfgp, _u64, _u64, _u64, _u32, _u32, _u32, _u32, _i32]),
@@ -110,6 +116,10 @@ SIGNATURES = {
     "t0b_tune_cache_load": (_i32, [C.c_char_p, _u32, _u32, _u32, _cfgp, C.POINTER(_f)]),
     "t0b_tune_cache_invalidate": (_i32, [C.c_char_p, _u32, _u32, _u32]),
     "t0b_set_autotune_dir": (_i32, [_ctx, C.c_char_p]),
+    "t0b_get_or_create_bf16": (_i32, [_ctx, _u64, _u64, _sz, C.POINTER(_u64)]),
+    "t0b_invalidate_bf16": (_i32, [_ctx, _u64]),
+    "t0b_clear_bf16_cache": (_i32, [_ctx]),
+    "t0b_bf16_cache_stats": (_i32, [_ctx, C.POINTER(_u64), C.POINTER(_u64), C.POINTER(_u64)]),
     "t0b_cast_f32_to_bf16": (_i32, [_ctx, _u64, _u64, _sz, _i32]),
     "t0b_cast_f32_to_bf16_transpose": (_i32, [_ctx, _u64, _u64, _u32, _u32, _i32]),
     "t0b_rmsnorm_fwd": (_i32, [_ctx, _u64, _u64, _u64, _u64, _u32, _u32, _f, _i32]),

@@ -16,10 +16,10 @@ OUT_DIR = os.path.join(HERE, "lib")
 OUT = os.path.join(OUT_DIR, "libt0b200.so")
 OBJ_DIR = os.path.join(OUT_DIR, "obj")
 
-SOURCES = ["t0b_runtime.cu", "t0b_gemm.cu", "t0b_rowops.cu", "t0b_embedding.cu", "t0b_gemm_gen.cpp", "t0b_tile_ir.cpp"]
+SOURCES = ["t0b_runtime.cu", "t0b_gemm.cu", "t0b_rowops.cu", "t0b_embedding.cu", "t0b_util.cu", "t0b_gemm_gen.cpp", "t0b_tile_ir.cpp"]
 # The GEMM kernel variants (BN, CG, MT, ND): gemm_variant.cu compiled once per entry, side by side.
 GEMM_VARIANTS = ["256,2,2,1", "256,2,2,0", "256,2,1,0", "128,2,1,0", "256,1,1,0", "128,1,1,0", "64,1,1,0"]
-HEADERS = ["gemm_sm100.cuh", "gemm_launch.cuh", "ptx_sm100.cuh", "t0b_internal.hpp", os.path.join("..", "..", "include", "t0b200.h")]
+HEADERS = ["gemm_sm100.cuh", "gemm_launch.cuh", "ptx_sm100.cuh", "t0b_internal.hpp", "t0b_tuned_table.inc", os.path.join("..", "..", "include", "t0b200.h")]
 
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]

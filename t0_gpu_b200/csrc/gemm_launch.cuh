@@ -11,7 +11,7 @@ namespace t0b {
 
 template <int BN, int CG, int MT, int ND = 0>
 int32_t launch_variant(t0b_ctx* ctx, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc,
-                       const GemmParams& p, int num_work) {
+                       const GemmParams& p, int num_work, int cluster_sk = 0) {
     using T = GemmTraits<BN, CG, MT, ND>;
     auto kfn = gemm_bf16_tcgen05_kernel<BN, CG, MT, ND>;
     static bool configured[64] = {};
@@ -50,7 +50,10 @@ int32_t launch_variant(t0b_ctx* ctx, const CUtensorMap& ta, const CUtensorMap& t
     }
     int avail = max_clusters[dev];
     if (ctx->sm_limit > 0) avail = std::min(avail, std::max(1, ctx->sm_limit / CG));   // leave SMs to concurrent kernels
-    const int clusters = std::max(1, std::min(num_work, avail));
+    int clusters = std::max(1, std::min(num_work, avail));
+    // Cluster split-K: one CTA per work item (not persistent), clusters of `cluster_sk` consecutive CTAs; the hardware
+    // schedules whole clusters, so the K ranges of a tile always run together whatever the number of waves.
+    if (cluster_sk > 1) clusters = num_work;
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(clusters * CG, 1, 1);
     cfg.blockDim = dim3(T::kThreads, 1, 1);
@@ -58,7 +61,7 @@ int32_t launch_variant(t0b_ctx* ctx, const CUtensorMap& ta, const CUtensorMap& t
     cfg.stream = ctx->stream;
     cudaLaunchAttribute attrs[2];
     attrs[0].id = cudaLaunchAttributeClusterDimension;
-    attrs[0].val.clusterDim.x = CG;
+    attrs[0].val.clusterDim.x = cluster_sk > 1 ? cluster_sk : CG;
     attrs[0].val.clusterDim.y = 1;
     attrs[0].val.clusterDim.z = 1;
     // The kernel's set-up (barriers, TMEM allocation) overlaps the tail of the previous kernel in the stream; the
@@ -74,7 +77,7 @@ int32_t launch_variant(t0b_ctx* ctx, const CUtensorMap& ta, const CUtensorMap& t
 #ifndef T0B_VARIANT
 #define T0B_EXTERN_VARIANT(BN, CG, MT, ND)                                                                              \
     extern template int32_t launch_variant<BN, CG, MT, ND>(t0b_ctx*, const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, \
-                                                            const GemmParams&, int);
+                                                            const GemmParams&, int, int);
 T0B_GEMM_VARIANTS(T0B_EXTERN_VARIANT)
 #undef T0B_EXTERN_VARIANT
 #endif

@@ -77,6 +77,8 @@ struct GemmParams {
     int* status;
     unsigned long long wait_limit_ns;
     int tma_store;          // 1: the epilogue writes C with TMA stores through the third tensor map
+    int cluster_sk;         // > 1: split-K inside a thread-block cluster of that many CTAs (one per K range): the partial
+                            // tiles stay in shared memory and are summed over distributed shared memory; 0 = slabs
 };
 
 constexpr int kBmCta = 128;   // accumulator rows per MMA per CTA (TMEM lanes)
@@ -130,8 +132,9 @@ struct WorkItem {
 
 __device__ __forceinline__ WorkItem decode_work(const GemmParams& p, int w, int bm, int bn) {
     const int num_tiles = p.tiles_m * p.tiles_n;
-    const int split = w / num_tiles;
-    const int tile = w - split * num_tiles;
+    // Cluster split-K: the CTAs of a cluster (consecutive work items) are the K ranges of one tile.
+    const int split = p.cluster_sk > 1 ? w % p.cluster_sk : w / num_tiles;
+    const int tile = p.cluster_sk > 1 ? w / p.cluster_sk : w - split * num_tiles;
     int major_cnt = p.raster_along_n ? p.tiles_n : p.tiles_m;   // dimension that is grouped
     int minor_cnt = p.raster_along_n ? p.tiles_m : p.tiles_n;
     const int per_group = p.group * minor_cnt;
@@ -183,6 +186,29 @@ __device__ __forceinline__ bool bounded_wait(uint32_t bar, uint32_t parity, cons
             }
         }
     }
+}
+
+// The same wait for a whole warp: lane 0 polls (with a suspend-time hint, so the thread sleeps in hardware between
+// polls instead of spinning beside the MMA issuer for a whole main loop), the result is broadcast.
+__device__ __forceinline__ bool bounded_wait_warp(uint32_t bar, uint32_t parity, const WaitCtl& ctl, int code, int lane) {
+    int ok = 1;
+    if (lane == 0) {
+        ok = 0;
+        if (ptx::mbar_try_wait_hint(bar, parity, 20000u)) ok = 1;
+        else {
+            const uint64_t t0 = ptx::globaltimer_ns();
+            while (true) {
+                if (ptx::mbar_try_wait_hint(bar, parity, 20000u)) { ok = 1; break; }
+                if (*ctl.abort) break;
+                if (ptx::globaltimer_ns() - t0 > ctl.limit_ns) {
+                    *ctl.abort = 1;
+                    *reinterpret_cast<volatile int*>(ctl.status) = code;
+                    break;
+                }
+            }
+        }
+    }
+    return __shfl_sync(0xffffffffu, ok, 0) != 0;
 }
 
 __device__ __forceinline__ bool chain_has_bias(const EpiChain& e) {
@@ -273,6 +299,33 @@ __device__ __forceinline__ void flush_chunk_f32(uint32_t stage, int lane, float*
             *reinterpret_cast<float4*>(base + static_cast<long long>(row0 + r) * ld + col0 + c * 4) = q;
     }
 }
+// TMA-store path: every 32x32 chunk goes out through two 2 KiB half tiles (rows of 64 bytes, 64-byte TMA swizzle:
+// 16-byte piece c of row r sits at piece c ^ ((r >> 1) & 3)), so that one half is being read by its TMA store while
+// the warp fills the other.  f32: a half holds 16 of the chunk's columns; bf16: a half holds one whole chunk.
+__device__ __forceinline__ void stage_half_f32_sw64(uint32_t half_tile, int lane, const float* v) {
+    const uint32_t row = half_tile + lane * 64;
+    const int x = (lane >> 1) & 3;
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+        asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(row + ((j ^ x) << 4)), "f"(v[4 * j]), "f"(v[4 * j + 1]),
+                     "f"(v[4 * j + 2]), "f"(v[4 * j + 3])
+                     : "memory");
+}
+__device__ __forceinline__ void stage_chunk_bf16_sw64(uint32_t half_tile, int lane, const float (&v)[32]) {
+    const uint32_t row = half_tile + lane * 64;
+    const int x = (lane >> 1) & 3;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        __nv_bfloat162 h0 = __floats2bfloat162_rn(v[8 * j + 0], v[8 * j + 1]);
+        __nv_bfloat162 h1 = __floats2bfloat162_rn(v[8 * j + 2], v[8 * j + 3]);
+        __nv_bfloat162 h2 = __floats2bfloat162_rn(v[8 * j + 4], v[8 * j + 5]);
+        __nv_bfloat162 h3 = __floats2bfloat162_rn(v[8 * j + 6], v[8 * j + 7]);
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(row + ((j ^ x) << 4)), "r"(*reinterpret_cast<uint32_t*>(&h0)),
+                     "r"(*reinterpret_cast<uint32_t*>(&h1)), "r"(*reinterpret_cast<uint32_t*>(&h2)),
+                     "r"(*reinterpret_cast<uint32_t*>(&h3))
+                     : "memory");
+    }
+}
 // bf16 output: two 32-column chunks share one tile (32 rows x 64 bf16 = 128-byte rows), so the flush writes
 // whole 128-byte lines, local or remote.
 __device__ __forceinline__ void stage_half_bf16(uint32_t stage, int lane, int half, const float (&v)[32]) {
@@ -360,6 +413,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
     }
     ptx::tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    // Cluster split-K (single-CTA tiles only): the CTAs of the cluster are the K ranges of one tile.
+    const bool csk = (CG == 1 && MT == 1) && p.cluster_sk > 1;
     // Programmatic dependent launch: everything above (barriers, TMEM, descriptor prefetch) may run while the previous
     // kernel of the stream drains; nothing below may touch global memory before that kernel has completed.
     ptx::grid_dependency_wait();
@@ -513,7 +568,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
         constexpr int kChunks = BN / 32 / T::kEpiSplit;          // 32-column chunks per warp and tile
         const int c_begin = (T::kEpiSplit == 2) ? group * kChunks : 0;
         uint32_t slot_phase = 0;
-        const bool to_slab = p.split_k > 1;
+        const bool to_slab = p.split_k > 1 && !csk;
         const long long ld_out = to_slab ? p.ld_partial : p.ldc;
         bool vec_ok;
         if (to_slab || !p.out_bf16) {
@@ -534,7 +589,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
         const uint32_t stage = ctrl + T::kCtrlBytes + static_cast<uint32_t>(warp - 2) * 4096u;
         for (int w = cluster_id; w < num_work; w += num_clusters) {
             const WorkItem wi = decode_work(p, w, BM, BNT);
-            if (!bounded_wait(tfull_bar(slot), slot_phase, ctl, DEV_TIMEOUT_TMEM_FULL)) break;
+            if (!bounded_wait_warp(tfull_bar(slot), slot_phase, ctl, DEV_TIMEOUT_TMEM_FULL, lane)) break;
             ptx::tc_fence_after();
             const int row0 = wi.m0 + ((MT == 2 && ND == 0) ? group * kMmaM : 0) + static_cast<int>(cta_rank) * kBmCta + q * 32;
             const int n_base = wi.n0 + (ND == 1 ? group * BN : 0);
@@ -561,12 +616,44 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                 }
                 const int col0 = n_base + c * 32;
                 const int ncols = p.N - col0;
-                if (staged && out16) {
-                    const int half = c & 1;
-                    if (half == 0) {
-                        if (tma_out && lane == 0) ptx::bulk_wait_group_read<0>();   // the TMA store has read the tile
-                        __syncwarp();   // the previous pair's reads of the staging tile are done
+                if (csk) {
+                    // The partial tile goes to shared memory (the operand ring is idle: this CTA has one work item and
+                    // its last MMA has completed), row-major [128][BN] f32 with the 16-byte pieces of every 128-byte
+                    // segment XOR-swizzled by row, for the cluster-wide sum after the barrier below.
+                    const int rl = q * 32 + lane;
+                    const uint32_t seg = smem_base + static_cast<uint32_t>(rl * BN * 4 + c * 128);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j)
+                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(seg + ((j ^ (rl & 7)) << 4)), "r"(raw[4 * j]),
+                                     "r"(raw[4 * j + 1]), "r"(raw[4 * j + 2]), "r"(raw[4 * j + 3])
+                                     : "memory");
+                } else if (tma_out && out16) {
+                    if (row0 < p.M && ncols > 0) {   // warp-uniform
+                        float v[32];
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(raw[j]);
+                        if (has_epi) {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) {
+                                float b = 0.0f;
+                                if (need_bias && j < ncols) b = __ldg(p.epi.bias + col0 + j);
+                                v[j] = apply_chain(v[j], p.epi, b);
+                            }
+                        }
+                        const uint32_t half_tile = stage + static_cast<uint32_t>(c & 1) * 2048u;
+                        if (lane == 0) ptx::bulk_wait_group_read<1>();   // the store that last used this half has read it
+                        __syncwarp();
+                        stage_chunk_bf16_sw64(half_tile, lane, v);
+                        ptx::fence_proxy_async_smem();
+                        __syncwarp();
+                        if (lane == 0) {
+                            ptx::tma_store_2d(&tmap_c, half_tile, col0, row0);
+                            ptx::bulk_commit_group();
+                        }
                     }
+                } else if (staged && out16) {
+                    const int half = c & 1;
+                    if (half == 0) __syncwarp();   // the previous pair's reads of the staging tile are done
                     if (row0 < p.M && ncols > 0) {   // warp-uniform
                         float v[32];
 #pragma unroll
@@ -581,15 +668,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                         }
                         stage_half_bf16(stage, lane, half, v);
                     }
-                    if (half == 1 && tma_out) {
-                        ptx::fence_proxy_async_smem();
-                        __syncwarp();
-                        const int cbase = col0 - 32;
-                        if (row0 < p.M && cbase < p.N && lane == 0) {
-                            ptx::tma_store_2d(&tmap_c, stage, cbase, row0);
-                            ptx::bulk_commit_group();
-                        }
-                    } else if (half == 1) {
+                    if (half == 1) {
                         __syncwarp();
                         const int cbase = col0 - 32;
                         if (row0 < p.M && cbase < p.N) {
@@ -610,17 +689,26 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                                 v[j] = apply_chain(v[j], p.epi, b);
                             }
                         }
-                        if (tma_out && lane == 0) ptx::bulk_wait_group_read<0>();   // the TMA store has read the tile
+                        if (tma_out) {
+#pragma unroll
+                            for (int h = 0; h < 2; ++h) {
+                                const uint32_t half_tile = stage + static_cast<uint32_t>(h) * 2048u;
+                                if (lane == 0) ptx::bulk_wait_group_read<1>();   // the store that last used this half has read it
+                                __syncwarp();
+                                stage_half_f32_sw64(half_tile, lane, v + 16 * h);
+                                ptx::fence_proxy_async_smem();
+                                __syncwarp();
+                                if (lane == 0 && col0 + 16 * h < p.N) {
+                                    ptx::tma_store_2d(&tmap_c, half_tile, col0 + 16 * h, row0);
+                                    ptx::bulk_commit_group();
+                                }
+                            }
+                            continue;
+                        }
                         __syncwarp();   // the previous chunk's reads of the staging tile are done
                         stage_chunk_f32(stage, lane, v);
-                        if (tma_out) ptx::fence_proxy_async_smem();
                         __syncwarp();
-                        if (tma_out) {
-                            if (lane == 0) {
-                                ptx::tma_store_2d(&tmap_c, stage, col0, row0);
-                                ptx::bulk_commit_group();
-                            }
-                        } else if (to_slab) {
+                        if (to_slab) {
                             flush_chunk_f32(stage, lane, p.partial + static_cast<long long>(wi.split) * p.slab_stride, ld_out,
                                             row0, col0, p.M, p.N);
                         } else {
@@ -660,6 +748,67 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
             }
         }
         if (tma_out && lane == 0) ptx::bulk_wait_group<0>();   // every TMA store of this warp has completed
+    }
+
+    if (csk) {
+        // Every CTA of the cluster has its partial tile in shared memory after this barrier (release / acquire at
+        // cluster scope).  CTA r then sums rows [r, r+1) * 128 / sk of the tile over the sk partials IN K-RANGE ORDER,
+        // starting from +0.0 -- the arithmetic of splitk_reduce_kernel and of the reference's host-side slab sum
+        // (examples/test_gemm_correctness.rs:203-207) -- and writes them to C.  No slab ever reaches global memory.
+        ptx::cluster_arrive();
+        ptx::cluster_wait();
+        if (warp >= 2 && !*abort_flag) {
+            const int sk = p.cluster_sk;
+            const WorkItem wi = decode_work(p, blockIdx.x, BM, BNT);
+            const int rows_per = kBmCta / sk;
+            constexpr int kPiecesPerRow = BN / 4;
+            const int total = rows_per * kPiecesPerRow;
+            const bool need_bias = chain_has_bias(p.epi);
+            const bool vec_c = (p.N % 4 == 0) && (p.ldc % (p.out_bf16 ? 2 : 4) == 0) &&
+                               ((reinterpret_cast<uintptr_t>(p.c_dst[0]) & 15) == 0) && (!p.out_bf16 || p.ldc % 4 == 0);
+            for (int i = static_cast<int>(threadIdx.x) - 64; i < total; i += T::kEpiWarps * 32) {
+                const int rl = wi.split * rows_per + i / kPiecesPerRow;
+                const int pc = i % kPiecesPerRow;
+                const uint32_t off = smem_base + static_cast<uint32_t>(rl * BN * 4 + (pc >> 3) * 128 + (((pc & 7) ^ (rl & 7)) << 4));
+                float4 part[8];
+#pragma unroll
+                for (int sidx = 0; sidx < 8; ++sidx)
+                    if (sidx < sk) part[sidx] = ptx::ld_shared_cluster_v4(ptx::mapa(off, static_cast<uint32_t>(sidx)));
+                float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+                for (int sidx = 0; sidx < 8; ++sidx)
+                    if (sidx < sk) {
+                        acc[0] = acc[0] + part[sidx].x; acc[1] = acc[1] + part[sidx].y;
+                        acc[2] = acc[2] + part[sidx].z; acc[3] = acc[3] + part[sidx].w;
+                    }
+                const int row = wi.m0 + rl, col = wi.n0 + pc * 4;
+                if (row >= p.M || col >= p.N) continue;
+                if (p.epi.n > 0) {
+#pragma unroll
+                    for (int e = 0; e < 4; ++e)
+                        acc[e] = apply_chain(acc[e], p.epi, (need_bias && col + e < p.N) ? __ldg(p.epi.bias + col + e) : 0.0f);
+                }
+                if (p.out_bf16) {
+                    __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.c_dst[0]) + static_cast<long long>(row) * p.ldc + col;
+                    if (vec_c) {
+                        __nv_bfloat162 h0 = __floats2bfloat162_rn(acc[0], acc[1]), h1 = __floats2bfloat162_rn(acc[2], acc[3]);
+                        uint2 qv;
+                        qv.x = *reinterpret_cast<uint32_t*>(&h0);
+                        qv.y = *reinterpret_cast<uint32_t*>(&h1);
+                        *reinterpret_cast<uint2*>(dst) = qv;
+                    } else {
+                        for (int e = 0; e < 4 && col + e < p.N; ++e) dst[e] = __float2bfloat16_rn(acc[e]);
+                    }
+                } else {
+                    float* dst = static_cast<float*>(p.c_dst[0]) + static_cast<long long>(row) * p.ldc + col;
+                    if (vec_c) *reinterpret_cast<float4*>(dst) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+                    else for (int e = 0; e < 4 && col + e < p.N; ++e) dst[e] = acc[e];
+                }
+            }
+        }
+        // Nobody leaves while a peer may still read its shared memory.
+        ptx::cluster_arrive();
+        ptx::cluster_wait();
     }
 
     // ---------------------------------------------------------------------- teardown (normal and abort paths)

@@ -8,5 +8,5 @@
 #include "gemm_launch.cuh"
 
 namespace t0b {
-template int32_t launch_variant<T0B_VARIANT>(t0b_ctx*, const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, const GemmParams&, int);
+template int32_t launch_variant<T0B_VARIANT>(t0b_ctx*, const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, const GemmParams&, int, int);
 }  // namespace t0b

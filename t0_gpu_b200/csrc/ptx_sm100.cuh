@@ -38,6 +38,13 @@ __device__ __forceinline__ uint32_t mapa(uint32_t smem_addr, uint32_t rank) {
     return r;
 }
 
+// 16-byte load from distributed shared memory (a shared::cluster address, own CTA or a peer of the cluster).
+__device__ __forceinline__ float4 ld_shared_cluster_v4(uint32_t cluster_addr) {
+    float4 v;
+    asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(cluster_addr) : "memory");
+    return v;
+}
+
 // ------------------------------------------------------------------------------------------ mbarrier
 
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
@@ -69,6 +76,22 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
         "}"
         : "=r"(done)
         : "r"(bar), "r"(parity)
+        : "memory");
+    return done != 0;
+}
+
+// The same with a suspend-time hint: the thread may sleep in hardware for up to about `hint_ns` before the instruction
+// returns false (it returns at once when the phase completes).
+__device__ __forceinline__ bool mbar_try_wait_hint(uint32_t bar, uint32_t parity, uint32_t hint_ns) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t"
+        "}"
+        : "=r"(done)
+        : "r"(bar), "r"(parity), "r"(hint_ns)
         : "memory");
     return done != 0;
 }

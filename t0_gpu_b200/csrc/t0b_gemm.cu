@@ -34,7 +34,7 @@ EncodeTiledFn encode_tiled_fn() {
 }
 
 // 2-D tensor map (bf16, or f32 when elem == 4): inner (contiguous) extent d0, outer extent d1, outer pitch ld
-// elements, box b0 x b1, 128-byte swizzle; out-of-bounds elements read as zero and are not written.
+// elements, box b0 x b1, swizzled; out-of-bounds elements read as zero and are not written.
 int32_t get_tmap(t0b_ctx* ctx, uint64_t ptr, uint64_t d0, uint64_t d1, uint64_t ld, uint32_t b0, uint32_t b1,
                  CUtensorMap* out, uint32_t elem = 2) {
     t0b_ctx::TmapKey key{ptr, d0, d1, ld, b0, b1, elem};
@@ -49,8 +49,11 @@ int32_t get_tmap(t0b_ctx* ctx, uint64_t ptr, uint64_t d0, uint64_t d1, uint64_t 
     cuuint64_t strides[1] = {ld * elem};
     cuuint32_t box[2] = {b0, b1};
     cuuint32_t estr[2] = {1, 1};
+    // Boxes with 128-byte rows (the operand tiles) use the 128-byte swizzle, boxes with 64-byte rows (the epilogue's
+    // half tiles) the 64-byte swizzle.
+    const CUtensorMapSwizzle swz = (b0 * elem == 64) ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B;
     CUresult r = fn(out, elem == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, reinterpret_cast<void*>(ptr), dims, strides, box, estr,
-                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, swz, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS)
         return set_error(ctx, T0B_ERR_INVALID,
@@ -159,11 +162,9 @@ int32_t run_gemm(t0b_ctx* ctx, const GemmCall& g) {
     t0b_gemm_config cfg;
     if (g.cfg) cfg = *g.cfg;
     else {
-        const std::string key = std::to_string(g.m) + "x" + std::to_string(g.n) + "x" + std::to_string(g.k) + "/" +
-                                std::to_string(g.trans_a) + std::to_string(g.trans_b) + std::to_string(g.out_bf16);
-        auto it = ctx->tuned.find(key);
-        if (it != ctx->tuned.end()) cfg = it->second;
-        else default_b200_config(g.m, g.k, g.n, ctx->num_sms, &cfg);
+        // Measured in this process (t0b_tune), else the table shipped with the library, else the cost model.
+        if (!tuned_lookup(g.m, g.n, g.k, g.trans_a, g.trans_b, g.out_bf16, &cfg, nullptr))
+            default_b200_config(g.m, g.k, g.n, ctx->num_sms, &cfg);
         if (g.no_auto_split) cfg.split_k = 0;
     }
     if (g.slabs_only) cfg.split_k = g.force_split;
@@ -176,16 +177,40 @@ int32_t run_gemm(t0b_ctx* ctx, const GemmCall& g) {
 
     const size_t elem = g.out_bf16 ? 2 : 4;
     if (g.k == 0) {
-        // Empty contraction: the result is epilogue(0); only the plain store is meaningful.
-        for (int d = 0; d < g.n_dst; ++d)
-            for (uint32_t r = 0; r < g.m; ++r) {
-                int32_t rc = check_cuda(ctx, cudaMemsetAsync(reinterpret_cast<char*>(g.c_dst[d]) + r * g.ldc * elem, 0,
-                                                             g.n * elem, ctx->stream), "cudaMemsetAsync(k=0)");
+        // Empty contraction: every accumulator is +0.0, so the result is epilogue(0).
+        if (g.slabs_only) {
+            // Every slab the caller expects carries an empty K range (the slabs are dense and adjacent).
+            return check_cuda(ctx, cudaMemsetAsync(reinterpret_cast<void*>(g.c_dst[0]), 0,
+                                                   static_cast<size_t>(g.force_split) * g.m * g.n * 4, ctx->stream),
+                              "cudaMemsetAsync(k=0 slabs)");
+        }
+        for (int d = 0; d < g.n_dst; ++d) {
+            if (g.epi.n == 0) {
+                int32_t rc = check_cuda(ctx, cudaMemset2DAsync(reinterpret_cast<void*>(g.c_dst[d]), g.ldc * elem, 0, g.n * elem, g.m,
+                                                               ctx->stream), "cudaMemset2DAsync(k=0)");
                 if (rc != T0B_OK) return rc;
+                continue;
             }
+            // With a fused store-phase chain the CUDA-core kernel applies it to the zero accumulators.
+            SimtParams sp{};
+            sp.a = reinterpret_cast<const __nv_bfloat16*>(g.a);
+            sp.b = reinterpret_cast<const __nv_bfloat16*>(g.b);
+            sp.lda = g.lda; sp.ldb = g.ldb; sp.M = g.m; sp.N = g.n; sp.K = 0;
+            sp.trans_a = g.trans_a; sp.trans_b = g.trans_b; sp.k_begin = 0; sp.k_end = 0;
+            sp.c = reinterpret_cast<void*>(g.c_dst[d]); sp.ldc = g.ldc; sp.out_bf16 = g.out_bf16; sp.epi = g.epi;
+            dim3 grid((g.n + 63) / 64, (g.m + 63) / 64);
+            gemm_bf16_simt_kernel<<<grid, 256, 0, ctx->stream>>>(sp);
+            int32_t rc = check_cuda(ctx, cudaGetLastError(), "simt gemm launch (k=0)");
+            if (rc != T0B_OK) return rc;
+            ++ctx->launches;
+        }
         return T0B_OK;
     }
 
+    // Split-K inside clusters (see below) needs no slabs at all.
+    const bool cluster_sk_possible = !g.slabs_only && plan.split_k > 1 && plan.split_k <= 8 && (plan.split_k & (plan.split_k - 1)) == 0 &&
+                                     g.n_dst == 1 && plan.use_tma && plan.cta_group == 1 && plan.m_tiles == 1 && plan.n_tiles == 1 &&
+                                     ctx->cluster_splitk;
     // Where do split-K partials go?
     float* partial = nullptr;
     uint64_t slab_stride = static_cast<uint64_t>(g.m) * g.n, ld_partial = g.n;
@@ -199,7 +224,7 @@ int32_t run_gemm(t0b_ctx* ctx, const GemmCall& g) {
                                     "cudaMemsetAsync(empty slabs)");
             if (rc != T0B_OK) return rc;
         }
-    } else if (sk > 1) {
+    } else if (sk > 1 && !cluster_sk_possible) {
         const size_t need = static_cast<size_t>(sk) * slab_stride * 4;
         if (g.workspace) {
             if (g.workspace_bytes < need)
@@ -221,6 +246,12 @@ int32_t run_gemm(t0b_ctx* ctx, const GemmCall& g) {
         }
     }
     const bool to_slabs = g.slabs_only || sk > 1;
+    // Split-K on a single-CTA tile with up to eight K ranges runs as thread-block clusters: the CTAs of a cluster take the
+    // K ranges of one tile, keep their partial tiles in shared memory and sum them over distributed shared memory in
+    // K-range order -- one launch, no slabs in global memory, the same bits as the slab sum.  T0B_CLUSTER_SPLITK=0 keeps
+    // the slab path (GEMM into slabs + reduce kernel), as do CTA-pair tiles, more than eight ranges, the unreduced-slab
+    // contract and operands TMA cannot address.
+    const bool cluster_sk = cluster_sk_possible;
 
     if (!plan.use_tma) {
         // Operands TMA cannot address: CUDA-core kernel, one launch per K range.
@@ -299,11 +330,12 @@ int32_t run_gemm(t0b_ctx* ctx, const GemmCall& g) {
             const uint32_t oelem = p.out_bf16 ? 2u : 4u;
             // TMA clips a store at the tensor edge in 16-byte units, so N must be a whole number of them for
             // nothing beyond column N to be touched.
+            p.cluster_sk = cluster_sk ? static_cast<int>(sk) : 0;
             const bool ok = !to_slabs && p.n_dst == 1 && (g.c_dst[0] % 16 == 0) && ((static_cast<uint64_t>(p.ldc) * oelem) % 16 == 0) &&
                             ((static_cast<uint64_t>(g.n) * oelem) % 16 == 0);
             p.tma_store = 0;
             if (ok) {
-                rc = get_tmap(ctx, g.c_dst[0], g.n, g.m, static_cast<uint64_t>(p.ldc), p.out_bf16 ? 64 : 32, 32, &tc, oelem);
+                rc = get_tmap(ctx, g.c_dst[0], g.n, g.m, static_cast<uint64_t>(p.ldc), p.out_bf16 ? 32 : 16, 32, &tc, oelem);   // 64-byte rows
                 if (rc != T0B_OK) return rc;
                 p.tma_store = 1;
             }
@@ -315,15 +347,15 @@ int32_t run_gemm(t0b_ctx* ctx, const GemmCall& g) {
             else if (plan.bn == 256) rc = launch_variant<256, 2, 1>(ctx, ta, tb, tc, p, num_work);
             else rc = launch_variant<128, 2, 1>(ctx, ta, tb, tc, p, num_work);
         } else {
-            if (plan.bn == 256) rc = launch_variant<256, 1, 1>(ctx, ta, tb, tc, p, num_work);
-            else if (plan.bn == 128) rc = launch_variant<128, 1, 1>(ctx, ta, tb, tc, p, num_work);
-            else rc = launch_variant<64, 1, 1>(ctx, ta, tb, tc, p, num_work);
+            if (plan.bn == 256) rc = launch_variant<256, 1, 1>(ctx, ta, tb, tc, p, num_work, p.cluster_sk);
+            else if (plan.bn == 128) rc = launch_variant<128, 1, 1>(ctx, ta, tb, tc, p, num_work, p.cluster_sk);
+            else rc = launch_variant<64, 1, 1>(ctx, ta, tb, tc, p, num_work, p.cluster_sk);
         }
         if (rc != T0B_OK) return rc;
         ++ctx->launches;
     }
 
-    if (!g.slabs_only && sk > 1) {
+    if (!g.slabs_only && sk > 1 && !cluster_sk) {
         for (int d = 0; d < g.n_dst; ++d) {
             int32_t rc = launch_reduce(ctx, partial, sk, g.m, g.n, slab_stride, ld_partial, reinterpret_cast<void*>(g.c_dst[d]),
                                        g.ldc, g.out_bf16, g.epi);
@@ -514,8 +546,24 @@ int32_t t0b_gemm_host(t0b_ctx* ctx, const t0b_gemm_config* cfg, int32_t trans_a,
     if (rc != T0B_OK) return rc;
     for (cudaError_t x : {e, e1, e2, e3})
         if (x != cudaSuccess) return check_cuda(ctx, x, "gemm_host");
-    const int st = t0b_device_status(ctx, 0);
+    const int st = take_device_status(ctx);
     if (st != 0) return set_error(ctx, T0B_ERR_DEVICE, "gemm_host: device status %d (a bounded in-kernel wait ran out)", st);
+    return T0B_OK;
+}
+
+int32_t t0b_multi_dst_config(uint32_t m, uint32_t k, uint32_t n_local, int32_t n_dst, int32_t num_sms, t0b_gemm_config* out) {
+    if (!out || n_dst < 1 || n_dst > kMaxDst) return T0B_ERR_INVALID;
+    default_b200_config(m, k, n_local, num_sms > 0 ? num_sms : 148, out);
+    // Stores to a peer retire at the NVLink rate, far below the rate the epilogue can issue them, so with peers the
+    // epilogue warps spend most of a tile's time blocked in stores.  The tiles that keep both TMEM accumulators for one
+    // tile (256x512, 512x256) cannot start the next main loop until that epilogue is over; the 256x256 tile
+    // double-buffers its accumulators, so the stores of tile i retire while tile i+1 is multiplied.
+    if (n_dst > 1 && (out->tile_m >= 512 || out->tile_n >= 512)) {
+        out->tile_m = 256;
+        out->tile_n = 256;
+        out->wg_size = 192;
+    }
+    out->split_k = 0;   // the fused store writes final values; there is no slab stage
     return T0B_OK;
 }
 
@@ -534,11 +582,7 @@ int32_t t0b_gemm_multi_dst(t0b_ctx* ctx, const t0b_gemm_config* cfg, int32_t tra
         local.split_k = 0;   // the fused store writes final values; no slab stage
         g.cfg = &local;
     } else {
-        default_b200_config(m, k, n_local, ctx->num_sms, &local);
-        // Remote stores are slow to retire: with peers, prefer the tile whose two TMEM accumulators double-buffer,
-        // so the epilogue of one tile (which issues the peer stores) overlaps the main loop of the next.
-        if (n_dst > 1 && local.tile_m >= 512) { local.tile_m = 256; local.wg_size = 192; }
-        local.split_k = 0;
+        t0b_multi_dst_config(m, k, n_local, n_dst, ctx->num_sms, &local);
         g.cfg = &local;
     }
     g.trans_a = trans_a != 0; g.trans_b = trans_b != 0; g.a = a; g.b = b;
@@ -715,7 +759,7 @@ int32_t t0b_gemm_time(t0b_ctx* ctx, const t0b_gemm_config* cfg, int32_t trans_a,
     cudaEventDestroy(e1);
     if (rc != T0B_OK) return rc;
     if (e != cudaSuccess) return check_cuda(ctx, e, "gemm_time");
-    const int st = t0b_device_status(ctx, 0);
+    const int st = take_device_status(ctx);
     if (st != 0) return set_error(ctx, T0B_ERR_DEVICE, "gemm_time: device status %d", st);
     *ms = total / static_cast<float>(iters);
     return T0B_OK;
@@ -726,14 +770,12 @@ int32_t t0b_tune(t0b_ctx* ctx, uint32_t m, uint32_t n, uint32_t k, int32_t trans
     int32_t rc = precheck(ctx);
     if (rc != T0B_OK) return rc;
     if (!best || m == 0 || n == 0 || k == 0) return set_error(ctx, T0B_ERR_INVALID, "tune: bad arguments");
-    const std::string tkey = std::to_string(m) + "x" + std::to_string(n) + "x" + std::to_string(k) + "/" +
-                             std::to_string(trans_a != 0) + std::to_string(trans_b != 0) + std::to_string(out_dtype == T0B_OUT_BF16);
     if (!ctx->autotune_dir.empty() && !trans_a && trans_b && out_dtype == T0B_OUT_F32) {
         // The disk cache is keyed by (M, N, K) only, like the reference's; it describes the NT / f32-out kernel.
         float tf = 0.0f;
         if (t0b_tune_cache_load(ctx->autotune_dir.c_str(), m, n, k, best, &tf) == T0B_OK) {
             if (best_tflops) *best_tflops = tf;
-            ctx->tuned[tkey] = *best;
+            tuned_remember(m, n, k, trans_a, trans_b, out_dtype == T0B_OUT_BF16, *best);
             return T0B_OK;
         }
     }
@@ -742,19 +784,19 @@ int32_t t0b_tune(t0b_ctx* ctx, uint32_t m, uint32_t n, uint32_t k, int32_t trans
     rc = t0b_alloc(ctx, static_cast<size_t>(m) * k * 2, &a);
     if (rc == T0B_OK) rc = t0b_alloc(ctx, static_cast<size_t>(n) * k * 2, &b);
     if (rc == T0B_OK) rc = t0b_alloc(ctx, static_cast<size_t>(m) * n * elem, &c);
-    if (rc != T0B_OK) return rc;
+    const uint64_t lda = trans_a ? m : k, ldb = trans_b ? k : n;
+    float best_ms = 1e30f;
+    if (rc != T0B_OK) goto done;
     {
         const float scale = 1.7f / sqrtf(static_cast<float>(k));   // unit-variance-like products, as in the benchmark inputs
         fill_random_bf16_kernel<<<ctx->num_sms * 8, 256, 0, ctx->stream>>>(reinterpret_cast<__nv_bfloat16*>(a), static_cast<size_t>(m) * k, 0x1234u, scale);
         fill_random_bf16_kernel<<<ctx->num_sms * 8, 256, 0, ctx->stream>>>(reinterpret_cast<__nv_bfloat16*>(b), static_cast<size_t>(n) * k, 0x5678u, scale);
         rc = check_cuda(ctx, cudaGetLastError(), "tuner fill");
-        if (rc != T0B_OK) return rc;
+        if (rc != T0B_OK) goto done;
     }
-    const uint64_t lda = trans_a ? m : k, ldb = trans_b ? k : n;
     static const char* tiles[] = {"b200_256x512", "b200_512x256", "b200_256x256", "b200_256x128", "b200_128x256", "b200_128x128", "b200_128x64"};
-    const uint32_t kb_total = (k + 63) / 64;
-    float best_ms = 1e30f;
     for (const char* t : tiles) {
+        const uint32_t kb_total = (k + 63) / 64;
         for (uint32_t sk = 1; sk <= 16; sk *= 2) {
             if (sk > 1 && kb_total / sk < 2) break;
             t0b_gemm_config cfg;
@@ -775,14 +817,14 @@ int32_t t0b_tune(t0b_ctx* ctx, uint32_t m, uint32_t n, uint32_t k, int32_t trans
         }
     }
 done:
-    t0b_recycle(ctx, a);
-    t0b_recycle(ctx, b);
-    t0b_recycle(ctx, c);
+    // Every exit path returns the operands to the pool (only the ones that were obtained).
+    if (a) t0b_recycle(ctx, a);
+    if (b) t0b_recycle(ctx, b);
+    if (c) t0b_recycle(ctx, c);
     if (rc != T0B_OK) return rc;
-    if (best_tflops) *best_tflops = 2.0f * m * n * static_cast<float>(k) / (best_ms * 1e-3f) / 1e12f;
-    const std::string key = std::to_string(m) + "x" + std::to_string(n) + "x" + std::to_string(k) + "/" +
-                            std::to_string(trans_a != 0) + std::to_string(trans_b != 0) + std::to_string(out_dtype == T0B_OUT_BF16);
-    ctx->tuned[key] = *best;
+    const float tflops = 2.0f * m * n * static_cast<float>(k) / (best_ms * 1e-3f) / 1e12f;
+    if (best_tflops) *best_tflops = tflops;
+    tuned_remember(m, n, k, trans_a, trans_b, out_dtype == T0B_OUT_BF16, *best);   // config-less GEMM calls and t0b_auto_select answer from it
     if (!ctx->autotune_dir.empty() && !trans_a && trans_b && out_dtype == T0B_OUT_F32)
         t0b_tune_cache_save(ctx->autotune_dir.c_str(), m, n, k, best, best_tflops ? *best_tflops : 0.0f);
     return T0B_OK;

@@ -10,7 +10,9 @@
 #include <cstring>
 #include <fstream>
 #include <sstream>
+#include <mutex>
 #include <string>
+#include <unordered_map>
 
 #include "t0b_internal.hpp"
 
@@ -101,6 +103,64 @@ int stages_for(uint32_t bn, uint32_t cg, uint32_t mt) {
 }  // namespace
 
 namespace t0b {
+
+// ---- measured configs: this process's tuner results, then the shipped table ------------------------------------
+struct TunedRow {
+    uint32_t m, n, k;
+    int trans_a, trans_b, out_bf16;
+    const char* tile;          // preset name
+    uint32_t split_k, swap_grid;
+    float tflops;
+};
+// Measured on B200 with t0b_tune (python -m t0_gpu_b200.make_tuned_table), one row per benchmark shape and layout.
+static const TunedRow kShippedTable[] = {
+#include "t0b_tuned_table.inc"
+};
+
+static std::mutex g_tuned_mu;
+static std::unordered_map<std::string, t0b_gemm_config>& process_tuned() {
+    static std::unordered_map<std::string, t0b_gemm_config> map;
+    return map;
+}
+
+std::string tuned_key(uint32_t m, uint32_t n, uint32_t k, int trans_a, int trans_b, int out_bf16) {
+    return std::to_string(m) + "x" + std::to_string(n) + "x" + std::to_string(k) + "/" + std::to_string(trans_a != 0) +
+           std::to_string(trans_b != 0) + std::to_string(out_bf16 != 0);
+}
+
+void tuned_remember(uint32_t m, uint32_t n, uint32_t k, int trans_a, int trans_b, int out_bf16, const t0b_gemm_config& cfg) {
+    std::lock_guard<std::mutex> lk(g_tuned_mu);
+    process_tuned()[tuned_key(m, n, k, trans_a, trans_b, out_bf16)] = cfg;
+}
+
+void tuned_forget(uint32_t m, uint32_t n, uint32_t k) {
+    std::lock_guard<std::mutex> lk(g_tuned_mu);
+    for (int bits = 0; bits < 8; ++bits) process_tuned().erase(tuned_key(m, n, k, bits & 4, bits & 2, bits & 1));
+}
+
+// source: 2 = measured in this process, 1 = the shipped table.
+bool tuned_lookup(uint32_t m, uint32_t n, uint32_t k, int trans_a, int trans_b, int out_bf16, t0b_gemm_config* out, int* source) {
+    {
+        std::lock_guard<std::mutex> lk(g_tuned_mu);
+        auto it = process_tuned().find(tuned_key(m, n, k, trans_a, trans_b, out_bf16));
+        if (it != process_tuned().end()) {
+            *out = it->second;
+            if (source) *source = 2;
+            return true;
+        }
+    }
+    for (const TunedRow& r : kShippedTable) {
+        if (r.m != m || r.n != n || r.k != k || (r.trans_a != 0) != (trans_a != 0) || (r.trans_b != 0) != (trans_b != 0) ||
+            (r.out_bf16 != 0) != (out_bf16 != 0))
+            continue;
+        if (t0b_config_preset(r.tile, out) != T0B_OK) continue;
+        out->split_k = r.split_k > 1 ? r.split_k : 0;
+        out->swap_grid = r.swap_grid;
+        if (source) *source = 1;
+        return true;
+    }
+    return false;
+}
 
 // Pick the B200 tile for a shape with a small cost model whose constants were measured on B200 (on-device tuner,
 // random operands, SM clock ~1.5 GHz under tensor load).  It stands where the reference has its RDNA3 cost model
@@ -269,8 +329,23 @@ int32_t t0b_config_is_feasible(const t0b_gemm_config* c) {
 
 int32_t t0b_auto_select(uint32_t m, uint32_t k, uint32_t n, t0b_gemm_config* out) {
     if (!out || m == 0 || n == 0 || k == 0) return T0B_ERR_INVALID;
+    // Like the reference's predict_best over its tune cache (src/t0/cost_model.rs:593-601, 788-1078): a measurement of
+    // this process first, then the table measured on B200 that ships with the library, then the cost model.  The
+    // call carries no layout, so the NT / f32 entry (the reference's only layout) is preferred, then NN, then any.
+    static const int order[][3] = {{0, 1, 0}, {0, 0, 0}, {1, 0, 0}, {1, 1, 0}, {0, 1, 1}, {0, 0, 1}, {1, 0, 1}, {1, 1, 1}};
+    for (const auto& o : order)
+        if (t0b::tuned_lookup(m, n, k, o[0], o[1], o[2], out, nullptr)) return T0B_OK;
     t0b::default_b200_config(m, k, n, 148, out);
     return T0B_OK;
+}
+
+int32_t t0b_auto_select_source(uint32_t m, uint32_t k, uint32_t n, int32_t trans_a, int32_t trans_b, int32_t out_dtype,
+                               t0b_gemm_config* out) {
+    if (!out || m == 0 || n == 0 || k == 0) return T0B_ERR_INVALID;
+    int source = 0;
+    if (t0b::tuned_lookup(m, n, k, trans_a != 0, trans_b != 0, out_dtype == T0B_OUT_BF16, out, &source)) return source;
+    t0b::default_b200_config(m, k, n, 148, out);
+    return 0;
 }
 
 int32_t t0b_auto_select_legacy(uint32_t m, uint32_t k, uint32_t n, t0b_gemm_config* out) {
@@ -472,6 +547,7 @@ int32_t t0b_tune_cache_load(const char* dir, uint32_t m, uint32_t n, uint32_t k,
 
 int32_t t0b_tune_cache_invalidate(const char* dir, uint32_t m, uint32_t n, uint32_t k) {
     std::remove(tune_path(dir, m, n, k).c_str());
+    t0b::tuned_forget(m, n, k);   // and what this process measured for the shape (GemmTuner::invalidate, auto_gemm.rs:394-397)
     return T0B_OK;
 }
 

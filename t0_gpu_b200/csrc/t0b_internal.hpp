@@ -18,6 +18,7 @@ struct t0b_ctx {
     int device = 0;
     int num_sms = 148;
     bool pdl = true;            // launch GEMMs with programmatic stream serialization (T0B_PDL=0 turns it off)
+    bool cluster_splitk = true; // split-K of single-CTA tiles runs as thread-block clusters (T0B_CLUSTER_SPLITK=0: slabs + reduce kernel)
     int sm_limit = 0;           // > 0: the persistent GEMM kernels occupy at most this many SMs
     cudaStream_t own_stream = nullptr;
     cudaStream_t stream = nullptr;
@@ -29,6 +30,7 @@ struct t0b_ctx {
     int* status_host = nullptr;
     int* status_dev = nullptr;
     unsigned long long wait_limit_ns = 2000000000ull;
+    int last_status = 0;        // the code most recently taken from the status word (kept for t0b_device_status)
     // Buffer pool keyed by 4 KiB-rounded size.
     std::multimap<size_t, void*> pool_free;
     std::unordered_map<void*, size_t> live;
@@ -36,6 +38,10 @@ struct t0b_ctx {
     // Grow-only split-K workspace.
     void* ws = nullptr;
     size_t ws_bytes = 0;
+    // bf16 copies of f32 weight buffers, by caller-chosen tensor id (GpuRuntime::bf16_cache, src/ignis/gpu_context.rs:392-432).
+    struct Bf16Entry { uint64_t ptr; size_t n; };
+    std::unordered_map<uint64_t, Bf16Entry> bf16_cache;
+    uint64_t bf16_conversions = 0, bf16_hits = 0;
     // Tensor-map cache.
     struct TmapKey {
         uint64_t ptr, d0, d1, ld;
@@ -61,11 +67,10 @@ struct t0b_ctx {
     std::unordered_map<uint64_t, cudaGraphExec_t> graphs;
     uint64_t next_graph = 1;
     uint64_t launches = 0;
-    // In-memory autotune results keyed by "MxNxK/ta/tb/out".
-    std::unordered_map<std::string, t0b_gemm_config> tuned;
     std::string autotune_dir;   // empty: the disk cache is not consulted
     // Copy streams of the host-buffer GEMM (created on first use).
     cudaStream_t h2d_stream = nullptr, d2h_stream = nullptr;
+    bool d2h_pending = false;   // an asynchronous read-back was queued since the last t0b_sync
 };
 
 namespace t0b {
@@ -78,9 +83,17 @@ constexpr int kDevBadIndex = 110;
 int32_t precheck(t0b_ctx* ctx);                 // null / poisoned checks, sets the device
 // Launch-error check (+ sync and status-word check when !async). `count` kernels are added to the launch counter.
 int32_t finish(t0b_ctx* ctx, int32_t async, const char* what, int count = 1);
+// Read the status word; a non-zero code is moved to ctx->last_status and the word is cleared, so one failed kernel is
+// reported by one call and does not fail the calls after it.
+int take_device_status(t0b_ctx* ctx);
 
 // Host-side GemmConfig logic (t0b_gemm_gen.cpp).
 void default_b200_config(uint32_t m, uint32_t k, uint32_t n, int num_sms, t0b_gemm_config* out);
+
+// Measured configs (t0b_gemm_gen.cpp): results of t0b_tune in this process, then the table shipped with the library.
+bool tuned_lookup(uint32_t m, uint32_t n, uint32_t k, int trans_a, int trans_b, int out_bf16, t0b_gemm_config* out, int* source);
+void tuned_remember(uint32_t m, uint32_t n, uint32_t k, int trans_a, int trans_b, int out_bf16, const t0b_gemm_config& cfg);
+void tuned_forget(uint32_t m, uint32_t n, uint32_t k);
 
 struct PlanInput {
     uint32_t m, n, k;

@@ -11,6 +11,8 @@
 #include <cstdlib>
 
 #include "ptx_sm100.cuh"
+#include <mutex>
+
 #include "t0b_internal.hpp"
 
 using namespace t0b;
@@ -818,7 +820,9 @@ int32_t t0b_rmsnorm_bwd(t0b_ctx* ctx, uint64_t dy, uint64_t x, uint64_t weight, 
 // Make that first call outside any stream capture.
 constexpr size_t kNoAllocScratchFloats = 512u * 1024u;   // 2 MiB
 static __device__ __align__(256) float g_rmsnorm_bwd_scratch[kNoAllocScratchFloats];
+// Per-device address of the array, shared by every context of the process: guarded by its own mutex.
 static float* g_rmsnorm_bwd_scratch_addr[64] = {};
+static std::mutex g_rmsnorm_bwd_scratch_mu;
 
 int32_t t0b_rmsnorm_bwd_noalloc(t0b_ctx* ctx, uint64_t dy, uint64_t x, uint64_t weight, uint64_t dx, uint64_t dgamma,
                                 uint32_t rows, uint32_t cols, float eps, int32_t async) {
@@ -833,11 +837,17 @@ int32_t t0b_rmsnorm_bwd_noalloc(t0b_ctx* ctx, uint64_t dy, uint64_t x, uint64_t 
                          "(2 MiB); use t0b_rmsnorm_bwd with caller-provided scratch",
                          kDgammaRowBlocks, need, kNoAllocScratchFloats);
     if (ctx->device < 0 || ctx->device >= 64) return set_error(ctx, T0B_ERR_INVALID, "rmsnorm_bwd_noalloc: device index out of range");
-    if (rows == 0) return check_cuda(ctx, cudaMemsetAsync(reinterpret_cast<void*>(dgamma), 0, static_cast<size_t>(cols) * 4, ctx->stream),
-                                     "cudaMemsetAsync(dgamma)");
+    if (rows == 0) {
+        // No rows: dgamma is a sum over nothing.  The memset is ordered on the stream like a kernel, and a synchronous
+        // call waits for it like any other.
+        rc = check_cuda(ctx, cudaMemsetAsync(reinterpret_cast<void*>(dgamma), 0, static_cast<size_t>(cols) * 4, ctx->stream),
+                        "cudaMemsetAsync(dgamma)");
+        if (rc != T0B_OK) return rc;
+        return finish(ctx, async, "rmsnorm_bwd_noalloc", 0);
+    }
     float* scratch = nullptr;
     {
-        std::lock_guard<std::recursive_mutex> lk(ctx->mu);
+        std::lock_guard<std::mutex> lk(g_rmsnorm_bwd_scratch_mu);
         scratch = g_rmsnorm_bwd_scratch_addr[ctx->device];
         if (!scratch) {
             rc = check_cuda(ctx, cudaGetSymbolAddress(reinterpret_cast<void**>(&scratch), g_rmsnorm_bwd_scratch),

@@ -42,6 +42,17 @@ int32_t precheck(t0b_ctx* ctx) {
     return T0B_OK;
 }
 
+int take_device_status(t0b_ctx* ctx) {
+    if (!ctx || !ctx->status_host) return 0;
+    volatile int* w = reinterpret_cast<volatile int*>(ctx->status_host);
+    const int st = *w;
+    if (st != 0) {
+        ctx->last_status = st;
+        *w = 0;
+    }
+    return st;
+}
+
 int32_t finish(t0b_ctx* ctx, int32_t async, const char* what, int count) {
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return check_cuda(ctx, e, what);
@@ -49,7 +60,7 @@ int32_t finish(t0b_ctx* ctx, int32_t async, const char* what, int count) {
     if (async || ctx->capturing) return T0B_OK;
     e = cudaStreamSynchronize(ctx->stream);
     if (e != cudaSuccess) return check_cuda(ctx, e, what);
-    const int st = *reinterpret_cast<volatile int*>(ctx->status_host);
+    const int st = take_device_status(ctx);
     if (st != 0) return set_error(ctx, T0B_ERR_DEVICE, "%s: device status %d (101-105: a bounded in-kernel wait ran out; 110: an index outside its table)", what, st);
     return T0B_OK;
 }
@@ -59,6 +70,17 @@ int32_t finish(t0b_ctx* ctx, int32_t async, const char* what, int count) {
 using namespace t0b;
 
 static size_t round4k(size_t b) { return (b + 4095) & ~static_cast<size_t>(4095); }
+
+// A cached bf16 copy keyed by this device address (the default key of an f32 weight buffer) describes contents that are
+// about to change or go away: drop it.  Copies under caller-chosen ids are the caller's to invalidate.
+static void drop_bf16_of(t0b_ctx* ctx, uint64_t f32_addr) {
+    if (ctx->bf16_cache.empty()) return;
+    auto it = ctx->bf16_cache.find(f32_addr);
+    if (it == ctx->bf16_cache.end()) return;
+    const uint64_t copy = it->second.ptr;
+    ctx->bf16_cache.erase(it);
+    t0b_recycle(ctx, copy);
+}
 
 extern "C" {
 
@@ -83,6 +105,7 @@ int32_t t0b_ctx_create(int32_t device, t0b_ctx** out) {
     if (rc == T0B_OK) {
         ctx->num_sms = prop.multiProcessorCount;
         if (const char* e = std::getenv("T0B_PDL")) ctx->pdl = std::atoi(e) != 0;
+        if (const char* e = std::getenv("T0B_CLUSTER_SPLITK")) ctx->cluster_splitk = std::atoi(e) != 0;
         rc = check_cuda(ctx, cudaStreamCreateWithFlags(&ctx->own_stream, cudaStreamNonBlocking), "cudaStreamCreate");
         ctx->stream = ctx->own_stream;
     }
@@ -121,7 +144,19 @@ void t0b_ctx_destroy(t0b_ctx* ctx) {
 int32_t t0b_ctx_set_stream(t0b_ctx* ctx, void* s) {
     if (!ctx) return T0B_ERR_INVALID;
     std::lock_guard<std::recursive_mutex> lk(ctx->mu);
-    ctx->stream = s ? static_cast<cudaStream_t>(s) : ctx->own_stream;
+    cudaStream_t next = s ? static_cast<cudaStream_t>(s) : ctx->own_stream;
+    if (next != ctx->stream && !ctx->capturing) {
+        // Work queued on the old stream may still use buffers that were recycled to the pool (or the split-K
+        // workspace); everything launched on the new stream is ordered behind it.
+        cudaSetDevice(ctx->device);
+        cudaEvent_t ev = nullptr;
+        cudaError_t e = cudaEventCreateWithFlags(&ev, cudaEventDisableTiming);
+        if (e == cudaSuccess) e = cudaEventRecord(ev, ctx->stream);
+        if (e == cudaSuccess) e = cudaStreamWaitEvent(next, ev, 0);
+        if (ev) cudaEventDestroy(ev);
+        if (e != cudaSuccess) return check_cuda(ctx, e, "t0b_ctx_set_stream (ordering the new stream behind the old)");
+    }
+    ctx->stream = next;
     return T0B_OK;
 }
 
@@ -143,8 +178,13 @@ int32_t t0b_set_sm_limit(t0b_ctx* ctx, int32_t sms) {
 
 int32_t t0b_device_status(t0b_ctx* ctx, int32_t clear) {
     if (!ctx || !ctx->status_host) return 0;
-    const int st = *reinterpret_cast<volatile int*>(ctx->status_host);
-    if (clear) *reinterpret_cast<volatile int*>(ctx->status_host) = 0;
+    std::lock_guard<std::recursive_mutex> lk(ctx->mu);
+    const int word = *reinterpret_cast<volatile int*>(ctx->status_host);
+    const int st = word != 0 ? word : ctx->last_status;
+    if (clear) {
+        *reinterpret_cast<volatile int*>(ctx->status_host) = 0;
+        ctx->last_status = 0;
+    }
     return st;
 }
 
@@ -201,6 +241,8 @@ int32_t t0b_recycle(t0b_ctx* ctx, uint64_t dptr) {
     void* p = reinterpret_cast<void*>(dptr);
     auto it = ctx->live.find(p);
     if (it == ctx->live.end()) return set_error(ctx, T0B_ERR_INVALID, "t0b_recycle: unknown buffer %p", p);
+    drop_bf16_of(ctx, dptr);
+    it = ctx->live.find(p);
     ctx->pool_free.emplace(it->second, p);
     ctx->pool_cached += it->second;
     ctx->live.erase(it);
@@ -213,7 +255,8 @@ int32_t t0b_free(t0b_ctx* ctx, uint64_t dptr) {
     void* p = reinterpret_cast<void*>(dptr);
     auto it = ctx->live.find(p);
     if (it == ctx->live.end()) return set_error(ctx, T0B_ERR_INVALID, "t0b_free: unknown buffer %p", p);
-    ctx->live.erase(it);
+    drop_bf16_of(ctx, dptr);
+    ctx->live.erase(p);
     // Tensor maps that point into this buffer must not outlive it.
     ctx->tmaps.clear();
     cudaSetDevice(ctx->device);
@@ -237,6 +280,10 @@ int32_t t0b_memcpy_h2d(t0b_ctx* ctx, uint64_t dst, const void* src, size_t bytes
     if (rc != T0B_OK) return rc;
     if (bytes == 0) return T0B_OK;
     if (!dst || !src) return set_error(ctx, T0B_ERR_INVALID, "t0b_memcpy_h2d: null pointer");
+    {
+        std::lock_guard<std::recursive_mutex> lk(ctx->mu);
+        drop_bf16_of(ctx, dst);   // new contents: a cached bf16 copy of this buffer is stale
+    }
     rc = check_cuda(ctx, cudaMemcpyAsync(reinterpret_cast<void*>(dst), src, bytes, cudaMemcpyHostToDevice, ctx->stream),
                     "cudaMemcpyAsync(h2d)");
     if (rc != T0B_OK) return rc;
@@ -267,6 +314,62 @@ int32_t t0b_memcpy2d_d2h(t0b_ctx* ctx, void* dst, size_t dst_pitch, uint64_t src
     return check_cuda(ctx, cudaStreamSynchronize(ctx->stream), "cudaStreamSynchronize(d2h 2d)");
 }
 
+namespace {
+// The copy streams of the asynchronous host copies and of the host-buffer GEMM, created on first use.
+int32_t ensure_copy_streams(t0b_ctx* ctx) {
+    if (ctx->h2d_stream) return T0B_OK;
+    int32_t rc = check_cuda(ctx, cudaStreamCreateWithFlags(&ctx->h2d_stream, cudaStreamNonBlocking), "cudaStreamCreate(h2d)");
+    if (rc == T0B_OK) rc = check_cuda(ctx, cudaStreamCreateWithFlags(&ctx->d2h_stream, cudaStreamNonBlocking), "cudaStreamCreate(d2h)");
+    return rc;
+}
+// Make stream `later` wait for everything queued so far on stream `earlier`.
+cudaError_t order_behind(cudaStream_t later, cudaStream_t earlier) {
+    cudaEvent_t ev = nullptr;
+    cudaError_t e = cudaEventCreateWithFlags(&ev, cudaEventDisableTiming);
+    if (e == cudaSuccess) e = cudaEventRecord(ev, earlier);
+    if (e == cudaSuccess) e = cudaStreamWaitEvent(later, ev, 0);
+    if (ev) cudaEventDestroy(ev);
+    return e;
+}
+}  // namespace
+
+int32_t t0b_memcpy_h2d_async(t0b_ctx* ctx, uint64_t dst, const void* src, size_t bytes) {
+    int32_t rc = precheck(ctx);
+    if (rc != T0B_OK) return rc;
+    if (bytes == 0) return T0B_OK;
+    if (!dst || !src) return set_error(ctx, T0B_ERR_INVALID, "t0b_memcpy_h2d_async: null pointer");
+    if (ctx->capturing) return set_error(ctx, T0B_ERR_INVALID, "t0b_memcpy_h2d_async: not available during graph capture");
+    std::lock_guard<std::recursive_mutex> lk(ctx->mu);
+    drop_bf16_of(ctx, dst);
+    rc = ensure_copy_streams(ctx);
+    if (rc != T0B_OK) return rc;
+    // The copy waits for the kernels queued so far (they may still read the destination) and later launches wait for it.
+    cudaError_t e = order_behind(ctx->h2d_stream, ctx->stream);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(reinterpret_cast<void*>(dst), src, bytes, cudaMemcpyHostToDevice, ctx->h2d_stream);
+    if (e == cudaSuccess) e = order_behind(ctx->stream, ctx->h2d_stream);
+    return check_cuda(ctx, e, "t0b_memcpy_h2d_async");
+}
+
+int32_t t0b_memcpy2d_d2h_async(t0b_ctx* ctx, void* dst, size_t dst_pitch, uint64_t src, size_t src_pitch, size_t width_bytes,
+                               size_t height) {
+    int32_t rc = precheck(ctx);
+    if (rc != T0B_OK) return rc;
+    if (width_bytes == 0 || height == 0) return T0B_OK;
+    if (!dst || !src || dst_pitch < width_bytes || src_pitch < width_bytes)
+        return set_error(ctx, T0B_ERR_INVALID, "t0b_memcpy2d_d2h_async: null pointer or pitch smaller than the row");
+    if (ctx->capturing) return set_error(ctx, T0B_ERR_INVALID, "t0b_memcpy2d_d2h_async: not available during graph capture");
+    std::lock_guard<std::recursive_mutex> lk(ctx->mu);
+    rc = ensure_copy_streams(ctx);
+    if (rc != T0B_OK) return rc;
+    // Behind the work queued so far; launches made after this call do not wait for the copy.
+    cudaError_t e = order_behind(ctx->d2h_stream, ctx->stream);
+    if (e == cudaSuccess)
+        e = cudaMemcpy2DAsync(dst, dst_pitch, reinterpret_cast<void*>(src), src_pitch, width_bytes, height, cudaMemcpyDeviceToHost,
+                              ctx->d2h_stream);
+    ctx->d2h_pending = true;
+    return check_cuda(ctx, e, "t0b_memcpy2d_d2h_async");
+}
+
 int32_t t0b_memset0(t0b_ctx* ctx, uint64_t dst, size_t bytes) {
     int32_t rc = precheck(ctx);
     if (rc != T0B_OK) return rc;
@@ -280,12 +383,75 @@ int32_t t0b_sync(t0b_ctx* ctx) {
     if (rc != T0B_OK) return rc;
     rc = check_cuda(ctx, cudaStreamSynchronize(ctx->stream), "cudaStreamSynchronize");
     if (rc != T0B_OK) return rc;
-    const int st = *reinterpret_cast<volatile int*>(ctx->status_host);
+    if (ctx->d2h_pending) {   // asynchronous read-backs (t0b_memcpy2d_d2h_async) complete here too
+        ctx->d2h_pending = false;
+        rc = check_cuda(ctx, cudaStreamSynchronize(ctx->d2h_stream), "cudaStreamSynchronize(d2h)");
+        if (rc != T0B_OK) return rc;
+    }
+    const int st = take_device_status(ctx);
     if (st != 0) return set_error(ctx, T0B_ERR_DEVICE, "device status %d (101-105: a bounded in-kernel wait ran out; 110: an index outside its table)", st);
     return T0B_OK;
 }
 
 uint64_t t0b_launch_count(t0b_ctx* ctx) { return ctx ? ctx->launches : 0; }
+
+// ------------------------------------------------------------------------------------------------ bf16 weight cache
+
+int32_t t0b_get_or_create_bf16(t0b_ctx* ctx, uint64_t tensor_id, uint64_t f32_ptr, size_t n_elems, uint64_t* bf16_ptr) {
+    int32_t rc = precheck(ctx);
+    if (rc != T0B_OK) return rc;
+    if (!bf16_ptr || !f32_ptr || n_elems == 0) return set_error(ctx, T0B_ERR_INVALID, "get_or_create_bf16: null pointer or no elements");
+    std::lock_guard<std::recursive_mutex> lk(ctx->mu);
+    auto it = ctx->bf16_cache.find(tensor_id);
+    if (it != ctx->bf16_cache.end() && it->second.n == n_elems) {
+        ++ctx->bf16_hits;
+        *bf16_ptr = it->second.ptr;
+        return T0B_OK;
+    }
+    if (it != ctx->bf16_cache.end()) {   // same id, another size: the old copy is stale
+        t0b_recycle(ctx, it->second.ptr);
+        ctx->bf16_cache.erase(it);
+    }
+    uint64_t out = 0;
+    rc = t0b_alloc(ctx, ((n_elems * 2) + 255) & ~static_cast<size_t>(255), &out);
+    if (rc != T0B_OK) return rc;
+    rc = t0b_cast_f32_to_bf16(ctx, f32_ptr, out, n_elems, 1);   // stream-ordered before the GEMM that will read it
+    if (rc != T0B_OK) {
+        t0b_recycle(ctx, out);
+        return rc;
+    }
+    ++ctx->bf16_conversions;
+    ctx->bf16_cache[tensor_id] = t0b_ctx::Bf16Entry{out, n_elems};
+    *bf16_ptr = out;
+    return T0B_OK;
+}
+
+int32_t t0b_invalidate_bf16(t0b_ctx* ctx, uint64_t tensor_id) {
+    if (!ctx) return T0B_ERR_INVALID;
+    std::lock_guard<std::recursive_mutex> lk(ctx->mu);
+    auto it = ctx->bf16_cache.find(tensor_id);
+    if (it == ctx->bf16_cache.end()) return T0B_OK;
+    t0b_recycle(ctx, it->second.ptr);   // reuse is stream-ordered behind the GEMMs that still read the copy
+    ctx->bf16_cache.erase(it);
+    return T0B_OK;
+}
+
+int32_t t0b_clear_bf16_cache(t0b_ctx* ctx) {
+    if (!ctx) return T0B_ERR_INVALID;
+    std::lock_guard<std::recursive_mutex> lk(ctx->mu);
+    for (auto& kv : ctx->bf16_cache) t0b_recycle(ctx, kv.second.ptr);
+    ctx->bf16_cache.clear();
+    return T0B_OK;
+}
+
+int32_t t0b_bf16_cache_stats(t0b_ctx* ctx, uint64_t* entries, uint64_t* conversions, uint64_t* hits) {
+    if (!ctx) return T0B_ERR_INVALID;
+    std::lock_guard<std::recursive_mutex> lk(ctx->mu);
+    if (entries) *entries = ctx->bf16_cache.size();
+    if (conversions) *conversions = ctx->bf16_conversions;
+    if (hits) *hits = ctx->bf16_hits;
+    return T0B_OK;
+}
 
 
 // ------------------------------------------------------------------------------------------------ IPC

@@ -140,6 +140,16 @@ def auto_select(m: int, k: int, n: int) -> GemmConfig:
     return _select(lib().t0b_auto_select, m, k, n)
 
 
+def auto_select_source(m: int, k: int, n: int, trans_a: bool = False, trans_b: bool = True, out_dtype: int = 0):
+    """The config a config-less GEMM call of this shape, layout and output type runs, and where it came from:
+    "tuned" (measured in this process), "table" (the table shipped with the library) or "model" (the cost model)."""
+    c = GemmConfigC()
+    src = lib().t0b_auto_select_source(m, k, n, int(trans_a), int(trans_b), out_dtype, C.byref(c))
+    if src < 0:
+        raise ValueError(f"auto_select_source: invalid shape ({m}, {k}, {n})")
+    return GemmConfig.from_c(c), ("model", "table", "tuned")[src]
+
+
 def auto_select_legacy(m: int, k: int, n: int) -> GemmConfig:
     return _select(lib().t0b_auto_select_legacy, m, k, n)
 

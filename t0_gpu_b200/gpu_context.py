@@ -157,6 +157,27 @@ class GpuRuntime:
         lib().t0b_pool_stats(self._ctx, C.byref(a), C.byref(b), C.byref(c))
         return {"cached_bytes": a.value, "hits": b.value, "misses": c.value}
 
+    # ------------------------------------------------------------------ bf16 weight cache (gpu_context.rs:392-432)
+    def get_or_create_bf16(self, tensor_id: int, f32_buf: GpuBuffer, n_elems: int) -> GpuBuffer:
+        """`GpuRuntime::get_or_create_bf16(tensor_id, f32_buf, n_elems, convert_kernel)`: the cached bf16 copy of an f32
+        weight buffer, converted on the device on first use (no convert-kernel argument: the library owns the kernel).
+        The returned handle is borrowed -- the cache owns the memory."""
+        p = C.c_uint64()
+        self._check(lib().t0b_get_or_create_bf16(self._ctx, tensor_id, f32_buf.gpu_addr(), n_elems, C.byref(p)))
+        return GpuBuffer(self, p.value, n_elems * 2, owned=False)
+
+    def invalidate_bf16(self, tensor_id: int) -> None:
+        """Call after a weight update (gpu_context.rs:420-424)."""
+        self._check(lib().t0b_invalidate_bf16(self._ctx, tensor_id))
+
+    def clear_bf16_cache(self) -> None:
+        self._check(lib().t0b_clear_bf16_cache(self._ctx))
+
+    def bf16_cache_stats(self) -> dict:
+        a, b, c = C.c_uint64(), C.c_uint64(), C.c_uint64()
+        lib().t0b_bf16_cache_stats(self._ctx, C.byref(a), C.byref(b), C.byref(c))
+        return {"entries": a.value, "conversions": b.value, "hits": c.value}
+
     # ------------------------------------------------------------------ sync (gpu_context.rs:297-332)
     def synchronize(self) -> None:
         self._check(lib().t0b_sync(self._ctx))
@@ -203,11 +224,19 @@ class GpuRuntime:
     def dispatch_async(self, kernel, grid, kernargs: bytes) -> None:
         self._dispatch(kernel, grid, kernargs, True)
 
-    def dispatch_bench(self, kernel, grid, kernargs: bytes) -> None:
+    def dispatch_bench(self, kernel, grid, kernargs: bytes) -> float:
         """`GpuRuntime::dispatch_bench` (gpu_context.rs:297-307): the reference's low-overhead submit + spin-wait for
-        benchmarks.  A stream launch followed by a stream synchronise has no cheaper form here, so it is `dispatch`;
-        batches are better timed with `gemm_time` or a captured graph."""
-        self._dispatch(kernel, grid, kernargs, False)
+        benchmarks.  Here: one launch bracketed by CUDA events on the stream; returns the device time in milliseconds
+        (the reference returns nothing and leaves the timing to the caller's wall clock)."""
+        import torch
+
+        stream = torch.cuda.ExternalStream(lib().t0b_ctx_stream(self._ctx) or 0)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        self._dispatch(kernel, grid, kernargs, True)
+        e1.record(stream)
+        self.synchronize()
+        return e0.elapsed_time(e1)
 
     def _dispatch(self, kernel, grid, kernargs, async_):
         blob = (C.c_uint8 * len(kernargs)).from_buffer_copy(kernargs)
@@ -290,7 +319,8 @@ class GpuKernel:
         self.cfg = cfg
 
     @staticmethod
-    def load(rt: "GpuRuntime", blob: bytes, load_cfg: Optional[KernelLoadConfig] = None) -> "GpuKernel":
+    def load(rt, blob: bytes, load_cfg: Optional[KernelLoadConfig] = None) -> "GpuKernel":
+        """`GpuKernel::load(&device, &elf, &KernelLoadConfig{..})`; `rt` is a GpuRuntime or a KfdDevice."""
         import json
         from .gemm_gen import EpilogueOp, GemmTranspose
         if not blob.startswith(b"T0B200\0"):
@@ -300,17 +330,105 @@ class GpuKernel:
         return GpuKernel(GemmConfig(**d))
 
 
+class KernargBuffer:
+    """One kernarg slot of a `DispatchPool`.  In the reference this is a 256-byte uncached GPU buffer the command
+    processor reads; a CUDA launch takes its arguments by value, so the slot is host memory with the same
+    `write` / `read` / `size` surface, and `AqlQueue.submit` reads the blob out of it at submission."""
+
+    SLOT_BYTES = 256
+
+    def __init__(self):
+        self._data = bytearray(self.SLOT_BYTES)
+        self._len = 0
+
+    def write(self, data: bytes) -> None:
+        if len(data) > self.SLOT_BYTES:
+            raise AssertionError(f"KernargBuffer.write: {len(data)} bytes into a {self.SLOT_BYTES}-byte slot")
+        self._data[:len(data)] = data
+        self._len = len(data)
+
+    def read(self) -> bytes:
+        return bytes(self._data[:self._len])
+
+    def size(self) -> int:
+        return self.SLOT_BYTES
+
+
+class DispatchPool:
+    """`kfd::DispatchPool` (src/kfd/mod.rs:2853-2930): an auto-growing ring of kernarg slots addressed by index.
+    `new(device, initial_slots)` pre-creates `initial_slots` slots (0 = 1024); any index may be used, missing slots
+    are created on access.  The completion signal of the reference has no counterpart: completion is the stream's."""
+
+    def __init__(self, device, initial_slots: int = 0):
+        self.device = device
+        n = 1024 if initial_slots == 0 else initial_slots
+        self._ring = [KernargBuffer() for _ in range(n)]
+
+    @staticmethod
+    def new(device, initial_slots: int = 0) -> "DispatchPool":
+        return DispatchPool(device, initial_slots)
+
+    def _ensure_slot(self, idx: int) -> None:
+        if idx < 0:
+            raise IndexError("DispatchPool: negative slot index")
+        while idx >= len(self._ring):
+            self._ring.append(KernargBuffer())
+
+    def get_kernargs(self, idx: int) -> KernargBuffer:
+        self._ensure_slot(idx)
+        return self._ring[idx]
+
+    def write_kernargs(self, idx: int, data: bytes) -> KernargBuffer:
+        """Write the blob into slot `idx` (created on demand) and return the slot (mod.rs:2901-2910)."""
+        buf = self.get_kernargs(idx)
+        buf.write(data)
+        return buf
+
+    def dispatch(self, queue: "AqlQueue", kernel, grid, ka_idx: int) -> None:
+        """Submit with the blob of slot `ka_idx` and wait for completion (mod.rs:2912-2925)."""
+        queue.submit(kernel, grid, self.get_kernargs(ka_idx))
+        queue.wait_idle()
+
+    def len(self) -> int:
+        return len(self._ring)
+
+    __len__ = len
+
+    def capacity(self) -> int:
+        return len(self._ring)
+
+
 class AqlQueue:
-    """`queue.submit` + `queue.wait_idle` over the runtime's stream."""
+    """`queue.submit` + `queue.wait_idle` over the runtime's stream.  `kernargs` is a blob or a `DispatchPool` slot."""
 
     def __init__(self, rt: "GpuRuntime"):
         self.rt = rt
 
-    def submit(self, kernel: GpuKernel, grid, kernargs: bytes) -> None:
-        self.rt.dispatch_async(kernel.cfg, (grid[0], grid[1]), kernargs)
+    def submit(self, kernel: GpuKernel, grid, kernargs) -> None:
+        blob = kernargs.read() if isinstance(kernargs, KernargBuffer) else kernargs
+        self.rt.dispatch_async(kernel.cfg, (grid[0], grid[1]), blob)
 
     def wait_idle(self) -> None:
         self.rt.synchronize()
+
+
+class KfdDevice:
+    """The device handle the reference's examples open first (`KfdDevice::open()`, src/kfd/mod.rs): here a thin view
+    of a `GpuRuntime` with the three calls those examples make -- `create_queue`, `alloc_vram`, and being passed to
+    `GpuKernel::load` / `DispatchPool::new`."""
+
+    def __init__(self, rt: "GpuRuntime"):
+        self.rt = rt
+
+    @staticmethod
+    def open(device: int = 0, rt: Optional["GpuRuntime"] = None) -> "KfdDevice":
+        return KfdDevice(rt if rt is not None else GpuRuntime(device))
+
+    def create_queue(self) -> AqlQueue:
+        return AqlQueue(self.rt)
+
+    def alloc_vram(self, size: int) -> GpuBuffer:
+        return self.rt.alloc(size)
 
 
 def _addr(b) -> int:

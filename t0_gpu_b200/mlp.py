@@ -93,12 +93,14 @@ class MlpTrainer:
     """One data-parallel replica.  `rows` is this rank's share of the batch, `rows_total` the global batch."""
 
     def __init__(self, rt: GpuRuntime, cfg: MlpConfig, rows: int, rows_total: Optional[int] = None, group=None,
-                 seed: int = 100, shard_optimizer: bool = False, autotune: bool = True):
+                 seed: int = 100, shard_optimizer: bool = False, autotune: bool = True, local_only: bool = False):
+        """local_only: a single-rank replica even while a process group is up (no gradient exchange) -- the one-rank
+        side of a data-parallel equivalence check."""
         import torch
         import torch.distributed as dist
 
         self.torch, self.rt, self.cfg, self.rows, self.group = torch, rt, cfg, rows, group
-        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.world = dist.get_world_size(group) if (dist.is_initialized() and not local_only) else 1
         self.rows_total = rows_total if rows_total is not None else rows * self.world
         self.dev = torch.device("cuda", torch.cuda.current_device())
         self.L = lib()
@@ -188,8 +190,11 @@ class MlpTrainer:
         shapes.add((B, V, k, False, False))
         shapes.add((k // len(self._layer_units[-1]), V, B, True, False))
         shapes.add((B, k, V, False, True))
-        for (m, n, kk, ta, tb) in sorted(shapes):
+        done = self.rt.__dict__.setdefault("_mlp_tuned_shapes", set())   # a second trainer on this runtime measures nothing twice
+        for shape in sorted(shapes - done):
+            m, n, kk, ta, tb = shape
             self.rt.tune(m, n, kk, trans_a=ta, trans_b=tb)
+            done.add(shape)
 
     # ------------------------------------------------------------------ helpers (each one C-ABI call)
     def _ck(self, rc):

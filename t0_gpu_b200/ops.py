@@ -16,30 +16,46 @@ RMSNORM_EPS = 1e-5   # the constant Ignis hard-codes (src/ignis/ops/rmsnorm.rs:1
 
 
 def _bf16_of(rt: GpuRuntime, buf: GpuBuffer, n: int) -> GpuBuffer:
+    """A temporary bf16 copy of an activation (cast on the device, stream-ordered)."""
     out = rt.alloc(max(n * 2, 16))
     rt._check(lib().t0b_cast_f32_to_bf16(rt.handle, buf.gpu_addr(), out.gpu_addr(), n, 1))
     return out
 
 
-def dispatch_gemm_forward(rt: GpuRuntime, x: GpuBuffer, w: GpuBuffer, m: int, k: int, n: int) -> GpuBuffer:
+def _weight_bf16(rt: GpuRuntime, w: GpuBuffer, n: int, weight_id: Optional[int]) -> GpuBuffer:
+    """The cached bf16 copy of a weight (gpu_context.rs:392-432), keyed by `weight_id` or, without one, by the f32
+    buffer's device address.  It is converted once and reused by every forward and backward call until
+    `weight_updated` / `adamw_step` invalidates it."""
+    return rt.get_or_create_bf16(weight_id if weight_id is not None else w.gpu_addr(), w, n)
+
+
+def weight_updated(rt: GpuRuntime, w: GpuBuffer, weight_id: Optional[int] = None) -> None:
+    """Tell the runtime that `w` changed (an optimizer step wrote it): its cached bf16 copy is dropped."""
+    rt.invalidate_bf16(weight_id if weight_id is not None else w.gpu_addr())
+
+
+# Every function below only queues work on the runtime's stream and returns (the reference waits for the queue to go
+# idle after every op, src/ignis/ops/bf16_matmul.rs:162-207).  Results are complete once the caller reads them
+# (`GpuBuffer.read` is ordered on the same stream) or calls `rt.synchronize()`.  Temporary buffers go back to the pool
+# as soon as the launches that use them are queued: the pool hands them out again only to later work of the stream.
+
+def dispatch_gemm_forward(rt: GpuRuntime, x: GpuBuffer, w: GpuBuffer, m: int, k: int, n: int,
+                          weight_id: Optional[int] = None) -> GpuBuffer:
     """Y[M,N] f32 = X[M,K] f32 * W[K,N] f32 via bf16 (bf16_matmul.rs:162-207)."""
-    x16, w16 = _bf16_of(rt, x, m * k), _bf16_of(rt, w, k * n)
+    x16, w16 = _bf16_of(rt, x, m * k), _weight_bf16(rt, w, k * n, weight_id)
     y = rt.alloc(max(m * n * 4, 16))
     rt.gemm(x16, w16, y, m, n, k, trans_a=False, trans_b=False, async_=True)
-    rt.synchronize()
     rt.recycle(x16)
-    rt.recycle(w16)
     return y
 
 
-def gemm_backward_data(rt: GpuRuntime, dy: GpuBuffer, w: GpuBuffer, m: int, k: int, n: int) -> GpuBuffer:
+def gemm_backward_data(rt: GpuRuntime, dy: GpuBuffer, w: GpuBuffer, m: int, k: int, n: int,
+                       weight_id: Optional[int] = None) -> GpuBuffer:
     """dX[M,K] = dY[M,N] * W[K,N]^T (bf16_matmul.rs:215-258): W is read as the [N_gemm, K_gemm] operand."""
-    dy16, w16 = _bf16_of(rt, dy, m * n), _bf16_of(rt, w, k * n)
+    dy16, w16 = _bf16_of(rt, dy, m * n), _weight_bf16(rt, w, k * n, weight_id)
     dx = rt.alloc(max(m * k * 4, 16))
     rt.gemm(dy16, w16, dx, m, k, n, trans_a=False, trans_b=True, async_=True)
-    rt.synchronize()
     rt.recycle(dy16)
-    rt.recycle(w16)
     return dx
 
 
@@ -48,19 +64,18 @@ def gemm_backward_weight(rt: GpuRuntime, x: GpuBuffer, dy: GpuBuffer, m: int, k:
     x16, dy16 = _bf16_of(rt, x, m * k), _bf16_of(rt, dy, m * n)
     dw = rt.alloc(max(k * n * 4, 16))
     rt.gemm(x16, dy16, dw, k, n, m, trans_a=True, trans_b=False, async_=True)
-    rt.synchronize()
     rt.recycle(x16)
     rt.recycle(dy16)
     return dw
 
 
-def matmul(rt: GpuRuntime, x: GpuBuffer, w: GpuBuffer, m: int, k: int, n: int):
+def matmul(rt: GpuRuntime, x: GpuBuffer, w: GpuBuffer, m: int, k: int, n: int, weight_id: Optional[int] = None):
     """`ops::bf16_matmul::matmul` (bf16_matmul.rs:33-98): returns (y, backward) where backward(dy) gives (dx, dw),
-    the closure the reference records on its tape."""
-    y = dispatch_gemm_forward(rt, x, w, m, k, n)
+    the closure the reference records on its tape.  The bf16 copy of W is taken from the runtime's cache."""
+    y = dispatch_gemm_forward(rt, x, w, m, k, n, weight_id)
 
     def backward(dy: GpuBuffer, x_needs: bool = True, w_needs: bool = True):
-        dx = gemm_backward_data(rt, dy, w, m, k, n) if x_needs else None
+        dx = gemm_backward_data(rt, dy, w, m, k, n, weight_id) if x_needs else None
         dw = gemm_backward_weight(rt, x, dy, m, k, n) if w_needs else None
         return dx, dw
 
@@ -74,9 +89,18 @@ def matmul_with_wt_bf16(rt: GpuRuntime, x: GpuBuffer, wt_bf16: GpuBuffer, m: int
     x16 = _bf16_of(rt, x, m * k)
     y = rt.alloc(max(m * n * 4, 16))
     rt.gemm(x16, wt_bf16, y, m, n, k, trans_a=False, trans_b=True, async_=True)
-    rt.synchronize()
     rt.recycle(x16)
     return y
+
+
+def adamw_step(rt: GpuRuntime, param: GpuBuffer, grad: GpuBuffer, m_state: GpuBuffer, v_state: GpuBuffer, n: int, t: int,
+               lr: float = 1e-3, beta1: float = 0.9, beta2: float = 0.999, eps: float = 1e-8, weight_decay: float = 0.01,
+               weight_id: Optional[int] = None) -> None:
+    """One fused AdamW update of an f32 parameter buffer (src/t0/adamw_kernels.rs:35-119), after which the parameter's
+    cached bf16 copy is invalidated, as the reference does after each optimizer step."""
+    rt._check(lib().t0b_adamw_step(rt.handle, param.gpu_addr(), grad.gpu_addr(), m_state.gpu_addr(), v_state.gpu_addr(), 0, n,
+                                   lr, beta1, beta2, eps, weight_decay, t, 1.0, 1))
+    weight_updated(rt, param, weight_id)
 
 
 def rmsnorm(rt: GpuRuntime, x: GpuBuffer, gamma: GpuBuffer, rows: int, dim: int, eps: float = RMSNORM_EPS):

@@ -399,7 +399,8 @@ def test_bad_arguments_are_rejected_before_launch(rt):
         rt.dispatch(cfg, (65, 1), b"\0" * 40)                      # grid not a multiple of wg_size
     ws = rt.alloc(64)
     with pytest.raises(t.T0Error):
-        rt.gemm(a, b, c, 32, 32, 1024, cfg=cfg.with_(split_k=4), workspace=ws)   # undersized workspace
+        # undersized workspace (a CTA-pair tile: its split-K goes through slabs; single-CTA tiles need none)
+        rt.gemm(a, b, c, 32, 32, 1024, cfg=GemmConfig.preset("b200_256x256").with_(split_k=4), workspace=ws)
     assert not rt.is_poisoned()                                    # validation errors do not poison
     rt.gemm(a, b, c, 16, 16, 16)                                   # and the runtime still works
 

@@ -27,6 +27,35 @@ def test_library_exports_every_declared_symbol():
     assert declared == set(_lib.SIGNATURES), declared ^ set(_lib.SIGNATURES)
 
 
+def test_sys_binding_matches_the_header():
+    """The Rust `-sys` file a maintainer of the reference crate adds is generated from the header: the committed copy
+    (include/t0b200_sys.rs) and the copy shown in INTEGRATION.md are both up to date, and every exported function is
+    declared in it with as many parameters as the C prototype has."""
+    import importlib.util
+
+    spec = importlib.util.spec_from_file_location("make_sys_rs", os.path.join(ROOT, "include", "make_sys_rs.py"))
+    gen = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(gen)
+    text = gen.generate()
+    with open(os.path.join(ROOT, "include", "t0b200_sys.rs")) as f:
+        assert f.read() == text, "include/t0b200_sys.rs is stale: run python include/make_sys_rs.py"
+    with open(os.path.join(ROOT, "INTEGRATION.md")) as f:
+        doc = f.read()
+    shown = doc.split("<!-- BEGIN t0b200_sys.rs -->\n```rust\n")[1].split("```\n<!-- END t0b200_sys.rs -->")[0]
+    assert shown == text, "the binding shown in INTEGRATION.md is stale"
+    with open(os.path.join(ROOT, "include", "t0b200.h")) as f:
+        header = re.sub(r"/\*.*?\*/", " ", f.read(), flags=re.S)
+    protos = re.findall(r"T0B_API\s+[\w\s\*]+?\b(t0b_\w+)\s*\((.*?)\)\s*;", header, flags=re.S)
+    assert len(protos) >= 100
+    for name, args in protos:
+        m = re.search(r"pub fn %s\((.*?)\)( -> [^;]+)?;" % name, text)
+        assert m, f"{name} is missing from the -sys binding"
+        n_c = 0 if args.strip() in ("", "void") else len(args.split(","))
+        n_rs = 0 if not m.group(1).strip() else len(m.group(1).split(", "))
+        assert n_c == n_rs, (name, n_c, n_rs)
+    assert "is_async: i32" in text and " async:" not in text          # `async` is a Rust keyword
+
+
 def test_no_gpu_means_loud_failure():
     import torch
     if torch.cuda.is_available():
@@ -47,6 +76,41 @@ def test_auto_select_sizes():
     assert 128 % c.tile_m == 0
     with pytest.raises(ValueError):
         t.auto_select(0, 16, 16)
+
+
+def _shipped_rows():
+    rows = []
+    with open(os.path.join(ROOT, "t0_gpu_b200", "csrc", "t0b_tuned_table.inc")) as f:
+        for line in f:
+            m = re.match(r'\{(\d+), (\d+), (\d+), (\d), (\d), (\d), "(\w+)", (\d+), (\d), ([\d.]+)f\},', line.strip())
+            if m and int(m.group(1)) > 0:
+                rows.append((int(m.group(1)), int(m.group(2)), int(m.group(3)), int(m.group(4)), int(m.group(5)), int(m.group(6)),
+                             m.group(7), int(m.group(8)), int(m.group(9))))
+    return rows
+
+
+def test_auto_select_answers_from_the_shipped_table_then_the_cost_model():
+    """auto_select = predict_best over the tune cache in the reference (src/t0/cost_model.rs:593-601, 788-1078): here a
+    table measured on B200 ships inside the library, and shapes it does not hold fall through to the cost model."""
+    rows = _shipped_rows()
+    for (m, n, k, ta, tb, ob, preset, sk, swap) in rows:
+        cfg, src = t.auto_select_source(m, k, n, bool(ta), bool(tb), ob)
+        want = t.GemmConfig.preset(preset)
+        assert src == "table", (m, n, k, src)
+        assert (cfg.tile_m, cfg.tile_n, cfg.split_k or 0, int(cfg.swap_grid)) == (want.tile_m, want.tile_n, sk if sk > 1 else 0, swap)
+    # the layout-less front door prefers the NT / f32 row of a shape
+    by_shape = {}
+    for r in rows:
+        by_shape.setdefault(r[:3], []).append(r)
+    for (m, n, k), rs in by_shape.items():
+        pick = sorted(rs, key=lambda r: [(0, 1, 0), (0, 0, 0), (1, 0, 0), (1, 1, 0), (0, 1, 1), (0, 0, 1), (1, 0, 1), (1, 1, 1)].index(r[3:6]))[0]
+        got = t.auto_select(m, k, n)
+        assert (got.tile_m, got.tile_n) == (t.GemmConfig.preset(pick[6]).tile_m, t.GemmConfig.preset(pick[6]).tile_n)
+    # a shape nobody measured: the cost model answers
+    cfg, src = t.auto_select_source(1000, 3000, 777)
+    assert src == "model" and cfg.tile_m >= 128
+    with pytest.raises(ValueError):
+        t.auto_select_source(0, 1, 1)
 
 
 def test_auto_select_legacy_preserved():

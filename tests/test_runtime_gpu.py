@@ -77,13 +77,30 @@ def test_tuner_returns_a_valid_config(rt):
     assert np.abs(c.read_as(np.float32, 1024 * 1024).reshape(1024, 1024)[5] - ref).max() < 2 ** -7 * 32
 
 
+def test_auto_select_prefers_what_this_process_tuned(rt, tmp_path):
+    """auto_select's first source is a measurement of this process (GemmTuner's memory cache in the reference,
+    src/t0/auto_gemm.rs:91-96); invalidating the shape hands the answer back to the shipped table / cost model."""
+    m, n, k = 384, 640, 512            # not a benchmark shape: not in the shipped table
+    _, before = t.auto_select_source(m, k, n)
+    assert before == "model"
+    best, tflops = rt.tune(m, n, k)
+    cfg, src = t.auto_select_source(m, k, n)
+    assert src == "tuned" and cfg.name() == best.name() and tflops > 0
+    assert t.auto_select(m, k, n).name() == best.name()
+    lib().t0b_tune_cache_invalidate(str(tmp_path).encode(), m, n, k)
+    assert t.auto_select_source(m, k, n)[1] == "model"
+
+
 def test_launch_counter_counts_kernels(rt):
     a = rt.alloc(64 * 256 * 2); c = rt.alloc(64 * 64 * 4)
     n0 = rt.launch_count()
     rt.gemm(a, a, c, 64, 64, 64, cfg=t.GemmConfig.preset("b200_128x64"))
     assert rt.launch_count() == n0 + 1
     rt.gemm(a, a, c, 64, 64, 256, cfg=t.GemmConfig.preset("b200_128x64").with_(split_k=2))
-    assert rt.launch_count() == n0 + 3      # GEMM + reduce
+    assert rt.launch_count() == n0 + 2      # split-K on a single-CTA tile: ONE launch (the cluster sums the partials)
+    b = rt.alloc(512 * 256 * 2); c2 = rt.alloc(512 * 512 * 4)
+    rt.gemm(b, b, c2, 512, 512, 256, cfg=t.GemmConfig.preset("b200_256x256").with_(split_k=2))
+    assert rt.launch_count() == n0 + 4      # split-K on a CTA-pair tile: GEMM into slabs + reduce kernel
 
 
 def test_gemm_rejects_operands_larger_than_their_buffers(rt):

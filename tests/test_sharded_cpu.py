@@ -27,6 +27,24 @@ def test_column_shards_tile_the_columns():
         column_shard(128, 2, 2)
 
 
+def test_multi_destination_gemm_uses_the_double_buffered_tile():
+    """With peers the epilogue issues NVLink stores, so the sharded benchmark shape must not run on a tile whose
+    epilogue is exposed (256x512 / 512x256 keep both TMEM accumulators for one tile)."""
+    from t0_gpu_b200.sharded import multi_dst_config
+
+    m, k = 32768, 8192
+    for world in (2, 4, 8):
+        n_local = 32768 // world
+        alone = multi_dst_config(m, k, n_local, 1)
+        assert (alone.tile_m, alone.tile_n) == (256, 512) and not alone.split_k      # what auto_select gives one GPU
+        fused = multi_dst_config(m, k, n_local, world)
+        assert (fused.tile_m, fused.tile_n, fused.wg_size) == (256, 256, 192) and not fused.split_k
+    small = multi_dst_config(256, 256, 256, 2)                                    # small tiles are left alone
+    assert small.tile_m <= 256 and small.tile_n <= 256 and not small.split_k
+    with pytest.raises(ValueError):
+        multi_dst_config(m, k, 4096, 9)
+
+
 def _free_port() -> int:
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
@@ -65,6 +83,101 @@ def test_handle_exchange_between_two_gloo_ranks():
         assert firsts == [0, 1] and hlen == 64                            # every rank sees every handle, in rank order
         assert (col0, n_local) == (rank * 512, 512)
         assert order[0] == rank and sorted(order) == [0, 1]
+
+
+class _FakeBuf:
+    def __init__(self, log, addr):
+        self.log, self.addr = log, addr
+
+    def gpu_addr(self):
+        return self.addr
+
+    def release(self):
+        self.log.append("free_c")
+
+
+class _FakeRt:
+    """Stands in for GpuRuntime: records the order of the calls the sharded GEMM makes."""
+
+    def __init__(self, log, rank):
+        self.log, self.rank, self.handle = log, rank, None
+
+    def alloc(self, size):
+        self.log.append("alloc_c")
+        return _FakeBuf(self.log, 0x1000 * (self.rank + 1))
+
+    def synchronize(self):
+        self.log.append("sync")
+
+
+class _FakeIpc:
+    def __init__(self, log, rank):
+        self.log, self.rank = log, rank
+
+    def export(self, ptr):
+        self.log.append("export")
+        return bytes([self.rank]) * 64
+
+    def open(self, handle):
+        self.log.append(f"open{handle[0]}")
+        return 0x100000 * (handle[0] + 1)
+
+    def close(self, ptr):
+        self.log.append(f"close{ptr // 0x100000 - 1}")
+
+
+def _order_worker(rank: int, world: int, port: int, q):
+    import torch.distributed as dist
+
+    import t0_gpu_b200.sharded as sh
+
+    dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world)
+    try:
+        log = []
+        real_barrier = dist.barrier
+
+        def logged_barrier(*a, **k):
+            log.append("barrier")
+            return real_barrier(*a, **k)
+
+        dist.barrier = logged_barrier
+        op = sh.ColumnShardedGemm(_FakeRt(log, rank), 256, 1024, 64, ipc=_FakeIpc(log, rank))
+        ptrs = list(op._peer_ptrs)
+        op.finish()
+        op.close()
+        op.close()                      # idempotent
+        closed_run = False
+        try:
+            op.run(None, None)
+        except RuntimeError:
+            closed_run = True
+        q.put((rank, log, ptrs, closed_run))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_sharded_gemm_orders_peer_stores_before_unmapping_and_freeing():
+    """finish() = wait for the local kernel, then a barrier; close() = the same, then the unmaps, then another barrier,
+    and only then this rank's C goes away -- no peer can still be storing into it."""
+    import torch.multiprocessing as mp
+
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_order_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = sorted(q.get(timeout=120) for _ in range(2))
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    for rank, log, ptrs, closed_run in results:
+        other = 1 - rank
+        assert log == ["alloc_c", "export", f"open{other}",            # construction: map the peer's C
+                       "sync", "barrier",                               # finish()
+                       "sync", "barrier", f"close{other}", "barrier", "free_c"]   # close()
+        assert ptrs == [0x1000 * (rank + 1), 0x100000 * (other + 1)]    # own buffer first, then the peer's mapping
+        assert closed_run
 
 
 def test_peer_order_spreads_the_writes():
