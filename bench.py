@@ -219,90 +219,110 @@ def time_steps(torch, fn, steps, stream):
     return e0.elapsed_time(e1) / steps
 
 
-def context_measurements(torch, rt, L, stream, dev):
-    """The memory-bound kernels (achieved HBM GB/s on working sets larger than L2) and the MLP training step of the
-    fifth benchmark config at its per-GPU size (1024 rows), next to the headline GEMM number."""
-    from t0_gpu_b200.mlp import MlpConfig, MlpTrainer
-
+def row_kernel_measurements(torch, rt, L, stream, dev, norm_sizes=((8192, 4096),), ce_sizes=((1024, 32000),), embedding=True):
+    """The memory-bound kernels: achieved HBM GB/s over their algorithmic bytes.  Every operand is rotated through four
+    buffer sets (more than 0.5 GiB per kernel) so that nothing is served from the 126 MB L2; each figure is the median
+    of five timings of 20 back-to-back launches after three warm-ups, CUDA events on the launching stream."""
     out = {}
-    hbm_peak, _ = measured_hbm()
+    hbm_peak, hbm_kind = measured_hbm()
 
     def gbs(fn, nbytes, steps=20):
         for _ in range(3):
             fn()
-        ms = time_steps(torch, fn, steps, stream)
+        ms = statistics.median(time_steps(torch, fn, steps, stream) for _ in range(5))
         g = nbytes / ms / 1e6
-        return {"ms": ms, "gbs": g, "frac_of_measured_hbm": (g / hbm_peak) if hbm_peak else None}
+        return {"ms": ms, "gbs": g, "frac_of_measured_hbm": g / hbm_peak, "hbm_peak_kind": hbm_kind, "algorithmic_bytes": nbytes}
 
-    rows, cols = 8192, 4096
-    nbuf = 4                                   # 4 x (128 MiB in + 128 MiB out): rotating so nothing is served from L2
-    xs = [torch.randn(rows, cols, device=dev) for _ in range(nbuf)]
-    ys = [torch.empty(rows, cols, device=dev) for _ in range(nbuf)]
-    w = torch.ones(cols, device=dev)
+    nbuf = 4
     i = [0]
 
-    def rms():
+    def nxt():
         j = i[0] % nbuf
         i[0] += 1
-        rt._check(L.t0b_rmsnorm_fwd(rt.handle, xs[j].data_ptr(), w.data_ptr(), ys[j].data_ptr(), 0, rows, cols, 1e-6, 1))
+        return j
 
-    out["rmsnorm_fwd_8192x4096"] = gbs(rms, 2 * rows * cols * 4)
-    dy = torch.randn(rows, cols, device=dev)
+    for rows, cols in norm_sizes:
+        tag = f"{rows}x{cols}"
+        xs = [torch.randn(rows, cols, device=dev) for _ in range(nbuf)]
+        ys = [torch.empty(rows, cols, device=dev) for _ in range(nbuf)]
+        dys = [torch.randn(rows, cols, device=dev) for _ in range(nbuf)]
+        h16 = [torch.empty(rows, cols, device=dev, dtype=torch.bfloat16) for _ in range(nbuf)]
+        w = torch.ones(cols, device=dev)
+        dg = torch.empty(cols, device=dev)
+        sb = L.t0b_rmsnorm_bwd_scratch_bytes(rows, cols)
+        scratch = torch.empty(sb, dtype=torch.uint8, device=dev)
 
-    def rms_bwd():
-        j = i[0] % nbuf
-        i[0] += 1
-        rt._check(L.t0b_rmsnorm_bwd(rt.handle, dy.data_ptr(), xs[j].data_ptr(), w.data_ptr(), ys[j].data_ptr(), 0, 0, 0,
-                                    rows, cols, 1e-6, 1))
+        def rms():
+            j = nxt()
+            rt._check(L.t0b_rmsnorm_fwd(rt.handle, xs[j].data_ptr(), w.data_ptr(), ys[j].data_ptr(), 0, rows, cols, 1e-6, 1))
 
-    out["rmsnorm_bwd_dx_8192x4096"] = gbs(rms_bwd, 3 * rows * cols * 4)
-    h16 = [torch.empty(rows, cols, device=dev, dtype=torch.bfloat16) for _ in range(nbuf)]
-    dg = torch.empty(cols, device=dev)
-    sb = L.t0b_rmsnorm_bwd_scratch_bytes(rows, cols)
-    scratch = torch.empty(sb, dtype=torch.uint8, device=dev)
+        def rms_bwd_dx():
+            j = nxt()
+            rt._check(L.t0b_rmsnorm_bwd(rt.handle, dys[j].data_ptr(), xs[j].data_ptr(), w.data_ptr(), ys[j].data_ptr(), 0, 0, 0,
+                                        rows, cols, 1e-6, 1))
 
-    def fused_fwd():
-        j = i[0] % nbuf
-        i[0] += 1
-        rt._check(L.t0b_rmsnorm_silu_fwd(rt.handle, xs[j].data_ptr(), w.data_ptr(), h16[j].data_ptr(), 0, rows, cols, 1e-6, 1))
+        def rms_bwd():
+            j = nxt()
+            rt._check(L.t0b_rmsnorm_bwd(rt.handle, dys[j].data_ptr(), xs[j].data_ptr(), w.data_ptr(), ys[j].data_ptr(), dg.data_ptr(),
+                                        scratch.data_ptr(), sb, rows, cols, 1e-6, 1))
 
-    def fused_bwd():
-        j = i[0] % nbuf
-        i[0] += 1
-        rt._check(L.t0b_rmsnorm_silu_bwd(rt.handle, dy.data_ptr(), xs[j].data_ptr(), w.data_ptr(), h16[j].data_ptr(), dg.data_ptr(),
-                                         scratch.data_ptr(), sb, rows, cols, 1e-6, 1))
+        def fused_fwd():
+            j = nxt()
+            rt._check(L.t0b_rmsnorm_silu_fwd(rt.handle, xs[j].data_ptr(), w.data_ptr(), h16[j].data_ptr(), 0, rows, cols, 1e-6, 1))
 
-    # algorithmic bytes: read x (f32) + write bf16; backward reads dh and x (f32), writes bf16 dx
-    out["rmsnorm_silu_bf16_fwd_8192x4096"] = gbs(fused_fwd, rows * cols * 6)
-    out["rmsnorm_silu_bf16_bwd_8192x4096"] = gbs(fused_bwd, rows * cols * 10)
-    del xs, ys, dy, h16
-    vocab, edim, tokens = 32000, 4096, 16384
-    table = torch.randn(vocab, edim, device=dev)
-    ids = torch.randint(0, vocab, (tokens,), device=dev, dtype=torch.int32)
-    eout = torch.empty(tokens, edim, device=dev)
-    gtab = torch.zeros(vocab, edim, device=dev)
-    out["embedding_fwd_16384x4096"] = gbs(lambda: rt._check(L.t0b_embedding_fwd(
-        rt.handle, table.data_ptr(), ids.data_ptr(), eout.data_ptr(), tokens, edim, vocab, 1)), 2 * tokens * edim * 4)
-    uniq = int(torch.unique(ids).numel())
-    out["embedding_bwd_16384x4096"] = gbs(lambda: rt._check(L.t0b_embedding_bwd(
-        rt.handle, gtab.data_ptr(), ids.data_ptr(), eout.data_ptr(), tokens, edim, vocab, 0, 0, 1)),
-        (tokens + 2 * uniq) * edim * 4)
-    del table, eout, gtab
-    rows, cols = 1024, 32000
-    nbuf = 4
-    xs = [torch.randn(rows, cols, device=dev) * 3 for _ in range(nbuf)]
-    ds = [torch.empty(rows, cols, device=dev) for _ in range(nbuf)]
-    tg = torch.randint(0, cols, (rows,), device=dev, dtype=torch.int32)
-    loss = torch.empty(rows, device=dev)
+        def fused_bwd():
+            j = nxt()
+            rt._check(L.t0b_rmsnorm_silu_bwd(rt.handle, dys[j].data_ptr(), xs[j].data_ptr(), w.data_ptr(), h16[j].data_ptr(),
+                                             dg.data_ptr(), scratch.data_ptr(), sb, rows, cols, 1e-6, 1))
 
-    def ce():
-        j = i[0] % nbuf
-        i[0] += 1
-        rt._check(L.t0b_softmax_ce(rt.handle, xs[j].data_ptr(), tg.data_ptr(), loss.data_ptr(), ds[j].data_ptr(), rows, cols,
-                                   cols, 1.0 / rows, 1))
+        out[f"rmsnorm_fwd_{tag}"] = gbs(rms, 2 * rows * cols * 4)
+        out[f"rmsnorm_bwd_dx_{tag}"] = gbs(rms_bwd_dx, 3 * rows * cols * 4)
+        out[f"rmsnorm_bwd_dx_dgamma_{tag}"] = gbs(rms_bwd, 3 * rows * cols * 4)
+        # algorithmic bytes: read x (f32) + write bf16; backward reads dh and x (f32), writes bf16 dx
+        out[f"rmsnorm_silu_bf16_fwd_{tag}"] = gbs(fused_fwd, rows * cols * 6)
+        out[f"rmsnorm_silu_bf16_bwd_{tag}"] = gbs(fused_bwd, rows * cols * 10)
+        del xs, ys, dys, h16
+    if embedding:
+        vocab, edim, tokens = 32000, 4096, 16384
+        table = torch.randn(vocab, edim, device=dev)
+        ids = torch.randint(0, vocab, (tokens,), device=dev, dtype=torch.int32)
+        eout = torch.empty(tokens, edim, device=dev)
+        gtab = torch.zeros(vocab, edim, device=dev)
+        out["embedding_fwd_16384x4096"] = gbs(lambda: rt._check(L.t0b_embedding_fwd(
+            rt.handle, table.data_ptr(), ids.data_ptr(), eout.data_ptr(), tokens, edim, vocab, 1)), 2 * tokens * edim * 4)
+        uniq = int(torch.unique(ids).numel())
+        out["embedding_bwd_16384x4096"] = gbs(lambda: rt._check(L.t0b_embedding_bwd(
+            rt.handle, gtab.data_ptr(), ids.data_ptr(), eout.data_ptr(), tokens, edim, vocab, 0, 0, 1)),
+            (tokens + 2 * uniq) * edim * 4)
+        del table, eout, gtab
+    for rows, cols in ce_sizes:
+        xs = [torch.randn(rows, cols, device=dev) * 3 for _ in range(nbuf)]
+        ds = [torch.empty(rows, cols, device=dev) for _ in range(nbuf)]
+        d16 = [torch.empty(rows, cols, device=dev, dtype=torch.bfloat16) for _ in range(nbuf)]
+        tg = torch.randint(0, cols, (rows,), device=dev, dtype=torch.int32)
+        loss = torch.empty(rows, device=dev)
 
-    out["softmax_ce_1024x32000"] = gbs(ce, 2 * rows * cols * 4)
-    del xs, ds
+        def ce():
+            j = nxt()
+            rt._check(L.t0b_softmax_ce(rt.handle, xs[j].data_ptr(), tg.data_ptr(), loss.data_ptr(), ds[j].data_ptr(), rows, cols,
+                                       cols, 1.0 / rows, 1))
+
+        def ce16():
+            j = nxt()
+            rt._check(L.t0b_softmax_ce_bf16(rt.handle, xs[j].data_ptr(), tg.data_ptr(), loss.data_ptr(), d16[j].data_ptr(), rows, cols,
+                                            cols, 1.0 / rows, 1))
+
+        out[f"softmax_ce_{rows}x{cols}"] = gbs(ce, 2 * rows * cols * 4)
+        out[f"softmax_ce_bf16grad_{rows}x{cols}"] = gbs(ce16, rows * cols * 6)
+        del xs, ds, d16
+    return out
+
+
+def context_measurements(torch, rt, L, stream, dev):
+    """The MLP training step of the fifth benchmark config at its per-GPU size (1024 rows), next to the headline GEMM."""
+    from t0_gpu_b200.mlp import MlpConfig, MlpTrainer
+
+    out = {}
     cfg = MlpConfig()
     tr = MlpTrainer(rt, cfg, 1024)
     x = torch.randn((1024, cfg.d_in), device=dev)
@@ -314,6 +334,31 @@ def context_measurements(torch, rt, L, stream, dev):
     out["mlp_step_1024rows_4096x3_32000"] = {"fwd_bwd_ms": ms_fb, "step_with_adamw_ms": ms_step,
                                              "gemm_tflops_fwd_bwd": cfg.flops_per_row() * 1024 / ms_fb / 1e9}
     return out
+
+
+def run_rows(args, local_rank):
+    """--workload rows: only the memory-bound kernels, at the sizes of the table in profiles/ (one GPU)."""
+    import torch
+
+    import t0_gpu_b200 as t
+    from t0_gpu_b200._lib import lib
+
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    rt = t.GpuRuntime(local_rank)
+    stream = torch.cuda.Stream(device=dev)
+    torch.cuda.set_stream(stream)
+    rt.set_stream(stream.cuda_stream)
+    sampler = ClockSampler(physical_gpu_index(local_rank), period_s=0.02)
+    sampler.start()
+    res = row_kernel_measurements(torch, rt, lib(), stream, dev, norm_sizes=((1024, 4096), (8192, 4096), (32768, 4096)),
+                                  ce_sizes=((1024, 32000), (8192, 32000)))
+    clocks = sampler.stop()
+    hbm, kind = measured_hbm()
+    print(json.dumps({"metric": "memory-bound kernels, achieved HBM GB/s over algorithmic bytes", "unit": "GB/s", "n_gpus": 1,
+                      "peak": hbm, "peak_kind": f"of {kind} copy bandwidth", "clocks": clocks, "kernels": res,
+                      "config": {"workload": "row_kernels", "l2": "operands rotated through four buffer sets > L2"}}), flush=True)
+    rt.close()
 
 
 def skinny_splitk_measurements(torch, t, rt, L, stream, dev):
@@ -394,6 +439,10 @@ def run_single(args, local_rank):
     rt.set_stream(stream.cuda_stream)
     L = lib()
 
+    # The memory-bound kernels go first, on a GPU that has not yet been loaded: after a second of back-to-back GEMMs at
+    # the power cap the same kernels run about 13 % slower until the GPU has idled for about a second (measured).
+    rows_first = {} if args.quick else row_kernel_measurements(torch, rt, L, stream, dev)
+
     m = n = k = 8192
     a = device_normal_bf16(torch, (m, k), 1234, 1.0 / k ** 0.5, dev)
     b = device_normal_bf16(torch, (k, n), 1235, 1.0 / k ** 0.5, dev)       # [K, N] row-major
@@ -470,6 +519,7 @@ def run_single(args, local_rank):
         del a4, b4, c4
 
     also.update(skinny_splitk_measurements(torch, t, rt, L, stream, dev))
+    also.update(rows_first)
     if not args.quick:
         also["sustained_8192"] = sustained_measurement(torch, step, ms, flops, stream, physical_gpu_index(local_rank))
         also.update(context_measurements(torch, rt, L, stream, dev))
@@ -861,8 +911,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--quick", action="store_true", help="skip the 32768^2 single-GPU context measurement")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
-    ap.add_argument("--workload", default="gemm", choices=["gemm", "mlp"],
-                    help="gemm: the headline GEMM (default); mlp: the data-parallel MLP training step")
+    ap.add_argument("--workload", default="gemm", choices=["gemm", "mlp", "rows"],
+                    help="gemm: the headline GEMM (default); mlp: the data-parallel MLP training step; "
+                         "rows: the memory-bound row kernels alone (one GPU)")
     ap.add_argument("--replicated-optimizer", action="store_true",
                     help="--workload mlp on several GPUs: all-reduce + replicated AdamW instead of the sharded optimizer")
     args = ap.parse_args()
@@ -874,7 +925,10 @@ def main():
         return
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-    if args.workload == "mlp":
+    if args.workload == "rows":
+        if rank == 0:
+            run_rows(args, local_rank)
+    elif args.workload == "mlp":
         run_mlp(args, rank, local_rank, world)
     elif world > 1:
         run_multi(args, rank, local_rank, world)

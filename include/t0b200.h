@@ -265,9 +265,10 @@ T0B_API int32_t t0b_hash_blocks(t0b_ctx* ctx, uint64_t src, size_t bytes, size_t
 T0B_API int32_t t0b_copy_d2d(t0b_ctx* ctx, uint64_t dst, size_t dst_pitch, uint64_t src, size_t src_pitch,
                              size_t width_bytes, size_t rows, int32_t async);
 /* The config t0b_gemm_multi_dst uses when it is given none: the auto_select tile for (m, k, n_local), except that
- * with more than one destination a tile that keeps both TMEM accumulators for one tile (256x512, 512x256) becomes
- * 256x256, whose accumulators double-buffer, so that the peer stores of one tile retire while the next is multiplied.
- * Never split-K.  No counterpart in the reference (single GPU). */
+ * with peers a tile that keeps both TMEM accumulators for one tile (256x512, 512x256) becomes 256x256 -- whose
+ * accumulators double-buffer, so that the peer stores of one tile retire while the next is multiplied -- once the
+ * NVLink time of the stores exceeds half of the math time (four and eight GPUs on the benchmark shape; two GPUs keep
+ * 256x512).  Never split-K.  No counterpart in the reference (single GPU). */
 T0B_API int32_t t0b_multi_dst_config(uint32_t m, uint32_t k, uint32_t n_local, int32_t n_dst, int32_t num_sms,
                                      t0b_gemm_config* out);
 /* Column-sharded GEMM with the all-gather folded into the epilogue: this rank computes C[:, col0 : col0+n_local]

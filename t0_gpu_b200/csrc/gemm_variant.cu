@@ -9,4 +9,7 @@
 
 namespace t0b {
 template int32_t launch_variant<T0B_VARIANT>(t0b_ctx*, const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, const GemmParams&, int, int);
+#if T0B_V_CG == 1 && T0B_V_MT == 1 && T0B_V_ND == 0
+template int max_active_splitk_clusters<T0B_V_BN>(t0b_ctx*, int);   // lives beside the single-CTA variant it queries
+#endif
 }  // namespace t0b

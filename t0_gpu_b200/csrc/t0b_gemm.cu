@@ -208,9 +208,18 @@ int32_t run_gemm(t0b_ctx* ctx, const GemmCall& g) {
     }
 
     // Split-K inside clusters (see below) needs no slabs at all.
-    const bool cluster_sk_possible = !g.slabs_only && plan.split_k > 1 && plan.split_k <= 8 && (plan.split_k & (plan.split_k - 1)) == 0 &&
-                                     g.n_dst == 1 && plan.use_tma && plan.cta_group == 1 && plan.m_tiles == 1 && plan.n_tiles == 1 &&
-                                     ctx->cluster_splitk;
+    bool cluster_sk_possible = !g.slabs_only && plan.split_k > 1 && plan.split_k <= 8 && (plan.split_k & (plan.split_k - 1)) == 0 &&
+                               g.n_dst == 1 && plan.use_tma && plan.cta_group == 1 && plan.m_tiles == 1 && plan.n_tiles == 1 &&
+                               ctx->cluster_splitk;
+    if (cluster_sk_possible && plan.split_k > 4) {
+        // Eight-CTA clusters do not tile every GPC: when the tiles need more clusters than fit at once, the second wave
+        // costs more than the slab round trip saves.
+        const int tiles = static_cast<int>(((g.m + plan.bm - 1) / plan.bm) * ((g.n + plan.bn - 1) / plan.bn));
+        const int fit = plan.bn == 256 ? max_active_splitk_clusters<256>(ctx, plan.split_k)
+                                       : (plan.bn == 128 ? max_active_splitk_clusters<128>(ctx, plan.split_k)
+                                                         : max_active_splitk_clusters<64>(ctx, plan.split_k));
+        if (tiles > fit) cluster_sk_possible = false;
+    }
     // Where do split-K partials go?
     float* partial = nullptr;
     uint64_t slab_stride = static_cast<uint64_t>(g.m) * g.n, ld_partial = g.n;
@@ -315,6 +324,7 @@ int32_t run_gemm(t0b_ctx* ctx, const GemmCall& g) {
             int grp = static_cast<int>(std::lround(std::sqrt(clusters * (cfg.swap_grid ? plan.bn : plan.bm) /
                                                              static_cast<double>(cfg.swap_grid ? plan.bm : plan.bn))));
             p.group = std::max(1, std::min(grp, 16));
+            if (ctx->raster_group > 0) p.group = ctx->raster_group;
         }
         p.mn_lbo = 8192; p.mn_sbo = 1024; p.mn_kstep = 2048;
         p.status = ctx->status_dev;
@@ -554,14 +564,21 @@ int32_t t0b_gemm_host(t0b_ctx* ctx, const t0b_gemm_config* cfg, int32_t trans_a,
 int32_t t0b_multi_dst_config(uint32_t m, uint32_t k, uint32_t n_local, int32_t n_dst, int32_t num_sms, t0b_gemm_config* out) {
     if (!out || n_dst < 1 || n_dst > kMaxDst) return T0B_ERR_INVALID;
     default_b200_config(m, k, n_local, num_sms > 0 ? num_sms : 148, out);
-    // Stores to a peer retire at the NVLink rate, far below the rate the epilogue can issue them, so with peers the
-    // epilogue warps spend most of a tile's time blocked in stores.  The tiles that keep both TMEM accumulators for one
-    // tile (256x512, 512x256) cannot start the next main loop until that epilogue is over; the 256x256 tile
-    // double-buffers its accumulators, so the stores of tile i retire while tile i+1 is multiplied.
+    // Stores to a peer retire at the NVLink rate (about 0.7 TB/s for SM-issued stores, measured), far below the rate the
+    // epilogue can issue them, so the epilogue warps of a tile block in stores for as long as the tile's share of the link
+    // time.  The tiles that keep both TMEM accumulators for one tile (256x512, 512x256) are the fastest at the math but
+    // cannot start the next main loop until that epilogue is over; the 256x256 tile double-buffers its accumulators, so
+    // the stores of tile i retire while tile i+1 is multiplied.  It pays once the link time is a sizeable part of the
+    // math time: measured on the 32768 x (32768/G) x 8192 blocks, two GPUs (link / math = 0.25) run 12 % faster on
+    // 256x512, four and eight GPUs (0.75 and 1.8) on 256x256.
     if (n_dst > 1 && (out->tile_m >= 512 || out->tile_n >= 512)) {
-        out->tile_m = 256;
-        out->tile_n = 256;
-        out->wg_size = 192;
+        const double link_s = static_cast<double>(n_dst - 1) * m * n_local * 2.0 / 0.70e12;   // bf16 output assumed
+        const double math_s = 2.0 * m * static_cast<double>(n_local) * k / 1.45e15;
+        if (link_s > 0.5 * math_s) {
+            out->tile_m = 256;
+            out->tile_n = 256;
+            out->wg_size = 192;
+        }
     }
     out->split_k = 0;   // the fused store writes final values; there is no slab stage
     return T0B_OK;

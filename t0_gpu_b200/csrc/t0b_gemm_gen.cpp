@@ -195,7 +195,13 @@ void default_b200_config(uint32_t m, uint32_t k, uint32_t n, int num_sms, t0b_ge
             double cyc = static_cast<double>(waves) * (kbps * c.kb_cycles + c.epi_exposed) + c.epi_tail + 4500.0;
             // The hidden epilogue of a double-buffered tile still bounds a tile whose main loop is shorter than it.
             if (c.epi_exposed == 0.0 && kbps * c.kb_cycles < c.epi_tail) cyc += static_cast<double>(waves - 1) * (c.epi_tail - kbps * c.kb_cycles);
-            if (sk > 1) cyc += 3000.0 + static_cast<double>(m) * n * 4.0 * (sk + 1) / 3300.0;   // reduce kernel: launch + bytes at ~5 TB/s
+            if (sk > 1) {
+                // Single-CTA tiles with up to four K ranges (eight when all clusters fit at once: GPC sizes allow about
+                // fifteen eight-CTA clusters) sum their partials inside a thread-block cluster; the rest pay the slab
+                // round trip and a reduce kernel (launch + bytes at ~5 TB/s).
+                const bool in_cluster = c.cg == 1 && (sk <= 4 || (sk == 8 && tiles <= 15));
+                cyc += in_cluster ? 2500.0 : 3000.0 + static_cast<double>(m) * n * 4.0 * (sk + 1) / 3300.0;
+            }
             if (cyc < best) {
                 best = cyc;
                 pick = c;

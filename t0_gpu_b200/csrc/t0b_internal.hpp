@@ -18,6 +18,7 @@ struct t0b_ctx {
     int device = 0;
     int num_sms = 148;
     bool pdl = true;            // launch GEMMs with programmatic stream serialization (T0B_PDL=0 turns it off)
+    int raster_group = 0;       // > 0: rasterisation group width for every GEMM (T0B_RASTER_GROUP, for measurements); 0 = chosen per shape
     bool cluster_splitk = true; // split-K of single-CTA tiles runs as thread-block clusters (T0B_CLUSTER_SPLITK=0: slabs + reduce kernel)
     int sm_limit = 0;           // > 0: the persistent GEMM kernels occupy at most this many SMs
     cudaStream_t own_stream = nullptr;

@@ -2,6 +2,7 @@
 // Stands where the reference has GpuRuntime + BufferPool (src/ignis/gpu_context.rs:30-106, 113-483) on top of
 // the KFD queue/VRAM layer (src/kfd/mod.rs): a CUDA stream replaces the AQL queue and doorbell, cudaMalloc
 // the VRAM mmap, a mapped status word the queue-timeout detection.
+#include <algorithm>
 #include <cstdlib>
 #include <cstring>
 
@@ -106,6 +107,7 @@ int32_t t0b_ctx_create(int32_t device, t0b_ctx** out) {
         ctx->num_sms = prop.multiProcessorCount;
         if (const char* e = std::getenv("T0B_PDL")) ctx->pdl = std::atoi(e) != 0;
         if (const char* e = std::getenv("T0B_CLUSTER_SPLITK")) ctx->cluster_splitk = std::atoi(e) != 0;
+        if (const char* e = std::getenv("T0B_RASTER_GROUP")) ctx->raster_group = std::max(0, std::atoi(e));
         rc = check_cuda(ctx, cudaStreamCreateWithFlags(&ctx->own_stream, cudaStreamNonBlocking), "cudaStreamCreate");
         ctx->stream = ctx->own_stream;
     }

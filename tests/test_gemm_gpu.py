@@ -232,6 +232,24 @@ def test_empty_and_degenerate_shapes(rt):
     assert np.all(c.read_as(np.float32, 256) == 5.0)
     rt.gemm(a, b, c, 8, 8, 0)            # K = 0: zeros
     assert np.all(c.read_as(np.float32, 64) == 0.0)
+    # K = 0 with a fused store-phase op: the result is epilogue(0), not 0 -- bias, and bias + ReLU (negative entries clamp)
+    bias = np.array([1.5, -2.0, 0.25, -0.5, 3.0, 0.0, -1.0, 7.0], np.float32)
+    bb = rt.upload_f32(bias)
+    rt.gemm(a, b, c, 8, 8, 0, epilogue=int(EpilogueOp.BiasAddStoreF32), bias=bb)
+    assert np.array_equal(c.read_as(np.float32, 64).reshape(8, 8), np.tile(bias, (8, 1)))
+    rt.gemm(a, b, c, 8, 8, 0, epilogue=int(EpilogueOp.BiasAddReluStoreF32), bias=bb)
+    assert np.array_equal(c.read_as(np.float32, 64).reshape(8, 8), np.tile(np.maximum(bias, 0), (8, 1)))
+    # K = 0, bf16 output, a row pitch wider than N: only the M x N block is written (one 2-D memset)
+    wide = rt.alloc(8 * 16 * 2)
+    wide.write(np.full(8 * 16, 0x4000, np.uint16))
+    rt.gemm(a, b, wide, 8, 8, 0, ldc=16, out_dtype=OUT_BF16)
+    got = wide.read_as(np.uint16, 8 * 16).reshape(8, 16)
+    assert np.all(got[:, :8] == 0) and np.all(got[:, 8:] == 0x4000)
+    # K = 0 through the unreduced-slab contract: EVERY slab the caller expects is zeroed, not only the first
+    slabs = rt.alloc(4 * 8 * 8 * 4)
+    slabs.write(np.full(4 * 64, 9.0, np.float32))
+    rt.gemm_slabs(a, b, slabs, 8, 8, 0, 4)
+    assert np.all(slabs.read_as(np.float32, 4 * 64) == 0.0)
 
 
 # ------------------------------------------------------------------------------------------------ known answers / goldens

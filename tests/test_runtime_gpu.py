@@ -184,3 +184,92 @@ def test_sm_limit_changes_the_grid_not_the_result(rt):
         assert np.array_equal(o, outs[0])
     assert lib().t0b_set_sm_limit(rt.handle, -1) == -1 and lib().t0b_set_sm_limit(rt.handle, 100000) == -1
     rt.set_sm_limit(0)
+
+
+def test_block_checksums_and_device_copy(rt):
+    """t0b_hash_blocks: equal buffers give equal checksums, one changed byte changes exactly its block, swapped words
+    change the block too (the words are mixed with their position).  t0b_copy_d2d: dense and pitched copies."""
+    n = 3 * 4096 + 512                                  # three full 4 KiB blocks and a short one
+    rng = np.random.default_rng(3)
+    data = rng.integers(0, 256, n, dtype=np.uint8)
+    a, b = rt.upload(data), rt.upload(data)
+    nb = 4
+    ha, hb = rt.alloc(nb * 16), rt.alloc(nb * 16)
+    L = lib()
+    rt._check(L.t0b_hash_blocks(rt.handle, a.gpu_addr(), n, 4096, ha.gpu_addr(), 0))
+    rt._check(L.t0b_hash_blocks(rt.handle, b.gpu_addr(), n, 4096, hb.gpu_addr(), 0))
+    A, B = ha.read_as(np.uint64, 2 * nb), hb.read_as(np.uint64, 2 * nb)
+    assert np.array_equal(A, B) and len(set(A.tolist())) == 2 * nb
+    changed = data.copy(); changed[4096 + 100] ^= 1
+    b.write(changed)
+    rt._check(L.t0b_hash_blocks(rt.handle, b.gpu_addr(), n, 4096, hb.gpu_addr(), 0))
+    B = hb.read_as(np.uint64, 2 * nb)
+    diff = [i for i in range(nb) if not np.array_equal(A[2 * i:2 * i + 2], B[2 * i:2 * i + 2])]
+    assert diff == [1]
+    swapped = data.copy().view(np.uint64); swapped[[0, 1]] = swapped[[1, 0]]
+    b.write(swapped.view(np.uint8))
+    rt._check(L.t0b_hash_blocks(rt.handle, b.gpu_addr(), n, 4096, hb.gpu_addr(), 0))
+    assert not np.array_equal(A[:2], hb.read_as(np.uint64, 2 * nb)[:2])
+    assert L.t0b_hash_blocks(rt.handle, a.gpu_addr(), n + 1, 4096, ha.gpu_addr(), 0) == -1       # sizes in 8-byte units
+    # copies: dense, then a 48-byte-wide column block out of rows of 64 bytes into rows of 80 bytes
+    src = rng.integers(0, 256, 64 * 32, dtype=np.uint8)
+    s_, d_ = rt.upload(src), rt.alloc(64 * 32)
+    rt._check(L.t0b_copy_d2d(rt.handle, d_.gpu_addr(), 2048, s_.gpu_addr(), 2048, 2048, 1, 0))
+    assert np.array_equal(d_.read_as(np.uint8, 2048), src)
+    p_ = rt.alloc(80 * 32); p_.write(np.zeros(80 * 32, np.uint8))
+    rt._check(L.t0b_copy_d2d(rt.handle, p_.gpu_addr() + 16, 80, s_.gpu_addr() + 16, 64, 48, 32, 0))
+    got = p_.read_as(np.uint8, 80 * 32).reshape(32, 80)
+    assert np.array_equal(got[:, 16:64], src.reshape(32, 64)[:, 16:64]) and not got[:, :16].any() and not got[:, 64:].any()
+    assert L.t0b_copy_d2d(rt.handle, p_.gpu_addr() + 8, 80, s_.gpu_addr(), 64, 48, 32, 0) == -1  # 16-byte alignment
+
+
+def test_async_host_copies_are_ordered_with_the_stream(rt):
+    """t0b_memcpy_h2d_async / t0b_memcpy2d_d2h_async: the upload is seen by the GEMM queued after it, the read-back sees
+    the GEMM queued before it and completes at t0b_sync."""
+    import torch
+
+    m = n = k = 256
+    A = oracle.rand_bf16(m * k, 1).reshape(m, k); Bt = oracle.rand_bf16(n * k, 2).reshape(n, k)
+    a_h = torch.from_numpy(A.view(np.int16).copy()).pin_memory(); b_h = torch.from_numpy(Bt.view(np.int16).copy()).pin_memory()
+    c_h = torch.zeros((m, n // 2), dtype=torch.float32).pin_memory()
+    a, b, c = rt.alloc(m * k * 2), rt.alloc(n * k * 2), rt.alloc(m * n * 4)
+    L = lib()
+    rt._check(L.t0b_memcpy_h2d_async(rt.handle, a.gpu_addr(), a_h.data_ptr(), m * k * 2))
+    rt._check(L.t0b_memcpy_h2d_async(rt.handle, b.gpu_addr(), b_h.data_ptr(), n * k * 2))
+    rt.gemm(a, b, c, m, n, k, async_=True)
+    # the right half of C, as a pitched read-back
+    rt._check(L.t0b_memcpy2d_d2h_async(rt.handle, c_h.data_ptr(), (n // 2) * 4, c.gpu_addr() + (n // 2) * 4, n * 4, (n // 2) * 4, m))
+    rt.synchronize()
+    ref = oracle.gemm_bf16(A, Bt, m, n, k, threads=4)
+    assert np.abs(c_h.numpy() - ref[:, n // 2:]).max() <= 2.0 ** -7 * np.sqrt(k)
+    assert np.array_equal(c_h.numpy(), c.read_as(np.float32, m * n).reshape(m, n)[:, n // 2:])
+
+
+def test_switching_streams_keeps_pooled_buffers_ordered(rt):
+    """A buffer recycled on one stream and handed out again after t0b_ctx_set_stream must not be overwritten while work
+    queued on the old stream still reads it: the new stream is ordered behind the old one."""
+    import torch
+
+    m = n = k = 1024
+    A = oracle.rand_bf16(m * k, 5).reshape(m, k)
+    a, c = rt.upload(A), rt.alloc(m * n * 4)
+    old = lib().t0b_ctx_stream(rt.handle)
+    s2 = torch.cuda.Stream()
+    try:
+        tmp = rt.alloc(m * k * 2)
+        tmp.write(A)
+        for _ in range(20):
+            rt.gemm(a, tmp, c, m, n, k, async_=True)       # queued on the old stream, reads tmp
+        addr = tmp.gpu_addr()
+        rt.recycle(tmp)
+        rt.set_stream(s2.cuda_stream)
+        got = [rt.alloc(m * k * 2) for _ in range(8)]      # the pool hands the same memory out (among others of its size)
+        again = [g for g in got if g.gpu_addr() == addr]
+        assert again, "the recycled buffer did not come back from the pool"
+        rt._check(lib().t0b_memset0(rt.handle, addr, m * k * 2))               # on the NEW stream
+        rt.synchronize()
+    finally:
+        rt.set_stream(old or 0)
+    rt.synchronize()
+    ref = oracle.gemm_bf16(A, A, m, n, k, row_begin=7, row_end=8)[7]
+    assert np.abs(c.read_as(np.float32, m * n).reshape(m, n)[7] - ref).max() <= 2.0 ** -7 * np.sqrt(k)   # not zeros
