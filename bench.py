@@ -336,6 +336,27 @@ def context_measurements(torch, rt, L, stream, dev):
     return out
 
 
+def run_skinny(args, local_rank):
+    """--workload skinny: only the skinny / split-K GEMMs of the third benchmark config (one GPU)."""
+    import torch
+
+    import t0_gpu_b200 as t
+    from t0_gpu_b200._lib import lib
+
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    rt = t.GpuRuntime(local_rank)
+    stream = torch.cuda.Stream(device=dev)
+    torch.cuda.set_stream(stream)
+    rt.set_stream(stream.cuda_stream)
+    res = skinny_splitk_measurements(torch, t, rt, lib(), stream, dev)
+    hbm, kind = measured_hbm()
+    print(json.dumps({"metric": "skinny and split-K bf16 GEMMs, microseconds per call (GEMM + reduce)", "unit": "us", "n_gpus": 1,
+                      "hbm_peak": hbm, "peak_kind": f"of {kind} copy bandwidth", "shapes": res,
+                      "config": {"workload": "skinny_splitk", "l2": "eight operand sets rotated (280 MiB) > L2"}}), flush=True)
+    rt.close()
+
+
 def run_rows(args, local_rank):
     """--workload rows: only the memory-bound kernels, at the sizes of the table in profiles/ (one GPU)."""
     import torch
@@ -378,18 +399,30 @@ def skinny_splitk_measurements(torch, t, rt, L, stream, dev):
         xs = [(torch.rand((m, k), generator=g, device=dev) * 2 - 1).to(torch.bfloat16) for _ in range(nset)]
         ws = [(torch.rand((n, k), generator=g, device=dev) * 2 - 1).to(torch.bfloat16) for _ in range(nset)]
         ys = [torch.empty((m, n), dtype=torch.float32, device=dev) for _ in range(nset)]
-        cfg = t.auto_select(m, k, n)
-        if sk:
-            cfg = cfg.with_(split_k=sk)
-        cc = cfg.to_c()
         i = [0]
+        cc = [None]
 
         def call():
             j = i[0] % nset
             i[0] += 1
-            rt._check(L.t0b_gemm(rt.handle, C.byref(cc), 0, 1, xs[j].data_ptr(), ws[j].data_ptr(), ys[j].data_ptr(), m, n, k,
+            rt._check(L.t0b_gemm(rt.handle, C.byref(cc[0]), 0, 1, xs[j].data_ptr(), ws[j].data_ptr(), ys[j].data_ptr(), m, n, k,
                                  k, k, n, t.OUT_F32, 0, 0, 1.0, 0, 0, 1))
 
+        cfg = t.auto_select(m, k, n)
+        if sk:
+            # split_k is pinned by the benchmark config; the tile is the one that runs fastest WITH that split (a short
+            # timing of every B200 tile preset, as the tuner does when split_k is free).
+            best = None
+            for name_ in ("b200_128x64", "b200_128x128", "b200_128x256", "b200_256x128", "b200_256x256"):
+                cand = t.GemmConfig.preset(name_).with_(split_k=sk)
+                cc[0] = cand.to_c()
+                for _ in range(nset):
+                    call()
+                ms_c = time_steps(torch, call, 24, stream)
+                if best is None or ms_c < best[0]:
+                    best = (ms_c, cand)
+            cfg = best[1]
+        cc[0] = cfg.to_c()
         for _ in range(nset):
             call()
         l0 = rt.launch_count()
@@ -439,9 +472,13 @@ def run_single(args, local_rank):
     rt.set_stream(stream.cuda_stream)
     L = lib()
 
-    # The memory-bound kernels go first, on a GPU that has not yet been loaded: after a second of back-to-back GEMMs at
-    # the power cap the same kernels run about 13 % slower until the GPU has idled for about a second (measured).
+    # Order of the measurements.  The latency- and memory-bound kernels (row kernels, the skinny / split-K GEMMs) go first,
+    # on a GPU that has not yet been loaded: after a run of large GEMMs at the power cap the SM clock stays near its
+    # sustained value (about 1.3 GHz against 1.97) for a while, and these kernels then take 13 % (row kernels) to 50 %
+    # (skinny GEMMs) longer until the GPU has idled for about a second (measured).  The headline GEMM follows with its own
+    # warm-up, then the long-running context measurements (32768^2, the sustained loop, the MLP step).
     rows_first = {} if args.quick else row_kernel_measurements(torch, rt, L, stream, dev)
+    skinny_first = skinny_splitk_measurements(torch, t, rt, L, stream, dev)
 
     m = n = k = 8192
     a = device_normal_bf16(torch, (m, k), 1234, 1.0 / k ** 0.5, dev)
@@ -518,7 +555,7 @@ def run_single(args, local_rank):
         also["colshard_32768x32768x8192_bf16out_g1"] = {"ms": t_ms, "tflops": 2.0 * bm * bn * bk / (t_ms * 1e-3) / 1e12}
         del a4, b4, c4
 
-    also.update(skinny_splitk_measurements(torch, t, rt, L, stream, dev))
+    also.update(skinny_first)
     also.update(rows_first)
     if not args.quick:
         also["sustained_8192"] = sustained_measurement(torch, step, ms, flops, stream, physical_gpu_index(local_rank))
@@ -781,6 +818,9 @@ def run_multi(args, rank, local_rank, world):
     a_slice = a[rank * a_rows:(rank + 1) * a_rows]
     strips = 8
     srows = m // strips
+    # This rank's column block leaves the device as dense rows: a strided read-back of 2/world-GiB in rows of
+    # n_local * 2 bytes at a 64 KiB pitch reaches only ~34 GB/s over PCIe, a dense one ~57 GB/s.
+    dense = torch.empty((m, sh.n_local), dtype=torch.bfloat16, device=dev)
 
     def e2e_step():
         rt._check(L.t0b_memcpy_h2d_async(rt.handle, a_slice.data_ptr(), a_h.data_ptr(), a_h.numel() * 2))
@@ -788,9 +828,11 @@ def run_multi(args, rank, local_rank, world):
         dist.all_gather_into_tensor(a, a_slice)                      # in place: slice r sits at rows [r*a_rows, ...)
         for i in range(strips):
             op.run(A, B, async_=True, gather=True, rows=(i * srows, srows))
-            rt._check(L.t0b_memcpy2d_d2h_async(rt.handle, c_h.data_ptr() + i * srows * sh.n_local * elem, sh.n_local * elem,
-                                               op.c.gpu_addr() + (i * srows * n + sh.col0) * elem, n * elem,
-                                               sh.n_local * elem, srows))
+            strip_bytes = srows * sh.n_local * elem
+            rt._check(L.t0b_copy_d2d(rt.handle, dense.data_ptr() + i * strip_bytes, sh.n_local * elem,
+                                     op.c.gpu_addr() + (i * srows * n + sh.col0) * elem, n * elem, sh.n_local * elem, srows, 1))
+            rt._check(L.t0b_memcpy2d_d2h_async(rt.handle, c_h.data_ptr() + i * strip_bytes, sh.n_local * elem,
+                                               dense.data_ptr() + i * strip_bytes, sh.n_local * elem, sh.n_local * elem, srows))
         rt.synchronize()
 
     e2e_step()
@@ -806,16 +848,17 @@ def run_multi(args, rank, local_rank, world):
                                                  rt.synchronize()), 2)
     legs["allgather_a_nvlink"] = timed(lambda: dist.all_gather_into_tensor(a, a_slice), 2)
     legs["gemm_fused_gather"] = ms
-    legs["d2h_own_block"] = timed(lambda: (rt._check(L.t0b_memcpy2d_d2h_async(rt.handle, c_h.data_ptr(), sh.n_local * elem,
-                                                                              op.c.gpu_addr() + sh.col0 * elem, n * elem, sh.n_local * elem, m)),
-                                           rt.synchronize()), 2)
+    legs["d2h_own_block_dense"] = timed(lambda: (rt._check(L.t0b_memcpy2d_d2h_async(rt.handle, c_h.data_ptr(), sh.n_local * elem,
+                                                                                    dense.data_ptr(), sh.n_local * elem, sh.n_local * elem, m)),
+                                                 rt.synchronize()), 2)
     e2e = {"value": flops / (e2e_ms * 1e-3) / 1e12, "unit": UNIT,
            "h2d_bytes_per_step": (a_h.numel() + b_h.numel()) * 2, "d2h_bytes_per_step": c_h.numel() * 2,
            "ms_per_step": e2e_ms, "steps": e2e_steps, "note": "bytes are per rank", "legs_alone_ms": legs,
            "api": "t0b_memcpy_h2d_async (1/world row slice of A + the B shard), NCCL all-gather of A over NVLink, "
-                  f"t0b_gemm_multi_dst in {strips} row strips, t0b_memcpy2d_d2h_async of each strip, t0b_sync"}
+                  f"t0b_gemm_multi_dst in {strips} row strips, t0b_copy_d2d of each strip of the own block into dense rows, "
+                  "t0b_memcpy2d_d2h_async of each strip, t0b_sync"}
     op.close()
-    del a, b, a_h, b_h, c_h, A, B
+    del a, b, a_h, b_h, c_h, A, B, a_slice, dense, ref
     torch.cuda.empty_cache()
 
     # ---- the data-parallel MLP training step (fifth config) at the same ranks: the all-reduce form and the sharded optimizer.
@@ -911,9 +954,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--quick", action="store_true", help="skip the 32768^2 single-GPU context measurement")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
-    ap.add_argument("--workload", default="gemm", choices=["gemm", "mlp", "rows"],
+    ap.add_argument("--workload", default="gemm", choices=["gemm", "mlp", "rows", "skinny"],
                     help="gemm: the headline GEMM (default); mlp: the data-parallel MLP training step; "
-                         "rows: the memory-bound row kernels alone (one GPU)")
+                         "rows: the memory-bound row kernels alone (one GPU); skinny: the skinny / split-K GEMMs alone (one GPU)")
     ap.add_argument("--replicated-optimizer", action="store_true",
                     help="--workload mlp on several GPUs: all-reduce + replicated AdamW instead of the sharded optimizer")
     args = ap.parse_args()
@@ -925,9 +968,9 @@ def main():
         return
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-    if args.workload == "rows":
+    if args.workload in ("rows", "skinny"):
         if rank == 0:
-            run_rows(args, local_rank)
+            (run_rows if args.workload == "rows" else run_skinny)(args, local_rank)
     elif args.workload == "mlp":
         run_mlp(args, rank, local_rank, world)
     elif world > 1:

@@ -57,7 +57,9 @@ typedef struct t0b_gemm_config {
     uint32_t wg_size;
     uint32_t use_lds, double_buffer;
     uint32_t split_k;        /* 0 = None (the reference's Option<u32>) */
-    uint32_t lds_pad, n_col_passes;
+    uint32_t lds_pad, n_col_passes;   /* lds_pad: RDNA3 LDS row padding in the reference; here, when non-zero, the
+                                         rasterisation group width in tiles (a pure speed knob like the original: the
+                                         tuner sets it, results never depend on it) */
     uint32_t swap_grid, wgp_mode;
     uint32_t transpose;      /* T0B_TRANSPOSE_* (a name tag in the reference; the data layout is given per call) */
     uint32_t epilogue;       /* T0B_EPI_* */
@@ -264,6 +266,11 @@ T0B_API int32_t t0b_hash_blocks(t0b_ctx* ctx, uint64_t src, size_t bytes, size_t
  * measures the NVLink store rate that bounds the fused all-gather of t0b_gemm_multi_dst.  No reference counterpart. */
 T0B_API int32_t t0b_copy_d2d(t0b_ctx* ctx, uint64_t dst, size_t dst_pitch, uint64_t src, size_t src_pitch,
                              size_t width_bytes, size_t rows, int32_t async);
+/* The same copy on a copy engine, asynchronously: it runs on a side stream of the context behind the work queued so
+ * far, launches made after the call do not wait for it, and t0b_sync waits for it.  With a peer-mapped destination it
+ * moves a finished panel of C to a peer over NVLink while the next panel is multiplied.  No reference counterpart. */
+T0B_API int32_t t0b_copy_d2d_async(t0b_ctx* ctx, uint64_t dst, size_t dst_pitch, uint64_t src, size_t src_pitch,
+                                   size_t width_bytes, size_t rows);
 /* The config t0b_gemm_multi_dst uses when it is given none: the auto_select tile for (m, k, n_local), except that
  * with peers a tile that keeps both TMEM accumulators for one tile (256x512, 512x256) becomes 256x256 -- whose
  * accumulators double-buffer, so that the peer stores of one tile retire while the next is multiplied -- once the

@@ -91,6 +91,7 @@ SIGNATURES = {
                              _i32, _u32]),
     "t0b_hash_blocks": (_i32, [_ctx, _u64, _sz, _sz, _u64, _i32]),
     "t0b_copy_d2d": (_i32, [_ctx, _u64, _sz, _u64, _sz, _sz, _sz, _i32]),
+    "t0b_copy_d2d_async": (_i32, [_ctx, _u64, _sz, _u64, _sz, _sz, _sz]),
     "t0b_multi_dst_config": (_i32, [_u32, _u32, _u32, _i32, _i32, _cfgp]),
     "t0b_gemm_multi_dst": (_i32, [_ctx, _cfgp, _i32, _i32, _u64, _u64, C.POINTER(_u64), _i32, _u32, _u32, _u32, _u64,
                                   _u64, _u64, _u64, _i32, _i32]),

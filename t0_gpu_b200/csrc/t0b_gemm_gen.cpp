@@ -109,7 +109,7 @@ struct TunedRow {
     uint32_t m, n, k;
     int trans_a, trans_b, out_bf16;
     const char* tile;          // preset name
-    uint32_t split_k, swap_grid;
+    uint32_t split_k, swap_grid, group;   // group: rasterisation group width (0 = automatic), carried in lds_pad
     float tflops;
 };
 // Measured on B200 with t0b_tune (python -m t0_gpu_b200.make_tuned_table), one row per benchmark shape and layout.
@@ -156,6 +156,7 @@ bool tuned_lookup(uint32_t m, uint32_t n, uint32_t k, int trans_a, int trans_b, 
         if (t0b_config_preset(r.tile, out) != T0B_OK) continue;
         out->split_k = r.split_k > 1 ? r.split_k : 0;
         out->swap_grid = r.swap_grid;
+        out->lds_pad = r.group;
         if (source) *source = 1;
         return true;
     }

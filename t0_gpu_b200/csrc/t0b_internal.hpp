@@ -72,6 +72,8 @@ struct t0b_ctx {
     // Copy streams of the host-buffer GEMM (created on first use).
     cudaStream_t h2d_stream = nullptr, d2h_stream = nullptr;
     bool d2h_pending = false;   // an asynchronous read-back was queued since the last t0b_sync
+    cudaStream_t p2p_stream = nullptr;   // device-to-device / peer copies that run beside the compute stream
+    bool p2p_pending = false;
 };
 
 namespace t0b {

@@ -138,6 +138,7 @@ void t0b_ctx_destroy(t0b_ctx* ctx) {
     if (ctx->ws) cudaFree(ctx->ws);
     if (ctx->h2d_stream) cudaStreamDestroy(ctx->h2d_stream);
     if (ctx->d2h_stream) cudaStreamDestroy(ctx->d2h_stream);
+    if (ctx->p2p_stream) cudaStreamDestroy(ctx->p2p_stream);
     if (ctx->status_host) cudaFreeHost(ctx->status_host);
     if (ctx->own_stream) cudaStreamDestroy(ctx->own_stream);
     delete ctx;
@@ -372,6 +373,28 @@ int32_t t0b_memcpy2d_d2h_async(t0b_ctx* ctx, void* dst, size_t dst_pitch, uint64
     return check_cuda(ctx, e, "t0b_memcpy2d_d2h_async");
 }
 
+int32_t t0b_copy_d2d_async(t0b_ctx* ctx, uint64_t dst, size_t dst_pitch, uint64_t src, size_t src_pitch, size_t width_bytes,
+                           size_t rows) {
+    int32_t rc = precheck(ctx);
+    if (rc != T0B_OK) return rc;
+    if (width_bytes == 0 || rows == 0) return T0B_OK;
+    if (!dst || !src || dst_pitch < width_bytes || src_pitch < width_bytes)
+        return set_error(ctx, T0B_ERR_INVALID, "t0b_copy_d2d_async: null pointer or pitch smaller than the row");
+    if (ctx->capturing) return set_error(ctx, T0B_ERR_INVALID, "t0b_copy_d2d_async: not available during graph capture");
+    std::lock_guard<std::recursive_mutex> lk(ctx->mu);
+    if (!ctx->p2p_stream) {
+        rc = check_cuda(ctx, cudaStreamCreateWithFlags(&ctx->p2p_stream, cudaStreamNonBlocking), "cudaStreamCreate(p2p)");
+        if (rc != T0B_OK) return rc;
+    }
+    // Behind the work queued so far on the compute stream; launches made after this call do not wait for the copy.
+    cudaError_t e = order_behind(ctx->p2p_stream, ctx->stream);
+    if (e == cudaSuccess)
+        e = cudaMemcpy2DAsync(reinterpret_cast<void*>(dst), dst_pitch, reinterpret_cast<void*>(src), src_pitch, width_bytes, rows,
+                              cudaMemcpyDeviceToDevice, ctx->p2p_stream);
+    ctx->p2p_pending = true;
+    return check_cuda(ctx, e, "t0b_copy_d2d_async");
+}
+
 int32_t t0b_memset0(t0b_ctx* ctx, uint64_t dst, size_t bytes) {
     int32_t rc = precheck(ctx);
     if (rc != T0B_OK) return rc;
@@ -385,6 +408,11 @@ int32_t t0b_sync(t0b_ctx* ctx) {
     if (rc != T0B_OK) return rc;
     rc = check_cuda(ctx, cudaStreamSynchronize(ctx->stream), "cudaStreamSynchronize");
     if (rc != T0B_OK) return rc;
+    if (ctx->p2p_pending) {   // side-stream device copies (t0b_copy_d2d_async) complete here too
+        ctx->p2p_pending = false;
+        rc = check_cuda(ctx, cudaStreamSynchronize(ctx->p2p_stream), "cudaStreamSynchronize(p2p)");
+        if (rc != T0B_OK) return rc;
+    }
     if (ctx->d2h_pending) {   // asynchronous read-backs (t0b_memcpy2d_d2h_async) complete here too
         ctx->d2h_pending = false;
         rc = check_cuda(ctx, cudaStreamSynchronize(ctx->d2h_stream), "cudaStreamSynchronize(d2h)");

@@ -52,14 +52,14 @@ def main():
     rt = GpuRuntime(0)
     lines = ["// Shipped autotune table.  Generated on a B200 by `python -m t0_gpu_b200.make_tuned_table` (t0b_tune over the",
              "// benchmark shapes and their backward shapes); one row per shape, layout and output type:",
-             "//   {M, N, K, trans_a, trans_b, out_bf16, tile preset, split_k, swap_grid, measured TFLOP/s}"]
+             "//   {M, N, K, trans_a, trans_b, out_bf16, tile preset, split_k, swap_grid, raster group, measured TFLOP/s}"]
     for (m, n, k, ta, tb, od) in shapes():
         cfg, tf = rt.tune(m, n, k, trans_a=bool(ta), trans_b=bool(tb), out_dtype=od)
         preset = PRESETS[(cfg.tile_m, cfg.tile_n)]
-        lines.append('{%d, %d, %d, %d, %d, %d, "%s", %d, %d, %.1ff},' % (m, n, k, ta, tb, int(od == OUT_BF16), preset, cfg.split_k or 0,
-                                                                       int(cfg.swap_grid), tf))
+        lines.append('{%d, %d, %d, %d, %d, %d, "%s", %d, %d, %d, %.1ff},' % (m, n, k, ta, tb, int(od == OUT_BF16), preset, cfg.split_k or 0,
+                                                                           int(cfg.swap_grid), cfg.lds_pad, tf))
         print(lines[-1], flush=True)
-    lines.append('{0, 0, 0, 0, 0, 0, "b200_128x128", 0, 0, 0.0f},   // terminator (never matches: shapes are non-zero)')
+    lines.append('{0, 0, 0, 0, 0, 0, "b200_128x128", 0, 0, 0, 0.0f},   // terminator (never matches: shapes are non-zero)')
     with open(args.out, "w") as f:
         f.write("\n".join(lines) + "\n")
     rt.close()

@@ -167,6 +167,29 @@ class ColumnShardedGemm:
                                                 arr, len(dsts), nrows, s.n_local, self.k, self.k, s.n_local, self.n,
                                                 s.col0, self.out_dtype, int(async_)))
 
+    def run_panels(self, a: GpuBuffer, b_shard: GpuBuffer, panels: int = 8) -> None:
+        """The same product with the gather on the copy engines: the GEMM is launched panel by panel (row strips of
+        A and C) with this rank's buffer as its only destination, and every finished panel is copied to each peer by
+        t0b_copy_d2d_async on a side stream, peer (rank + 1) first, while the next panel is multiplied.  At any moment
+        a rank sends to one peer, so the ranks' transfers form a permutation of the GPUs.  Same bits as run()."""
+        if self._closed:
+            raise RuntimeError("ColumnShardedGemm.run_panels after close()")
+        s = self.shard
+        if s.n_local == 0:
+            return
+        elem = 2 if self.out_dtype == OUT_BF16 else 4
+        rows_per = (self.m + panels - 1) // panels
+        rows_per = (rows_per + 255) // 256 * 256
+        width = s.n_local * elem
+        pitch = self.n * elem
+        for r0 in range(0, self.m, rows_per):
+            nrows = min(rows_per, self.m - r0)
+            self.run(a, b_shard, async_=True, gather=False, rows=(r0, nrows))
+            off = (r0 * self.n + s.col0) * elem
+            for peer in self._peer_ptrs[1:]:
+                self.rt._check(lib().t0b_copy_d2d_async(self.rt.handle, peer + off, pitch, self._peer_ptrs[0] + off, pitch,
+                                                        width, nrows))
+
     def finish(self) -> None:
         """Collective: wait for this rank's kernel, then for every rank's.  After it every rank's C is complete."""
         self.rt.synchronize()

@@ -82,10 +82,10 @@ def _shipped_rows():
     rows = []
     with open(os.path.join(ROOT, "t0_gpu_b200", "csrc", "t0b_tuned_table.inc")) as f:
         for line in f:
-            m = re.match(r'\{(\d+), (\d+), (\d+), (\d), (\d), (\d), "(\w+)", (\d+), (\d), ([\d.]+)f\},', line.strip())
+            m = re.match(r'\{(\d+), (\d+), (\d+), (\d), (\d), (\d), "(\w+)", (\d+), (\d), (\d+), ([\d.]+)f\},', line.strip())
             if m and int(m.group(1)) > 0:
                 rows.append((int(m.group(1)), int(m.group(2)), int(m.group(3)), int(m.group(4)), int(m.group(5)), int(m.group(6)),
-                             m.group(7), int(m.group(8)), int(m.group(9))))
+                             m.group(7), int(m.group(8)), int(m.group(9)), int(m.group(10))))
     return rows
 
 
@@ -93,11 +93,13 @@ def test_auto_select_answers_from_the_shipped_table_then_the_cost_model():
     """auto_select = predict_best over the tune cache in the reference (src/t0/cost_model.rs:593-601, 788-1078): here a
     table measured on B200 ships inside the library, and shapes it does not hold fall through to the cost model."""
     rows = _shipped_rows()
-    for (m, n, k, ta, tb, ob, preset, sk, swap) in rows:
+    assert len(rows) >= 20 and (8192, 8192, 8192, 0, 0, 0) in [r[:6] for r in rows]      # the benchmark shapes are in it
+    for (m, n, k, ta, tb, ob, preset, sk, swap, group) in rows:
         cfg, src = t.auto_select_source(m, k, n, bool(ta), bool(tb), ob)
         want = t.GemmConfig.preset(preset)
         assert src == "table", (m, n, k, src)
-        assert (cfg.tile_m, cfg.tile_n, cfg.split_k or 0, int(cfg.swap_grid)) == (want.tile_m, want.tile_n, sk if sk > 1 else 0, swap)
+        assert (cfg.tile_m, cfg.tile_n, cfg.split_k or 0, int(cfg.swap_grid), cfg.lds_pad) == \
+            (want.tile_m, want.tile_n, sk if sk > 1 else 0, swap, group)
     # the layout-less front door prefers the NT / f32 row of a shape
     by_shape = {}
     for r in rows:
