@@ -372,8 +372,11 @@ def run_rows(args, local_rank):
     rt.set_stream(stream.cuda_stream)
     sampler = ClockSampler(physical_gpu_index(local_rank), period_s=0.02)
     sampler.start()
-    res = row_kernel_measurements(torch, rt, lib(), stream, dev, norm_sizes=((1024, 4096), (8192, 4096), (32768, 4096)),
-                                  ce_sizes=((1024, 32000), (8192, 32000)))
+    if args.quick:     # the small set a profiler capture uses (about 2 GiB resident at a time)
+        res = row_kernel_measurements(torch, rt, lib(), stream, dev, embedding=False)
+    else:
+        res = row_kernel_measurements(torch, rt, lib(), stream, dev, norm_sizes=((1024, 4096), (8192, 4096), (32768, 4096)),
+                                      ce_sizes=((1024, 32000), (8192, 32000)))
     clocks = sampler.stop()
     hbm, kind = measured_hbm()
     print(json.dumps({"metric": "memory-bound kernels, achieved HBM GB/s over algorithmic bytes", "unit": "GB/s", "n_gpus": 1,
@@ -477,8 +480,8 @@ def run_single(args, local_rank):
     # sustained value (about 1.3 GHz against 1.97) for a while, and these kernels then take 13 % (row kernels) to 50 %
     # (skinny GEMMs) longer until the GPU has idled for about a second (measured).  The headline GEMM follows with its own
     # warm-up, then the long-running context measurements (32768^2, the sustained loop, the MLP step).
-    rows_first = {} if args.quick else row_kernel_measurements(torch, rt, L, stream, dev)
-    skinny_first = skinny_splitk_measurements(torch, t, rt, L, stream, dev)
+    rows_first = {} if (args.quick or args.headline_only) else row_kernel_measurements(torch, rt, L, stream, dev)
+    skinny_first = {} if args.headline_only else skinny_splitk_measurements(torch, t, rt, L, stream, dev)
 
     m = n = k = 8192
     a = device_normal_bf16(torch, (m, k), 1234, 1.0 / k ** 0.5, dev)
@@ -514,13 +517,15 @@ def run_single(args, local_rank):
 
     # The other sizes of the sweep and the 1-GPU time of the sharded workload, for context.
     also = {}
-    for s in (2048, 4096):
+    for s in (() if args.headline_only else (2048, 4096)):
         aa, bb, cc = a[:s, :s].contiguous(), b[:s, :s].contiguous(), torch.empty((s, s), dtype=torch.float32, device=dev)
         f = lambda: gemm(aa, bb, cc, s, s, s)
         for _ in range(3):
             f()
         t_ms = time_steps(torch, f, max(args.steps, 20), stream)
         also[f"square_{s}_nn_f32out"] = {"ms": t_ms, "tflops": 2.0 * s ** 3 / (t_ms * 1e-3) / 1e12}
+    if args.headline_only:
+        args.quick = True
     # 256^3 is launch-bound: time it as a stream of launches and as one CUDA graph of 64 launches replayed.
     import ctypes as C
     s = 256
@@ -954,6 +959,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--quick", action="store_true", help="skip the 32768^2 single-GPU context measurement")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--headline-only", action="store_true",
+                    help="time only the headline GEMM (plus 256^3 and the host-buffer leg): the short command profiler captures use")
     ap.add_argument("--workload", default="gemm", choices=["gemm", "mlp", "rows", "skinny"],
                     help="gemm: the headline GEMM (default); mlp: the data-parallel MLP training step; "
                          "rows: the memory-bound row kernels alone (one GPU); skinny: the skinny / split-K GEMMs alone (one GPU)")

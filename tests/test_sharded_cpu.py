@@ -35,11 +35,12 @@ def test_multi_destination_gemm_uses_the_double_buffered_tile():
     m, k = 32768, 8192
     for world in (2, 4, 8):
         n_local = 32768 // world
+        two_acc = {(256, 512), (512, 256)}      # the tiles that keep both TMEM accumulators for one tile
         alone = multi_dst_config(m, k, n_local, 1)
-        assert (alone.tile_m, alone.tile_n) == (256, 512) and not alone.split_k      # what auto_select gives one GPU
+        assert (alone.tile_m, alone.tile_n) in two_acc and not alone.split_k           # what one GPU runs (shipped table)
         fused = multi_dst_config(m, k, n_local, world)
         if world == 2:       # link time / math time = 0.25: the faster math tile wins (measured)
-            assert (fused.tile_m, fused.tile_n) == (256, 512) and not fused.split_k
+            assert (fused.tile_m, fused.tile_n) in two_acc and not fused.split_k
         else:                # 0.75 and 1.8: the stores must overlap the next main loop
             assert (fused.tile_m, fused.tile_n, fused.wg_size) == (256, 256, 192) and not fused.split_k
     small = multi_dst_config(256, 256, 256, 2)                                    # small tiles are left alone
