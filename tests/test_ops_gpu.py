@@ -141,6 +141,20 @@ def test_generate_load_submit_handshake(rt):
         GpuKernel.load(rt, b"not an elf")
 
 
+def test_dispatch_bench_times_one_launch(rt):
+    """`GpuRuntime::dispatch_bench` (src/ignis/gpu_context.rs:297-307): submit one kernel and wait; here it also returns
+    the device time of the launch (CUDA events on the runtime's stream)."""
+    cfg = t.GemmConfig.tile_64x64_k16()
+    m, k, n = 128, 256, 128
+    x = oracle.rand_bf16(m * k, 3); wt = oracle.rand_bf16(n * k, 4)
+    xb, wb, yb = rt.upload(x), rt.upload(wt), rt.alloc_zero(m * n * 4)
+    ka = t.build_kernargs(xb.gpu_addr(), wb.gpu_addr(), yb.gpu_addr(), k, n, m, cfg)
+    ms = rt.dispatch_bench(cfg, t.compute_grid(cfg, m, n), ka)
+    assert 0.0 < ms < 50.0
+    ref = oracle.gemm_bf16(x, wt, m, n, k)
+    assert np.abs(yb.read_as(np.float32, m * n).reshape(m, n) - ref).max() <= 2.0 ** -7 * np.sqrt(k)
+
+
 def test_example_gemm_correctness_ported_line_for_line(rt):
     """examples/test_gemm_correctness.rs:65-260 with this build's runtime objects standing where the reference's do:
     generate -> compile -> KfdDevice::open -> create_queue -> DispatchPool::new(&device, 32) -> GpuKernel::load ->
