@@ -476,7 +476,8 @@ int32_t t0b_gemm_host(t0b_ctx* ctx, const t0b_gemm_config* cfg, int32_t trans_a,
     if (chunk_rows == 0) chunk_rows = std::max<uint32_t>(512u, ((m + 7) / 8 + 511u) & ~511u);   // about eight blocks
     chunk_rows = (chunk_rows + 127u) & ~127u;
     const uint32_t nchunks = (m + chunk_rows - 1) / chunk_rows;
-    const uint32_t want_panels = std::max(1u, std::min(8u, n / 512u));
+    uint32_t want_panels = std::max(1u, std::min(8u, n / 512u));
+    if (const char* e = std::getenv("T0B_HOST_PANELS")) want_panels = std::max(1, std::atoi(e));   // measurement knob
     const uint32_t panel_cols = (((n + want_panels - 1) / want_panels) + 63u) & ~63u;
     const uint32_t npanels = (n + panel_cols - 1) / panel_cols;
     const uint32_t nsteps = std::max(nchunks, npanels);
