@@ -149,7 +149,16 @@ T0B_API int32_t t0b_resolve_plan(const t0b_gemm_config* cfg, uint32_t m, uint32_
  * and the KFD objects under it (KfdDevice / GpuBuffer / AqlQueue / DispatchPool, src/kfd/mod.rs).
  * ---------------------------------------------------------------------------------------------- */
 
-/* GpuRuntime::new(), gpu_context.rs:113.  Fails (T0B_ERR_CUDA) when no CUDA device is usable. */
+/* GpuRuntime::new(), gpu_context.rs:113.  Fails (T0B_ERR_CUDA) when no CUDA device is usable.
+ * Environment read here (the reference's knobs are T0_DUMP_ASM / T0_OPT_LEVEL / T0_VALIDATE_KA, src/t0/compile.rs:1149,
+ * src/t0/opt_passes.rs:30, src/ignis/gpu_context.rs:277; these are their counterparts for a library without a compiler):
+ *   T0_FORCE_CONFIG=<preset>  every GEMM called without a config runs this preset (t0b_config_preset names);
+ *   T0_DUMP_CONFIG=1          one stderr line per new GEMM shape: config name, who chose it (caller, forced, tuned in
+ *                             this process, shipped table, cost model) and the kernel variant it resolves to;
+ *   T0B_PDL=0                 launches without programmatic stream serialization;
+ *   T0B_CLUSTER_SPLITK=0      split-K always through slabs and the reduce kernel;
+ *   T0B_RASTER_GROUP=<n>      rasterisation group width for every GEMM (a measurement knob).
+ * Kernarg blobs are always validated (the reference does so under T0_VALIDATE_KA). */
 T0B_API int32_t t0b_ctx_create(int32_t device, t0b_ctx** out);
 T0B_API void t0b_ctx_destroy(t0b_ctx* ctx);
 /* Launch on a caller-owned cudaStream_t (e.g. the current stream of a host framework); NULL restores the

@@ -77,6 +77,7 @@ struct GemmParams {
     int* status;
     unsigned long long wait_limit_ns;
     int tma_store;          // 1: the epilogue writes C with TMA stores through the third tensor map
+    unsigned wait_hint_ns;  // suspend-time hint of the epilogue warps' wait for an accumulator
     int cluster_sk;         // > 1: split-K inside a thread-block cluster of that many CTAs (one per K range): the partial
                             // tiles stay in shared memory and are summed over distributed shared memory; 0 = slabs
 };
@@ -190,15 +191,16 @@ __device__ __forceinline__ bool bounded_wait(uint32_t bar, uint32_t parity, cons
 
 // The same wait for a whole warp: lane 0 polls (with a suspend-time hint, so the thread sleeps in hardware between
 // polls instead of spinning beside the MMA issuer for a whole main loop), the result is broadcast.
-__device__ __forceinline__ bool bounded_wait_warp(uint32_t bar, uint32_t parity, const WaitCtl& ctl, int code, int lane) {
+__device__ __forceinline__ bool bounded_wait_warp(uint32_t bar, uint32_t parity, const WaitCtl& ctl, int code, int lane,
+                                                  uint32_t hint_ns) {
     int ok = 1;
     if (lane == 0) {
         ok = 0;
-        if (ptx::mbar_try_wait_hint(bar, parity, 20000u)) ok = 1;
+        if (ptx::mbar_try_wait_hint(bar, parity, hint_ns)) ok = 1;
         else {
             const uint64_t t0 = ptx::globaltimer_ns();
             while (true) {
-                if (ptx::mbar_try_wait_hint(bar, parity, 20000u)) { ok = 1; break; }
+                if (ptx::mbar_try_wait_hint(bar, parity, hint_ns)) { ok = 1; break; }
                 if (*ctl.abort) break;
                 if (ptx::globaltimer_ns() - t0 > ctl.limit_ns) {
                     *ctl.abort = 1;
@@ -589,7 +591,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
         const uint32_t stage = ctrl + T::kCtrlBytes + static_cast<uint32_t>(warp - 2) * 4096u;
         for (int w = cluster_id; w < num_work; w += num_clusters) {
             const WorkItem wi = decode_work(p, w, BM, BNT);
-            if (!bounded_wait_warp(tfull_bar(slot), slot_phase, ctl, DEV_TIMEOUT_TMEM_FULL, lane)) break;
+            if (!bounded_wait_warp(tfull_bar(slot), slot_phase, ctl, DEV_TIMEOUT_TMEM_FULL, lane, p.wait_hint_ns)) break;
             ptx::tc_fence_after();
             const int row0 = wi.m0 + ((MT == 2 && ND == 0) ? group * kMmaM : 0) + static_cast<int>(cta_rank) * kBmCta + q * 32;
             const int n_base = wi.n0 + (ND == 1 ? group * BN : 0);

@@ -160,11 +160,22 @@ int32_t run_gemm(t0b_ctx* ctx, const GemmCall& g) {
     }
 
     t0b_gemm_config cfg;
+    const char* cfg_source = "caller";
+    int tuned_source = 0;
     if (g.cfg) cfg = *g.cfg;
     else {
-        // Measured in this process (t0b_tune), else the table shipped with the library, else the cost model.
-        if (!tuned_lookup(g.m, g.n, g.k, g.trans_a, g.trans_b, g.out_bf16, &cfg, nullptr))
+        // A forced preset (T0_FORCE_CONFIG), else measured in this process (t0b_tune), else the table shipped with the
+        // library, else the cost model.
+        if (!ctx->force_config.empty()) {
+            if (t0b_config_preset(ctx->force_config.c_str(), &cfg) != T0B_OK)
+                return set_error(ctx, T0B_ERR_INVALID, "gemm: T0_FORCE_CONFIG=%s is not a preset name", ctx->force_config.c_str());
+            cfg_source = "forced";
+        } else if (tuned_lookup(g.m, g.n, g.k, g.trans_a, g.trans_b, g.out_bf16, &cfg, &tuned_source)) {
+            cfg_source = tuned_source == 2 ? "tuned in this process" : "shipped table";
+        } else {
             default_b200_config(g.m, g.k, g.n, ctx->num_sms, &cfg);
+            cfg_source = "cost model";
+        }
         if (g.no_auto_split) cfg.split_k = 0;
     }
     if (g.slabs_only) cfg.split_k = g.force_split;
@@ -175,6 +186,15 @@ int32_t run_gemm(t0b_ctx* ctx, const GemmCall& g) {
     PlanInput pin{g.m, g.n, g.k, g.trans_a, g.trans_b, g.lda, g.ldb, g.a, g.b, ctx->num_sms};
     resolve_plan(&cfg, pin, &plan);
 
+    if (ctx->dump_config) {
+        // One line per new (shape, layout, output, config) on stderr: what was chosen, by whom, and what it runs as.
+        char name[96], line[320];
+        t0b_config_name(&cfg, name, sizeof(name));
+        std::snprintf(line, sizeof(line), "t0b gemm %ux%ux%u %c%c %s dst=%d: %s (%s) -> tile %ux%u cta_group %u stages %u split_k %u%s",
+                      g.m, g.n, g.k, g.trans_a ? 'T' : 'N', g.trans_b ? 'T' : 'N', g.out_bf16 ? "bf16" : "f32", g.n_dst, name, cfg_source,
+                      plan.bm, plan.bn, plan.cta_group, plan.stages, plan.split_k, plan.use_tma ? "" : " (CUDA-core kernel)");
+        if (ctx->dumped.emplace(line, 1).second) std::fprintf(stderr, "%s\n", line);
+    }
     const size_t elem = g.out_bf16 ? 2 : 4;
     if (g.k == 0) {
         // Empty contraction: every accumulator is +0.0, so the result is epilogue(0).
@@ -333,6 +353,7 @@ int32_t run_gemm(t0b_ctx* ctx, const GemmCall& g) {
         p.mn_lbo = 8192; p.mn_sbo = 1024; p.mn_kstep = 2048;
         p.status = ctx->status_dev;
         p.wait_limit_ns = ctx->wait_limit_ns;
+        p.wait_hint_ns = ctx->wait_hint_ns;
         if (g.slabs_only && sk == 1) {
             // One slab: store straight into it as f32.
             p.out_bf16 = 0; p.epi = EpiChain{}; p.n_dst = 1; p.ldc = static_cast<long long>(ld_partial);

@@ -20,6 +20,10 @@ struct t0b_ctx {
     bool pdl = true;            // launch GEMMs with programmatic stream serialization (T0B_PDL=0 turns it off)
     int raster_group = 0;       // > 0: rasterisation group width for every GEMM (T0B_RASTER_GROUP, for measurements); 0 = chosen per shape
     bool cluster_splitk = true; // split-K of single-CTA tiles runs as thread-block clusters (T0B_CLUSTER_SPLITK=0: slabs + reduce kernel)
+    std::string force_config;   // T0_FORCE_CONFIG=<preset name>: the tile every GEMM without an explicit config runs
+    bool dump_config = false;   // T0_DUMP_CONFIG=1: print the config and the kernel variant of each new GEMM shape to stderr
+    std::map<std::string, int> dumped;
+    unsigned wait_hint_ns = 20000;   // T0B_WAIT_HINT_NS: how long an epilogue warp may sleep in hardware per poll of its accumulator barrier
     int sm_limit = 0;           // > 0: the persistent GEMM kernels occupy at most this many SMs
     cudaStream_t own_stream = nullptr;
     cudaStream_t stream = nullptr;

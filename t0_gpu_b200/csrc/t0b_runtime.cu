@@ -107,6 +107,9 @@ int32_t t0b_ctx_create(int32_t device, t0b_ctx** out) {
         ctx->num_sms = prop.multiProcessorCount;
         if (const char* e = std::getenv("T0B_PDL")) ctx->pdl = std::atoi(e) != 0;
         if (const char* e = std::getenv("T0B_CLUSTER_SPLITK")) ctx->cluster_splitk = std::atoi(e) != 0;
+        if (const char* e = std::getenv("T0B_WAIT_HINT_NS")) ctx->wait_hint_ns = static_cast<unsigned>(std::max(0, std::atoi(e)));
+        if (const char* e = std::getenv("T0_FORCE_CONFIG")) ctx->force_config = e;
+        if (const char* e = std::getenv("T0_DUMP_CONFIG")) ctx->dump_config = std::atoi(e) != 0;
         if (const char* e = std::getenv("T0B_RASTER_GROUP")) ctx->raster_group = std::max(0, std::atoi(e));
         rc = check_cuda(ctx, cudaStreamCreateWithFlags(&ctx->own_stream, cudaStreamNonBlocking), "cudaStreamCreate");
         ctx->stream = ctx->own_stream;

@@ -23,8 +23,27 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import List, Optional
 
+import os
+
 from ._lib import lib
 from .gpu_context import OUT_BF16, OUT_F32, GpuRuntime
+
+
+def _nvtx_push(name: str) -> None:
+    """Open an NVTX range around a phase of the step when T0B_NVTX=1 (forward, loss, backward with its gradient
+    exchange, the optimizer), for a timeline profiler; otherwise nothing."""
+    if os.environ.get("T0B_NVTX", "0") == "1":
+        import torch
+
+        torch.cuda.nvtx.range_push(name)
+
+
+def _nvtx_pop() -> None:
+    if os.environ.get("T0B_NVTX", "0") == "1":
+        import torch
+
+        torch.cuda.nvtx.range_pop()
+
 
 
 @dataclass
@@ -219,6 +238,7 @@ class MlpTrainer:
         nh = len(cfg.hidden)
         scale = 1.0 / float(self.rows_total)
         # forward
+        _nvtx_push("t0b.mlp.forward")
         self._cast(x, self.x16, B * cfg.d_in)
         inp, k = self.x16, cfg.d_in
         self._wait_update(self._gamma_unit)      # gammas (read by every RMSNorm)
@@ -233,10 +253,14 @@ class MlpTrainer:
         V = cfg.n_classes
         self._wait_layer(nh)
         self._gemm(inp, self.w16[nh], self.logits, B, V, k, False, False, k, V)
+        _nvtx_pop()
         # loss and its gradient, stored directly as the bf16 operand of the two GEMMs that follow
+        _nvtx_push("t0b.mlp.loss")
         self._ck(L.t0b_softmax_ce_bf16(h, self.logits.data_ptr(), targets.data_ptr(), self.losses.data_ptr(),
                                        self.dlogits16.data_ptr(), B, V, V, scale, 1))
+        _nvtx_pop()
         # backward
+        _nvtx_push("t0b.mlp.backward")
         # dW_out[k, V] = h_last^T [k, B] * dlogits [B, V]: A stored [B, k] read transposed
         ids = self._layer_units[nh]
         per = k // len(ids)                     # rows of dW_out per panel = columns of h_last
@@ -259,7 +283,10 @@ class MlpTrainer:
                 self._gemm(self.dz16, self.w16[l], self.dh, B, k, n, False, True, n, n)
         if self.world > 1:
             self._start_reduce(self._gamma_unit) # the small gamma gradients go last, in one piece
+        _nvtx_pop()
+        _nvtx_push("t0b.mlp.grad_exchange_wait")
         self._finish_reduce()
+        _nvtx_pop()
 
     def _start_reduce(self, unit: int):
         """Start the exchange of one unit's gradient: all-reduce (replicated optimizer) or reduce-scatter (sharded)."""
@@ -341,7 +368,9 @@ class MlpTrainer:
 
     def step(self, x, targets):
         self.forward_backward(x, targets)
+        _nvtx_push("t0b.mlp.optimizer")
         self.optimizer_step()
+        _nvtx_pop()
 
     def mean_loss(self) -> float:
         """Global mean loss: sum of this rank's per-row losses / rows_total, summed over ranks."""

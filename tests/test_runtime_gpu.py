@@ -273,3 +273,38 @@ def test_switching_streams_keeps_pooled_buffers_ordered(rt):
     rt.synchronize()
     ref = oracle.gemm_bf16(A, A, m, n, k, row_begin=7, row_end=8)[7]
     assert np.abs(c.read_as(np.float32, m * n).reshape(m, n)[7] - ref).max() <= 2.0 ** -7 * np.sqrt(k)   # not zeros
+
+
+def test_force_and_dump_config_env():
+    """T0_FORCE_CONFIG makes every GEMM without an explicit config run the named preset, T0_DUMP_CONFIG prints one line
+    per new shape with the chooser and the kernel variant; the result still matches the oracle."""
+    import os
+    import subprocess
+    import sys
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    code = (
+        "import numpy as np, oracle, t0_gpu_b200 as t\n"
+        "rt = t.GpuRuntime(0)\n"
+        "m = n = k = 256\n"
+        "A = oracle.rand_bf16(m * k, 11); B = oracle.rand_bf16(n * k, 12)\n"
+        "da, db, dc = rt.upload(A), rt.upload(B), rt.alloc(m * n * 4)\n"
+        "rt.gemm(da, db, dc, m, n, k)\n"
+        "rt.gemm(da, db, dc, m, n, k)\n"
+        "ref = oracle.gemm_bf16(A, B, m, n, k, trans_b=True)\n"
+        "tol = 2.0 ** -7 * np.sqrt(k) * np.abs(oracle.bf16_to_f32(A)).max() * np.abs(oracle.bf16_to_f32(B)).max()\n"
+        "assert np.abs(dc.read_as(np.float32, m * n) - ref.ravel()).max() <= tol   # the GEMM tolerance of the parity suite\n"
+        "rt.gemm(da, db, dc, m, n, k, cfg=t.GemmConfig.preset('b200_128x64'))\n"
+        "print('ok')\n"
+    )
+    env = dict(os.environ, T0_FORCE_CONFIG="b200_128x128", T0_DUMP_CONFIG="1", PYTHONPATH=root)
+    r = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, cwd=root, timeout=600)
+    assert r.returncode == 0 and "ok" in r.stdout, r.stderr[-2000:]
+    lines = [ln for ln in r.stderr.splitlines() if ln.startswith("t0b gemm 256x256x256")]
+    assert len(lines) == 2, r.stderr                     # one per (shape, config), not one per call
+    assert "(forced) -> tile 128x128" in lines[0]
+    assert "(caller) -> tile 128x64" in lines[1]
+    # An unknown preset name is an error, not a silent fallback.
+    env["T0_FORCE_CONFIG"] = "no_such_tile"
+    r = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, cwd=root, timeout=600)
+    assert r.returncode != 0 and "T0_FORCE_CONFIG" in (r.stderr + r.stdout)
