@@ -417,15 +417,19 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
     const uint32_t tmem_base = *tmem_slot;
     // Cluster split-K (single-CTA tiles only): the CTAs of the cluster are the K ranges of one tile.
     const bool csk = (CG == 1 && MT == 1) && p.cluster_sk > 1;
-    // Programmatic dependent launch: everything above (barriers, TMEM, descriptor prefetch) may run while the previous
-    // kernel of the stream drains; nothing below may touch global memory before that kernel has completed.
-    ptx::grid_dependency_wait();
-    ptx::grid_launch_dependents();   // the next GEMM's CTAs may take over SMs as this grid's CTAs exit
-
     const WaitCtl ctl{abort_flag, p.status, p.wait_limit_ns};
     const int num_work = p.tiles_m * p.tiles_n * p.split_k;
     const int cluster_id = blockIdx.x / CG;
     const int num_clusters = gridDim.x / CG;
+    // The first work item is decoded here, before the dependency wait: the parameter reads and the divisions of the
+    // decode (half a microsecond on a cold SM, measured with globaltimer stamps) then overlap the previous kernel's
+    // tail.  The empty asm pins the values in front of the wait.
+    const WorkItem first_wi = decode_work(p, cluster_id < num_work ? cluster_id : 0, BM, BNT);
+    asm volatile("" ::"r"(first_wi.m0), "r"(first_wi.n0), "r"(first_wi.kb_begin), "r"(first_wi.kb_end), "r"(first_wi.split));
+    // Programmatic dependent launch: everything above (barriers, TMEM, descriptor prefetch) may run while the previous
+    // kernel of the stream drains; nothing below may touch global memory before that kernel has completed.
+    ptx::grid_dependency_wait();
+    ptx::grid_launch_dependents();   // the next GEMM's CTAs may take over SMs as this grid's CTAs exit
 
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
@@ -434,7 +438,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
             uint32_t ph = 0;
             bool ok = true;
             for (int w = cluster_id; w < num_work && ok; w += num_clusters) {
-                const WorkItem wi = decode_work(p, w, BM, BNT);
+                const WorkItem wi = (w == cluster_id) ? first_wi : decode_work(p, w, BM, BNT);
                 const int m0_cta = wi.m0 + static_cast<int>(cta_rank) * kBmCta;
                 const int n0_cta = wi.n0 + static_cast<int>(cta_rank) * T::kBnCta;
                 for (int kb = wi.kb_begin; kb < wi.kb_end; ++kb) {
@@ -498,7 +502,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
             uint32_t slot_ph[2] = {0u, 0u};    // phase of each accumulator slot
             bool ok = true;
             for (int w = cluster_id; w < num_work && ok; w += num_clusters) {
-                const WorkItem wi = decode_work(p, w, BM, BNT);
+                const WorkItem wi = (w == cluster_id) ? first_wi : decode_work(p, w, BM, BNT);
                 if constexpr (MT == 1) {
                     if (!bounded_wait(tempty_bar(acc), slot_ph[acc] ^ 1u, ctl, DEV_TIMEOUT_TMEM_EMPTY)) { ok = false; break; }
                     ptx::tc_fence_after();
@@ -590,7 +594,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
         if (tma_out && lane == 0) ptx::prefetch_tmap(&tmap_c);
         const uint32_t stage = ctrl + T::kCtrlBytes + static_cast<uint32_t>(warp - 2) * 4096u;
         for (int w = cluster_id; w < num_work; w += num_clusters) {
-            const WorkItem wi = decode_work(p, w, BM, BNT);
+            const WorkItem wi = (w == cluster_id) ? first_wi : decode_work(p, w, BM, BNT);
             if (!bounded_wait_warp(tfull_bar(slot), slot_phase, ctl, DEV_TIMEOUT_TMEM_FULL, lane, p.wait_hint_ns)) break;
             ptx::tc_fence_after();
             const int row0 = wi.m0 + ((MT == 2 && ND == 0) ? group * kMmaM : 0) + static_cast<int>(cta_rank) * kBmCta + q * 32;
@@ -757,11 +761,15 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
         // cluster scope).  CTA r then sums rows [r, r+1) * 128 / sk of the tile over the sk partials IN K-RANGE ORDER,
         // starting from +0.0 -- the arithmetic of splitk_reduce_kernel and of the reference's host-side slab sum
         // (examples/test_gemm_correctness.rs:203-207) -- and writes them to C.  No slab ever reaches global memory.
+        // This phase takes 3.9 us of a 13.5 us kernel (128x128 tile, four K ranges), and every alternative measured
+        // slower: sixteen loads in flight per thread instead of four (+1.3 us: the distributed-shared-memory path
+        // congests), pushing the rows to their owners with st.shared::cluster (+2.2 us), and exchanging the partials
+        // through slabs in L2 with the same cluster barrier between the stores and the loads (+3.9 us).
         ptx::cluster_arrive();
         ptx::cluster_wait();
         if (warp >= 2 && !*abort_flag) {
             const int sk = p.cluster_sk;
-            const WorkItem wi = decode_work(p, blockIdx.x, BM, BNT);
+            const WorkItem& wi = first_wi;   // a cluster split-K CTA has exactly one work item (CG == 1: cluster_id == blockIdx.x)
             const int rows_per = kBmCta / sk;
             constexpr int kPiecesPerRow = BN / 4;
             const int total = rows_per * kPiecesPerRow;
