@@ -357,6 +357,92 @@ def run_skinny(args, local_rank):
     rt.close()
 
 
+def run_timeline(args, local_rank):
+    """--workload timeline: where a GEMM launch spends its time, from %globaltimer stamps inside the kernels.  Uses the
+    timeline build of the library (libt0b200_trace.so: the same sources with -DT0B_TRACE, `python -m
+    t0_gpu_b200.build --trace`), its own context, and t0b_trace_set.  Sixteen launches go out back to back; the last
+    four are reported, each phase as the median over the CTAs of the launch."""
+    import ctypes as C
+
+    import numpy as np
+    import torch
+
+    from t0_gpu_b200._lib import load_trace_lib
+
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    L = load_trace_lib()
+    ctx = C.c_void_p()
+    if L.t0b_ctx_create(local_rank, C.byref(ctx)) != 0:
+        raise SystemExit("t0b_ctx_create failed in the timeline build")
+    stream = torch.cuda.Stream(device=dev)
+    torch.cuda.set_stream(stream)
+    assert L.t0b_ctx_set_stream(ctx, stream.cuda_stream) == 0
+    slots, ctas = 8, 160
+    trace = torch.zeros(slots * ctas * 16, dtype=torch.int64, device=dev)
+    shapes = [(256, 256, 256), (128, 4096, 4096), (2048, 2048, 2048), (1024, 4096, 4096), (4096, 4096, 4096)]
+    out = {}
+    for (m, n, k) in shapes:
+        a = device_normal_bf16(torch, (m, k), 77, 1.0 / k ** 0.5, dev)
+        b = device_normal_bf16(torch, (k, n), 78, 1.0 / k ** 0.5, dev)
+        cs = [torch.empty((m, n), dtype=torch.float32, device=dev) for _ in range(4)]
+        torch.cuda.synchronize()
+
+        def launch(i):
+            rc = L.t0b_gemm(ctx, None, 0, 0, a.data_ptr(), b.data_ptr(), cs[i & 3].data_ptr(), m, n, k, k, n, n, 0, 0, 0, 1.0, 0, 0, 1)
+            if rc != 0:
+                raise SystemExit(f"t0b_gemm failed: {rc}")
+
+        for i in range(4):
+            launch(i)
+        assert L.t0b_sync(ctx) == 0
+        trace.zero_()
+        torch.cuda.synchronize()
+        assert L.t0b_trace_set(ctx, trace.data_ptr(), slots) == 0
+        for i in range(2 * slots):
+            launch(i)
+        assert L.t0b_sync(ctx) == 0
+        assert L.t0b_trace_set(ctx, 0, 0) == 0
+        tr = trace.cpu().numpy().reshape(slots, ctas, 16)      # launches 8..15, in order
+        rows = []
+        for li in range(slots - 4, slots):
+            cur, prev = tr[li], tr[li - 1]
+            live = cur[:, 0] > 0
+            med = lambda slot: float(np.median(cur[live & (cur[:, slot] > 0), slot])) if (live & (cur[:, slot] > 0)).any() else None
+            prev_end = float(prev[prev[:, 14] > 0, 14].max())
+            prev_dep = float(np.median(prev[prev[:, 2] > 0, 2]))
+            dep, issue, data, mma, acc, staged, stored = med(2), med(3), med(4), med(5), med(6), med(7), med(8)
+            end = float(cur[live, 14].max())
+            # Slots 12 / 13 hold %globaltimer values (close to the other stamps) in a cluster split-K launch, cycle counters otherwise.
+            csk = med(13) is not None and bool((np.abs(cur[live, 13] - cur[live, 0]) < 1_000_000_000).all())
+            ph = {"previous_launch_gone_to_dependency_wait_done": dep - prev_end, "to_first_k_block_issued": issue - dep,
+                  "to_first_operands_in_smem": data - issue, "main_loop": mma - data, "to_accumulator_complete": acc - mma}
+            if csk:
+                ph["accumulator_to_shared_memory"] = staged - acc
+                ph["cluster_barrier"] = med(13) - staged
+                ph["sum_over_dsmem_and_closing_barrier"] = med(12) - med(13)
+                ph["teardown"] = end - med(12)
+            else:
+                ph["epilogue_stores_complete"] = stored - acc
+                ph["teardown"] = end - stored
+                mm = live & (cur[:, 12] > 0) & (cur[:, 13] > cur[:, 12])
+                if mm.any():
+                    ghz = (cur[mm, 13] - cur[mm, 12]).astype(float) / (cur[mm, 5] - cur[mm, 4]).astype(float)
+                    ph["sm_clock_ghz_main_loop"] = float(np.median(ghz))
+            ph = {kk: (round(v / 1000.0, 2) if not kk.startswith("sm_clock") else round(v, 3)) for kk, v in ph.items()}
+            ph["period"] = round((dep - prev_dep) / 1000.0, 2)
+            rows.append(ph)
+        keys = rows[0].keys()
+        out[f"{m}x{n}x{k}_nn_f32out"] = {"ctas": int((tr[slots - 1][:, 0] > 0).sum()), "cluster_split_k": bool(csk),
+                                          "us_median_of_last_4_launches": {kk: round(float(np.median([r[kk] for r in rows])), 3) for kk in keys}}
+        del a, b, cs
+    L.t0b_ctx_destroy(ctx)
+    print(json.dumps({"metric": "GEMM launch timeline from in-kernel %globaltimer stamps (timeline build), microseconds",
+                      "unit": "us", "n_gpus": 1, "shapes": out,
+                      "config": {"workload": "timeline", "launches": "16 back to back, programmatic dependent launch; the last 4 reported",
+                                 "library": "libt0b200_trace.so (-DT0B_TRACE)"}}), flush=True)
+
+
 def run_rows(args, local_rank):
     """--workload rows: only the memory-bound kernels, at the sizes of the table in profiles/ (one GPU)."""
     import torch
@@ -972,9 +1058,10 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--headline-only", action="store_true",
                     help="time only the headline GEMM (plus 256^3 and the host-buffer leg): the short command profiler captures use")
-    ap.add_argument("--workload", default="gemm", choices=["gemm", "mlp", "rows", "skinny"],
+    ap.add_argument("--workload", default="gemm", choices=["gemm", "mlp", "rows", "skinny", "timeline"],
                     help="gemm: the headline GEMM (default); mlp: the data-parallel MLP training step; "
-                         "rows: the memory-bound row kernels alone (one GPU); skinny: the skinny / split-K GEMMs alone (one GPU)")
+                         "rows: the memory-bound row kernels alone (one GPU); skinny: the skinny / split-K GEMMs alone (one GPU); "
+                         "timeline: phases of a GEMM launch from in-kernel timer stamps (needs the --trace build of the library)")
     ap.add_argument("--replicated-optimizer", action="store_true",
                     help="--workload mlp on several GPUs: all-reduce + replicated AdamW instead of the sharded optimizer")
     args = ap.parse_args()
@@ -986,9 +1073,9 @@ def main():
         return
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-    if args.workload in ("rows", "skinny"):
+    if args.workload in ("rows", "skinny", "timeline"):
         if rank == 0:
-            (run_rows if args.workload == "rows" else run_skinny)(args, local_rank)
+            {"rows": run_rows, "skinny": run_skinny, "timeline": run_timeline}[args.workload](args, local_rank)
     elif args.workload == "mlp":
         run_mlp(args, rank, local_rank, world)
     elif world > 1:

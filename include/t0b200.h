@@ -289,6 +289,18 @@ T0B_API int32_t t0b_copy_d2d_async(t0b_ctx* ctx, uint64_t dst, size_t dst_pitch,
  * 256x512).  Never split-K.  No counterpart in the reference (single GPU). */
 T0B_API int32_t t0b_multi_dst_config(uint32_t m, uint32_t k, uint32_t n_local, int32_t n_dst, int32_t num_sms,
                                      t0b_gemm_config* out);
+/* Launch timeline (diagnostic; works in libt0b200_trace.so, the same sources built with -DT0B_TRACE by
+ * `python -m t0_gpu_b200.build --trace`; the regular library returns T0B_ERR_UNSUPPORTED).  buf is a zeroed device
+ * buffer of launches x T0B_TRACE_CTAS x 16 uint64; GEMM launch i of the context (tcgen05 kernels with at most
+ * T0B_TRACE_CTAS CTAs) stamps %globaltimer nanoseconds into buf[i % launches][blockIdx.x][slot], one thread per role:
+ * 0 kernel entry, 1 set-up done, 2 dependency wait returned, 3 first K block issued, 4 first operands arrived, 5 last
+ * MMA issued, 6 accumulator complete, 7 last chunk staged, 8 stores complete, 9 teardown barrier, 10 all loads issued,
+ * 12 / 13 cluster split-K: closing barrier passed / partials visible (otherwise clock64 at 4 and 5, so that cycles per
+ * nanosecond gives the SM clock of the main loop), 14 TMEM freed.  buf = 0 stops the stamping.  `bench.py --workload
+ * timeline` prints the phases.  The reference has no GPU timers at all (wall-clock Instant around dispatches,
+ * src/t0/cost_model.rs:961-978). */
+#define T0B_TRACE_CTAS 160
+T0B_API int32_t t0b_trace_set(t0b_ctx* ctx, uint64_t buf, uint32_t launches);
 /* Column-sharded GEMM with the all-gather folded into the epilogue: this rank computes C[:, col0 : col0+n_local]
  * and stores every finished tile into each of the n_dst row-major [M, ldc] destinations (its own and its
  * peers', as peer-mapped device pointers).  No counterpart in the reference (single GPU). */

@@ -134,6 +134,7 @@ extern "C" {
     pub fn t0b_copy_d2d(ctx: *mut t0b_ctx, dst: u64, dst_pitch: usize, src: u64, src_pitch: usize, width_bytes: usize, rows: usize, is_async: i32) -> i32;
     pub fn t0b_copy_d2d_async(ctx: *mut t0b_ctx, dst: u64, dst_pitch: usize, src: u64, src_pitch: usize, width_bytes: usize, rows: usize) -> i32;
     pub fn t0b_multi_dst_config(m: u32, k: u32, n_local: u32, n_dst: i32, num_sms: i32, out: *mut t0b_gemm_config) -> i32;
+    pub fn t0b_trace_set(ctx: *mut t0b_ctx, buf: u64, launches: u32) -> i32;
     pub fn t0b_gemm_multi_dst(ctx: *mut t0b_ctx, cfg: *const t0b_gemm_config, trans_a: i32, trans_b: i32, a: u64, b: u64, c_dsts: *const u64, n_dst: i32, m: u32, n_local: u32, k: u32, lda: u64, ldb: u64, ldc: u64, col0: u64, out_dtype: i32, is_async: i32) -> i32;
     pub fn t0b_gemm_slabs(ctx: *mut t0b_ctx, cfg: *const t0b_gemm_config, x: u64, wt: u64, y: u64, m: u32, n: u32, k: u32, split_k: u32, is_async: i32) -> i32;
     pub fn t0b_splitk_reduce(ctx: *mut t0b_ctx, partial: u64, split_k: u32, m: u32, n: u32, slab_stride_elems: u64, ld_partial: u64, c: u64, ldc: u64, out_dtype: i32, epilogue: i32, bias: u64, alpha: f32, is_async: i32) -> i32;

@@ -92,6 +92,7 @@ SIGNATURES = {
     "t0b_hash_blocks": (_i32, [_ctx, _u64, _sz, _sz, _u64, _i32]),
     "t0b_copy_d2d": (_i32, [_ctx, _u64, _sz, _u64, _sz, _sz, _sz, _i32]),
     "t0b_copy_d2d_async": (_i32, [_ctx, _u64, _sz, _u64, _sz, _sz, _sz]),
+    "t0b_trace_set": (_i32, [_ctx, _u64, _u32]),
     "t0b_multi_dst_config": (_i32, [_u32, _u32, _u32, _i32, _i32, _cfgp]),
     "t0b_gemm_multi_dst": (_i32, [_ctx, _cfgp, _i32, _i32, _u64, _u64, C.POINTER(_u64), _i32, _u32, _u32, _u32, _u64,
                                   _u64, _u64, _u64, _i32, _i32]),
@@ -146,6 +147,20 @@ SIGNATURES = {
 }
 
 _LIB = None
+TRACE_LIB_PATH = os.path.join(HERE, "lib", "libt0b200_trace.so")
+
+
+def load_trace_lib() -> C.CDLL:
+    """The timeline build of the library (`python -m t0_gpu_b200.build --trace`): the same entry points, with GEMM
+    kernels that stamp their phase changes (t0b_trace_set).  A separate library with its own contexts."""
+    if not os.path.exists(TRACE_LIB_PATH):
+        raise ImportError(f"{TRACE_LIB_PATH} is missing: build it with `python -m t0_gpu_b200.build --trace`")
+    L = C.CDLL(TRACE_LIB_PATH)
+    for name, (res, args) in SIGNATURES.items():
+        fn = getattr(L, name)
+        fn.restype = res
+        fn.argtypes = args
+    return L
 
 
 def lib() -> C.CDLL:

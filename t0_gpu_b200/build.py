@@ -1,8 +1,9 @@
 """Build libt0b200.so (the C-ABI CUDA library) in-tree for sm_100a with nvcc.
 
-    python -m t0_gpu_b200.build [--force] [--verbose]
+    python -m t0_gpu_b200.build [--force] [--verbose] [--trace]
 
-The library is cross-compiled (no GPU needed) and lands in t0_gpu_b200/lib/libt0b200.so.
+The library is cross-compiled (no GPU needed) and lands in t0_gpu_b200/lib/libt0b200.so; `--trace` builds the timeline
+variant (the same sources with -DT0B_TRACE) as t0_gpu_b200/lib/libt0b200_trace.so.
 """
 from __future__ import annotations
 
@@ -15,6 +16,9 @@ CSRC = os.path.join(HERE, "csrc")
 OUT_DIR = os.path.join(HERE, "lib")
 OUT = os.path.join(OUT_DIR, "libt0b200.so")
 OBJ_DIR = os.path.join(OUT_DIR, "obj")
+# The timeline build: the same sources with -DT0B_TRACE (the GEMM kernels stamp %globaltimer at their phase changes).
+TRACE_OUT = os.path.join(OUT_DIR, "libt0b200_trace.so")
+TRACE_OBJ_DIR = os.path.join(OUT_DIR, "obj_trace")
 
 SOURCES = ["t0b_runtime.cu", "t0b_gemm.cu", "t0b_rowops.cu", "t0b_embedding.cu", "t0b_util.cu", "t0b_gemm_gen.cpp", "t0b_tile_ir.cpp"]
 # The GEMM kernel variants (BN, CG, MT, ND): gemm_variant.cu compiled once per entry, side by side.
@@ -30,12 +34,14 @@ def _newest(paths) -> float:
     return max(os.path.getmtime(p) for p in paths)
 
 
-def build(force: bool = False, verbose: bool = False) -> str:
+def build(force: bool = False, verbose: bool = False, trace: bool = False) -> str:
+    out, obj_dir = (TRACE_OUT, TRACE_OBJ_DIR) if trace else (OUT, OBJ_DIR)
+    extra = ["-DT0B_TRACE"] if trace else []
     # Up to date already (e.g. a built library shipped without its object files): nothing to do.
     all_inputs = [os.path.join(CSRC, f) for f in SOURCES + HEADERS + ["gemm_variant.cu"]]
-    if not force and os.path.exists(OUT) and os.path.getmtime(OUT) >= _newest(all_inputs):
-        return OUT
-    os.makedirs(OBJ_DIR, exist_ok=True)
+    if not force and os.path.exists(out) and os.path.getmtime(out) >= _newest(all_inputs):
+        return out
+    os.makedirs(obj_dir, exist_ok=True)
     hdr_time = _newest([os.path.join(CSRC, h) for h in HEADERS])
     objs, jobs = [], []
     units = [(src, os.path.splitext(src)[0] + ".o", []) for src in SOURCES]
@@ -43,11 +49,11 @@ def build(force: bool = False, verbose: bool = False) -> str:
               for v in GEMM_VARIANTS]
     for src, obj_name, defines in units:
         sp = os.path.join(CSRC, src)
-        obj = os.path.join(OBJ_DIR, obj_name)
+        obj = os.path.join(obj_dir, obj_name)
         objs.append(obj)
         stale = force or not os.path.exists(obj) or os.path.getmtime(obj) < max(os.path.getmtime(sp), hdr_time)
         if stale:
-            cmd = [NVCC, *ARCH, *CFLAGS, *defines, "-c", sp, "-o", obj]
+            cmd = [NVCC, *ARCH, *CFLAGS, *extra, *defines, "-c", sp, "-o", obj]
             if src.endswith(".cpp"):
                 cmd.insert(1, "-x")
                 cmd.insert(2, "cu")
@@ -60,13 +66,13 @@ def build(force: bool = False, verbose: bool = False) -> str:
     failed = [cmd for cmd, p in zip(jobs, procs) if p.wait() != 0]
     if failed:
         raise subprocess.CalledProcessError(1, failed[0])
-    if force or not os.path.exists(OUT) or os.path.getmtime(OUT) < _newest(objs):
-        cmd = [NVCC, *ARCH, "-shared", "-o", OUT, *objs, "-cudart", "static"]
+    if force or not os.path.exists(out) or os.path.getmtime(out) < _newest(objs):
+        cmd = [NVCC, *ARCH, "-shared", "-o", out, *objs, "-cudart", "static"]
         if verbose:
             print(" ".join(cmd), flush=True)
         subprocess.run(cmd, check=True)
-    return OUT
+    return out
 
 
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))
+    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv, trace="--trace" in sys.argv))

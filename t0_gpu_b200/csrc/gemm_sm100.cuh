@@ -78,6 +78,9 @@ struct GemmParams {
     unsigned long long wait_limit_ns;
     int tma_store;          // 1: the epilogue writes C with TMA stores through the third tensor map
     unsigned wait_hint_ns;  // suspend-time hint of the epilogue warps' wait for an accumulator
+#ifdef T0B_TRACE
+    unsigned long long* trace;   // timeline build only: [CTA][16] stamps of this launch (null = no stamps)
+#endif
     int cluster_sk;         // > 1: split-K inside a thread-block cluster of that many CTAs (one per K range): the partial
                             // tiles stay in shared memory and are summed over distributed shared memory; 0 = slabs
 };
@@ -164,6 +167,22 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, uint32_t lbo_
     d |= 2ull << 61;   // SWIZZLE_128B
     return d;
 }
+
+// Timeline build (-DT0B_TRACE, libt0b200_trace.so): one thread per role stamps %globaltimer (slots 12 / 13 of a
+// non-split-K launch: clock64, so that cycles / nanoseconds gives the SM clock of the main loop) into
+// trace[blockIdx.x][slot].  The regular build compiles the stamps away.
+//   0 kernel entry            1 set-up done (barriers, TMEM)   2 dependency wait returned     3 first K block issued (producer)
+//   4 first operands arrived  5 last MMA issued                6 accumulator complete (epilogue warp 0)
+//   7 last chunk staged       8 this warp's stores complete    9 teardown barrier passed      10 all loads issued
+//  12 cluster split-K: closing barrier passed (else clock64 at 4)    13 cluster split-K: partials visible (else clock64 at 5)
+//  14 TMEM freed
+#ifdef T0B_TRACE
+#define T0B_STAMP(slot) do { if (p.trace) p.trace[blockIdx.x * 16 + (slot)] = ptx::globaltimer_ns(); } while (0)
+#define T0B_STAMP_CLOCK(slot) do { if (p.trace) p.trace[blockIdx.x * 16 + (slot)] = static_cast<unsigned long long>(clock64()); } while (0)
+#else
+#define T0B_STAMP(slot) do { } while (0)
+#define T0B_STAMP_CLOCK(slot) do { } while (0)
+#endif
 
 struct WaitCtl {
     volatile int* abort;
@@ -384,6 +403,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) T0B_STAMP(0);
     const uint32_t cta_rank = (CG == 2) ? ptx::cluster_ctarank() : 0u;
     const bool is_leader = cta_rank == 0;
 
@@ -426,9 +446,11 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
     // tail.  The empty asm pins the values in front of the wait.
     const WorkItem first_wi = decode_work(p, cluster_id < num_work ? cluster_id : 0, BM, BNT);
     asm volatile("" ::"r"(first_wi.m0), "r"(first_wi.n0), "r"(first_wi.kb_begin), "r"(first_wi.kb_end), "r"(first_wi.split));
+    if (threadIdx.x == 0) T0B_STAMP(1);
     // Programmatic dependent launch: everything above (barriers, TMEM, descriptor prefetch) may run while the previous
     // kernel of the stream drains; nothing below may touch global memory before that kernel has completed.
     ptx::grid_dependency_wait();
+    if (threadIdx.x == 0) T0B_STAMP(2);
     ptx::grid_launch_dependents();   // the next GEMM's CTAs may take over SMs as this grid's CTAs exit
 
     if (warp == 0) {
@@ -475,9 +497,11 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                             for (int j = 0; j < T::kBnCta / 64; ++j) load(dst + j * 8192, &tmap_b, n_sub + j * 64, k0);
                         }
                     }
+                    if (w == cluster_id && kb == wi.kb_begin) T0B_STAMP(3);
                     if (++s == S) { s = 0; ph ^= 1u; }
                 }
             }
+            T0B_STAMP(10);
             // Tail: every slot must have been released, so no MMA-completion arrival can target this
             // CTA's shared memory after it exits.
             for (int i = 0; i < S && ok; ++i) {
@@ -509,6 +533,10 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                 }
                 for (int kb = wi.kb_begin; kb < wi.kb_end; ++kb) {
                     if (!bounded_wait(full_bar(s), ph, ctl, DEV_TIMEOUT_FULL)) { ok = false; break; }
+                    if (w == cluster_id && kb == wi.kb_begin) {
+                        T0B_STAMP(4);
+                        if (!csk) T0B_STAMP_CLOCK(12);
+                    }
                     ptx::tc_fence_after();
                     const uint32_t a_addr = smem_base + s * T::kStageBytes;
                     const uint32_t b_addr = a_addr + T::kATileBytes;
@@ -550,6 +578,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                     if (++s == S) { s = 0; ph ^= 1u; }
                 }
                 if (!ok) break;
+                T0B_STAMP(5);
+                if (!csk) T0B_STAMP_CLOCK(13);
                 if constexpr (MT == 1) {
                     if constexpr (CG == 1) ptx::mma_commit(tfull_bar(acc));
                     else ptx::mma_commit_pair(tfull_bar(acc), 0x3);
@@ -596,6 +626,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
         for (int w = cluster_id; w < num_work; w += num_clusters) {
             const WorkItem wi = (w == cluster_id) ? first_wi : decode_work(p, w, BM, BNT);
             if (!bounded_wait_warp(tfull_bar(slot), slot_phase, ctl, DEV_TIMEOUT_TMEM_FULL, lane, p.wait_hint_ns)) break;
+            if (warp == 2 && lane == 0) T0B_STAMP(6);
             ptx::tc_fence_after();
             const int row0 = wi.m0 + ((MT == 2 && ND == 0) ? group * kMmaM : 0) + static_cast<int>(cta_rank) * kBmCta + q * 32;
             const int n_base = wi.n0 + (ND == 1 ? group * BN : 0);
@@ -753,7 +784,9 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                 slot_phase ^= 1u;
             }
         }
+        if (warp == 2 && lane == 0) T0B_STAMP(7);
         if (tma_out && lane == 0) ptx::bulk_wait_group<0>();   // every TMA store of this warp has completed
+        if (warp == 2 && lane == 0) T0B_STAMP(8);
     }
 
     if (csk) {
@@ -767,6 +800,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
         // through slabs in L2 with the same cluster barrier between the stores and the loads (+3.9 us).
         ptx::cluster_arrive();
         ptx::cluster_wait();
+        if (threadIdx.x == 64) T0B_STAMP(13);
         if (warp >= 2 && !*abort_flag) {
             const int sk = p.cluster_sk;
             const WorkItem& wi = first_wi;   // a cluster split-K CTA has exactly one work item (CG == 1: cluster_id == blockIdx.x)
@@ -822,8 +856,10 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
     }
 
     // ---------------------------------------------------------------------- teardown (normal and abort paths)
+    if (csk && threadIdx.x == 64) T0B_STAMP(12);
     ptx::tc_fence_before();
     __syncthreads();
+    if (threadIdx.x == 0) T0B_STAMP(9);
     if (*abort_flag) {
         // Give this CTA's own TMA copies in flight time to land before the shared memory is released.
         const uint64_t t0 = ptx::globaltimer_ns();
@@ -837,6 +873,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
     if (warp == 1) {
         ptx::tc_fence_after();
         ptx::tmem_dealloc<CG>(tmem_base, T::kTmemCols);
+        if (lane == 0) T0B_STAMP(14);
     }
 }
 

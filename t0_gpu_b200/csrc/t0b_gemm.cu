@@ -13,6 +13,8 @@
 
 using namespace t0b;
 
+static constexpr int kTraceCtas = 160;   // CTAs per launch the timeline buffer has room for (T0B_TRACE_CTAS in the header)
+
 namespace {
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -376,6 +378,14 @@ int32_t run_gemm(t0b_ctx* ctx, const GemmCall& g) {
             }
         }
         const int num_work = p.tiles_m * p.tiles_n * p.split_k;
+#ifdef T0B_TRACE
+        p.trace = nullptr;
+        if (ctx->trace_buf && ctx->trace_slots > 0 && (cluster_sk ? num_work : ctx->num_sms) <= kTraceCtas) {
+            p.trace = reinterpret_cast<unsigned long long*>(ctx->trace_buf) +
+                      static_cast<size_t>(ctx->trace_next % ctx->trace_slots) * kTraceCtas * 16;
+            ++ctx->trace_next;
+        }
+#endif
         if (plan.cta_group == 2) {
             if (plan.n_tiles == 2) rc = launch_variant<256, 2, 2, 1>(ctx, ta, tb, tc, p, num_work);
             else if (plan.m_tiles == 2) rc = launch_variant<256, 2, 2>(ctx, ta, tb, tc, p, num_work);
@@ -419,6 +429,21 @@ uint64_t rd_u64(const uint8_t* p) { return rd_u32(p) | (static_cast<uint64_t>(rd
 }  // namespace
 
 extern "C" {
+
+int32_t t0b_trace_set(t0b_ctx* ctx, uint64_t buf, uint32_t launches) {
+    int32_t rc = precheck(ctx);
+    if (rc != T0B_OK) return rc;
+#ifdef T0B_TRACE
+    std::lock_guard<std::recursive_mutex> lk(ctx->mu);
+    ctx->trace_buf = buf;
+    ctx->trace_slots = buf ? launches : 0;
+    ctx->trace_next = 0;
+    return T0B_OK;
+#else
+    (void)buf; (void)launches;
+    return set_error(ctx, T0B_ERR_UNSUPPORTED, "trace_set: this is the regular build; the timeline build is libt0b200_trace.so");
+#endif
+}
 
 int32_t t0b_gemm(t0b_ctx* ctx, const t0b_gemm_config* cfg, int32_t trans_a, int32_t trans_b, uint64_t a, uint64_t b,
                  uint64_t c, uint32_t m, uint32_t n, uint32_t k, uint64_t lda, uint64_t ldb, uint64_t ldc,

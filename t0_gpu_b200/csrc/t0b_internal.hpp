@@ -24,6 +24,9 @@ struct t0b_ctx {
     bool dump_config = false;   // T0_DUMP_CONFIG=1: print the config and the kernel variant of each new GEMM shape to stderr
     std::map<std::string, int> dumped;
     unsigned wait_hint_ns = 20000;   // T0B_WAIT_HINT_NS: how long an epilogue warp may sleep in hardware per poll of its accumulator barrier
+    // Timeline build: where the stamps of the next GEMM launches go (t0b_trace_set); unused in the regular build.
+    uint64_t trace_buf = 0;
+    uint32_t trace_slots = 0, trace_next = 0;
     int sm_limit = 0;           // > 0: the persistent GEMM kernels occupy at most this many SMs
     cudaStream_t own_stream = nullptr;
     cudaStream_t stream = nullptr;

@@ -308,3 +308,44 @@ def test_force_and_dump_config_env():
     env["T0_FORCE_CONFIG"] = "no_such_tile"
     r = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, cwd=root, timeout=600)
     assert r.returncode != 0 and "T0_FORCE_CONFIG" in (r.stderr + r.stdout)
+
+
+def test_timeline_build_stamps_in_order():
+    """The timeline build of the library (-DT0B_TRACE) stamps the phases of a GEMM launch; the regular build refuses
+    t0b_trace_set.  Stamps of one CTA must be ordered: entry <= set-up <= dependency wait <= first issue <= first data <=
+    last MMA <= accumulator <= stores <= TMEM freed, and the product is the same as the regular build's."""
+    import os
+
+    import torch
+
+    from t0_gpu_b200 import _lib
+
+    rt = t.GpuRuntime(0)
+    assert lib().t0b_trace_set(rt.handle, 0, 0) == -6          # T0B_ERR_UNSUPPORTED in the regular build
+    if not os.path.exists(_lib.TRACE_LIB_PATH):
+        pytest.skip("timeline build not present (python -m t0_gpu_b200.build --trace)")
+    L = _lib.load_trace_lib()
+    ctx = C.c_void_p()
+    assert L.t0b_ctx_create(0, C.byref(ctx)) == 0
+    m = n = k = 512
+    A = oracle.rand_bf16(m * k, 5)
+    B = oracle.rand_bf16(n * k, 6)
+    da, db = rt.upload(A), rt.upload(B)
+    c_ref, c_tr = rt.alloc(m * n * 4), rt.alloc(m * n * 4)
+    rt.gemm(da, db, c_ref, m, n, k)
+    trace = torch.zeros(2 * 160 * 16, dtype=torch.int64, device="cuda:0")
+    assert L.t0b_trace_set(ctx, trace.data_ptr(), 2) == 0
+    for _ in range(2):
+        assert L.t0b_gemm(ctx, None, 0, 1, da.gpu_addr(), db.gpu_addr(), c_tr.gpu_addr(), m, n, k, k, k, n, 0, 0, 0, 1.0, 0, 0, 0) == 0
+    assert L.t0b_trace_set(ctx, 0, 0) == 0
+    tr = trace.cpu().numpy().reshape(2, 160, 16)
+    live = tr[1][:, 0] > 0
+    assert live.sum() >= 1
+    for cta in np.nonzero(live)[0]:
+        s = tr[1][cta]
+        chain = [s[0], s[1], s[2], s[3], s[4], s[5], s[6], s[8], s[14]]
+        assert all(x > 0 for x in chain), (cta, chain)
+        assert all(chain[i] <= chain[i + 1] for i in range(len(chain) - 1)), (cta, chain)
+        assert s[14] - s[0] < 1_000_000_000           # within a second
+    assert np.array_equal(c_tr.read_as(np.float32, m * n), c_ref.read_as(np.float32, m * n))
+    L.t0b_ctx_destroy(ctx)
