@@ -167,8 +167,11 @@ bool tuned_lookup(uint32_t m, uint32_t n, uint32_t k, int trans_a, int trans_b, 
 // random operands, SM clock ~1.5 GHz under tensor load).  It stands where the reference has its RDNA3 cost model
 // (src/t0/cost_model.rs:168-471): estimate the time of every candidate, keep the cheapest.
 //   time = waves * (k_blocks * cycles_per_k_block + exposed_epilogue) + launch, plus the slab reduce for split-K.
-// cycles_per_k_block: a 256-wide MMA runs at full rate, narrower ones take the same time for fewer columns; the
-// two-accumulator tiles (256x512, 512x256) move a quarter less operand data per FLOP but cannot hide their epilogue.
+// cycles_per_k_block: measured with in-kernel timer stamps (the timeline build).  Shared-memory bandwidth bounds the
+// main loop: the two-accumulator tiles (256x512, 512x256) need 128 B/clk and run 8 MMAs in ~1165 cycles, the 256x256
+// pair tile needs 160 B/clk (4 MMAs in ~780), the 128x256 single-CTA tile 192 B/clk (4 MMAs in ~760); narrower MMAs
+// take the same time for fewer columns.  The two-accumulator tiles cannot hide their epilogue.  The exchange of a
+// cluster split-K (barrier, sum over distributed shared memory, closing barrier) costs ~7000 cycles.
 void default_b200_config(uint32_t m, uint32_t k, uint32_t n, int num_sms, t0b_gemm_config* out) {
     struct Cand {
         uint32_t bm, bn, cg;
@@ -177,8 +180,8 @@ void default_b200_config(uint32_t m, uint32_t k, uint32_t n, int num_sms, t0b_ge
         double epi_tail;       // cycles after the last tile
     };
     static const Cand cands[] = {
-        {256, 512, 2, 1165.0, 10000.0, 0.0}, {512, 256, 2, 1175.0, 10000.0, 0.0}, {256, 256, 2, 650.0, 0.0, 8000.0},
-        {128, 256, 1, 700.0, 0.0, 8000.0},   {128, 128, 1, 700.0, 0.0, 5000.0},   {128, 64, 1, 550.0, 0.0, 3500.0},
+        {256, 512, 2, 1165.0, 10000.0, 0.0}, {512, 256, 2, 1175.0, 10000.0, 0.0}, {256, 256, 2, 780.0, 0.0, 8000.0},
+        {128, 256, 1, 760.0, 0.0, 8000.0},   {128, 128, 1, 700.0, 0.0, 5000.0},   {128, 64, 1, 550.0, 0.0, 3500.0},
     };
     if (num_sms <= 0) num_sms = 148;
     const uint32_t kb_total = std::max(1u, (k + 63) / 64);
@@ -198,10 +201,11 @@ void default_b200_config(uint32_t m, uint32_t k, uint32_t n, int num_sms, t0b_ge
             if (c.epi_exposed == 0.0 && kbps * c.kb_cycles < c.epi_tail) cyc += static_cast<double>(waves - 1) * (c.epi_tail - kbps * c.kb_cycles);
             if (sk > 1) {
                 // Single-CTA tiles with up to four K ranges (eight when all clusters fit at once: GPC sizes allow about
-                // fifteen eight-CTA clusters) sum their partials inside a thread-block cluster; the rest pay the slab
-                // round trip and a reduce kernel (launch + bytes at ~5 TB/s).
+                // fifteen eight-CTA clusters) sum their partials inside a thread-block cluster (~7000 cycles: barrier, sum
+                // over distributed shared memory, closing barrier); the rest pay the slab round trip and a second kernel
+                // (measured ~6 us more than the cluster path on 128x4096x4096: launch hand-over + bytes at ~5 TB/s).
                 const bool in_cluster = c.cg == 1 && (sk <= 4 || (sk == 8 && tiles <= 15));
-                cyc += in_cluster ? 2500.0 : 3000.0 + static_cast<double>(m) * n * 4.0 * (sk + 1) / 3300.0;
+                cyc += in_cluster ? 7000.0 : 14000.0 + static_cast<double>(m) * n * 4.0 * (sk + 1) / 3300.0;
             }
             if (cyc < best) {
                 best = cyc;
