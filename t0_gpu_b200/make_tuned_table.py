@@ -25,7 +25,7 @@ def shapes():
     out = []
     for ta, tb in ((0, 0), (0, 1), (1, 0), (1, 1)):                       # config 1: 256^3 in every layout
         out.append((256, 256, 256, ta, tb, OUT_F32))
-    for s in (2048, 4096, 8192):                                          # config 2: square sweep, row-major operands
+    for s in (512, 1024, 2048, 4096, 8192):                               # config 2: square sweep, row-major operands (512 and 1024: the reference's README table)
         out.append((s, s, s, 0, 0, OUT_F32))
         out.append((s, s, s, 0, 1, OUT_F32))
     for m, k, n in ((128, 4096, 4096), (4096, 4096, 128), (512, 16384, 512)):   # config 3: skinny and deep-K
