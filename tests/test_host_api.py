@@ -241,6 +241,19 @@ def test_split_k_selected_for_small_grids():
     assert _lib.lib().t0b_gemm_workspace_bytes(C.byref(c.to_c()), 512, 512, 16384) == (c.split_k) * 512 * 512 * 4
 
 
+def test_cost_model_split_k_paths_for_unmeasured_skinny_shapes():
+    """Shapes outside the shipped table: the model's split-K costs come from in-kernel timer measurements (cluster
+    exchange ~7000 cycles, slab round trip + second kernel ~14000 + bytes), so skinny shapes that fit one wave of
+    clusters take the one-launch cluster path (single-CTA tile, at most 8 K ranges) -- what the on-device tuner picks
+    for them -- and only deeper splits fall back to slabs."""
+    for (m, k, n) in ((256, 4096, 256), (16, 4096, 4096), (128, 8192, 8192), (1024, 8192, 1024)):
+        cfg, src = t.auto_select_source(m, k, n)
+        assert src == "model", (m, k, n, src)
+        assert cfg.tile_m == 128 and 2 <= (cfg.split_k or 1) <= 8, (m, k, n, cfg.name())
+    # A full grid needs no split at all, however deep K is.
+    assert t.auto_select_source(4096, 16384, 4096)[0].split_k is None
+
+
 def test_autotune_cache_roundtrip(tmp_path):
     """src/t0/auto_gemm.rs:578-610: save + load of the per-shape JSON cache, and a file in the reference's own
     format (as its `save_cache` writes it) parses to the same config."""
