@@ -661,6 +661,18 @@ def run_single(args, local_rank):
     also.update(rows_first)
     if not args.quick:
         also["sustained_8192"] = sustained_measurement(torch, step, ms, flops, stream, physical_gpu_index(local_rank))
+        # The same loop with bf16 output, the form of the cuBLAS run behind the sustained peak (torch.matmul of bf16
+        # tensors writes bf16): like for like, half the C bytes.
+        c16 = torch.empty((m, n), dtype=torch.bfloat16, device=dev)
+        step16 = lambda: gemm(a, b, c16, m, n, k, out_dtype=t.OUT_BF16)
+        for _ in range(3):
+            step16()
+        also["sustained_8192_bf16out"] = sustained_measurement(torch, step16, ms, flops, stream, physical_gpu_index(local_rank), seconds=1.5)
+        del c16
+        # The MLP step starts from a rested GPU, as `--workload mlp` does: four seconds of GEMMs at the power cap leave the
+        # SM clock near 1.3 GHz for about a second (see the note on the order of the measurements above).
+        torch.cuda.synchronize()
+        time.sleep(1.5)
         also.update(context_measurements(torch, rt, L, stream, dev))
 
     # End to end through the C ABI with host buffers.
