@@ -527,3 +527,45 @@ def test_host_buffer_gemm_pipeline(rt, m, n, k, ta, tb, chunk):
         else:
             assert np.linalg.norm(got - ref) / np.linalg.norm(ref) <= 5e-3
             assert np.all(c_h[:, n:] == 0xC61C)
+
+
+def test_randomized_shapes_layouts_and_configs(rt):
+    """Seeded random draw over what a caller can combine: aligned, 8-aligned and odd shapes (the last take the CUDA-core
+    kernel), the four layouts, both output types, no / bias / bias+ReLU epilogue, automatic or explicit tile with
+    split-K 2..16 (cluster path, slab path and effective-split clamping all occur) and both raster directions; every
+    case against the oracle within the GEMM tolerance."""
+    import random
+
+    rnd = random.Random(20240611)
+    presets = ["b200_128x64", "b200_128x128", "b200_128x256", "b200_256x128", "b200_256x256", "b200_512x256", "b200_256x512"]
+    for case in range(48):
+        kind = rnd.random()
+        if kind < 0.4:
+            m, n, k = rnd.randint(1, 8) * 64, rnd.randint(1, 8) * 64, rnd.randint(1, 10) * 64
+        elif kind < 0.8:
+            m, n, k = rnd.randint(1, 500), rnd.randint(1, 60) * 8, rnd.randint(1, 80) * 8
+        else:
+            m, n, k = rnd.randint(1, 300), rnd.randint(1, 300), rnd.randint(1, 300)
+        ta, tb = bool(rnd.randint(0, 1)), bool(rnd.randint(0, 1))
+        out_dtype = OUT_BF16 if rnd.randint(0, 1) else OUT_F32
+        epilogue = rnd.choice([EpilogueOp.StoreF32, EpilogueOp.StoreF32, EpilogueOp.BiasAddStoreF32, EpilogueOp.BiasAddReluStoreF32])
+        cfg = None
+        if rnd.random() < 0.7:
+            cfg = GemmConfig.preset(rnd.choice(presets)).with_(split_k=rnd.choice([None, None, 2, 4, 8, 16]),
+                                                              swap_grid=bool(rnd.randint(0, 1)))
+        A = oracle.rand_bf16(m * k, 9000 + case).reshape(m, k)
+        Bt = oracle.rand_bf16(n * k, 19000 + case).reshape(n, k)
+        bias = (np.arange(n, dtype=np.float32) % 7 - 3.0) * 0.25
+        ref = oracle.gemm_bf16(A, Bt, m, n, k, threads=8).reshape(m, n)
+        if epilogue != EpilogueOp.StoreF32:
+            ref = ref + bias[None, :]
+        if epilogue == EpilogueOp.BiasAddReluStoreF32:
+            ref = np.maximum(ref, 0.0)
+        got = gpu_gemm(rt, A, Bt, trans_a=ta, trans_b=tb, cfg=cfg, out_dtype=out_dtype, epilogue=int(epilogue),
+                       bias=bias if epilogue != EpilogueOp.StoreF32 else None)
+        extra = float(np.abs(ref).max()) * 2.0 ** -8 if out_dtype == OUT_BF16 else 0.0
+        try:
+            check(got, ref.astype(np.float32), k, A, Bt, extra_abs=extra + 1e-6)
+        except AssertionError as e:
+            raise AssertionError(f"case {case}: {(m, n, k)} ta={ta} tb={tb} out={out_dtype} epi={epilogue} cfg={cfg and cfg.name()}: {e}")
+    assert rt.device_status() == 0
