@@ -8,9 +8,10 @@
 // the K tail contributes zeros, :768-787) -- here the zero fill is TMA's out-of-bounds fill, so callers
 // do not have to pad.
 //
-// Roles per CTA: warp 0 = TMA producer, warp 1 = TMEM owner + MMA issuer, then one group of 4 epilogue
-// warps per accumulator owner (TMEM -> registers -> global); 192 threads, or 320 for the 2-A-tile variant.  Every wait is bounded: when a wait runs out the
-// CTA records a status code, raises its abort flag, drains, frees its TMEM and returns.
+// Roles per CTA: warp 0 = TMA producer, warp 1 = TMEM owner + MMA issuer, then four or eight epilogue warps
+// (TMEM -> registers -> shared-memory transpose tile -> TMA store or coalesced row stores): 192 threads for the
+// 64-column tile, 320 otherwise.  Every wait is bounded: when a wait runs out the CTA records a status code, raises
+// its abort flag, drains, frees its TMEM and returns.
 #pragma once
 #include <cuda_bf16.h>
 #include <cstdint>
