@@ -987,7 +987,9 @@ def run_multi(args, rank, local_rank, world):
         ingress = (world - 1) * m * sh.n_local * elem           # = egress: (G-1)/G * 2 GiB per GPU
         link_gbs = peer_gbs if peer_gbs else 713.0
         link_ms = ingress / (link_gbs * 1e9) * 1e3
-        compute_ms = flops / world / (sustained * 1e12) * 1e3
+        long_region = ms * args.steps > 1000.0          # the same rule as the one-GPU line: burst peak for a short timed region
+        peak = sustained if long_region else burst
+        compute_ms = flops / world / (peak * 1e12) * 1e3
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
@@ -998,9 +1000,9 @@ def run_multi(args, rank, local_rank, world):
                        "l2": "operands 0.5 GiB + output 2 GiB per GPU > L2, no flush", "output": "bf16"},
             "pct_of_dense_peak": 100.0 * per_gpu / DENSE_PEAK_TFLOPS,
             "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches), "checks": checks,
-            "roofline": {"bound": "tensor", "achieved": per_gpu, "peak": sustained, "unit": UNIT,
-                         "frac": per_gpu / sustained, "traffic": None,
-                         "peak_kind": f"of {kind} (sustained cuBLAS bf16), per GPU",
+            "roofline": {"bound": "tensor", "achieved": per_gpu, "peak": peak, "unit": UNIT,
+                         "frac": per_gpu / peak, "traffic": None,
+                         "peak_kind": f"of {kind} ({'sustained' if long_region else 'burst'} cuBLAS bf16), per GPU",
                          "nvlink_ingress_bytes_per_gpu": ingress,
                          "nvlink_store_gbs_measured": peer_gbs,
                          "nvlink_store_how": "t0b_copy_d2d of this rank's column block into the next rank's C, all ranks at once",
